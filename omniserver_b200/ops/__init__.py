@@ -1,0 +1,338 @@
+"""Python face of the CUDA kernels: argument checks, output allocation, launch.
+
+Every function here runs a kernel of ``csrc/`` on the current CUDA stream (or,
+for large bf16 matrix products, the vendor library's GEMM, which is where the
+reference's engine uses a library too: nn.Linear, omniserve/model/qwen2_llm.py:82-83,120-121,167).
+Tensors must live on a CUDA device; there is no CPU path.  The kernels take
+float32 and bfloat16 storage in any combination the signatures below allow.
+
+The object that does the work is ``kernels()``; model code calls it as
+``ops.kernels().<op>(...)``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import library
+from .library import KernelLibraryError
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_STATUS = {
+    10001: "unsupported dtype",
+    10002: "bad shape",
+    10003: "size not supported by this kernel",
+    10004: "size too large for this kernel",
+}
+
+_DEVICE_ERR = {
+    1: "a token id outside the vocabulary reached the embedding lookup",
+    2: "an embedding-override row outside the step's tokens",
+    3: "a cache slot outside the page pool in the key/value write",
+    4: "a page index outside the page pool in attention",
+}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda_contig(name: str, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> None:
+    _check(t.is_cuda, f"{name} must be a CUDA tensor (there is no CPU path)")
+    _check(t.is_contiguous(), f"{name} must be contiguous")
+    if dtype is not None:
+        _check(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+
+
+class CudaKernels:
+    """Launches the hand-written kernels. One instance per process."""
+
+    #: rows up to which the bf16 weight-streaming GEMM is used instead of the tiled tensor-core GEMM
+    SKINNY_MAX_ROWS = 64
+
+    def __init__(self) -> None:
+        self.lib = library.load()
+        self._err: Dict[int, torch.Tensor] = {}
+        self.launches = 0  # kernels of this library launched so far
+
+    # ------------------------------------------------------------------ plumbing
+    def _stream(self) -> ctypes.c_void_p:
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def err_flag(self, device: torch.device) -> torch.Tensor:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        if idx not in self._err:
+            self._err[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._err[idx]
+
+    def _ok(self, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc != 0:
+            why = _STATUS.get(rc, f"CUDA error {rc}")
+            raise KernelError(f"{what}: {why}")
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel recorded a bad index since the last check (synchronises)."""
+        for flag in self._err.values():
+            v = int(flag.item())
+            if v != 0:
+                flag.zero_()
+                raise KernelError("device-side check failed: " + _DEVICE_ERR.get(v, f"code {v}"))
+
+    # ------------------------------------------------------------------ embedding
+    def embed_lookup(self, table: torch.Tensor, ids: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        _cuda_contig("table", table)
+        _cuda_contig("ids", ids, torch.int32)
+        _check(table.dim() == 2 and ids.dim() == 1, "embed_lookup: table [V,H], ids [T]")
+        V, H = table.shape
+        T = ids.shape[0]
+        out = torch.empty((T, H), dtype=out_dtype, device=table.device)
+        rc = self.lib.osb_embed_lookup(_p(out), _dt(out), _p(table), _dt(table), _p(ids), T, H, V,
+                                       _p(self.err_flag(table.device)), self._stream())
+        self._ok(rc, "embed_lookup")
+        return out
+
+    def scatter_rows(self, x: torch.Tensor, rows: torch.Tensor, vals: torch.Tensor) -> None:
+        _cuda_contig("x", x)
+        _cuda_contig("rows", rows, torch.int32)
+        _cuda_contig("vals", vals)
+        _check(x.dim() == 2 and vals.dim() == 2 and vals.shape[1] == x.shape[1] and vals.shape[0] == rows.shape[0],
+               "scatter_rows: x [T,H], rows [R], vals [R,H]")
+        rc = self.lib.osb_scatter_rows(_p(x), _dt(x), _p(rows), _p(vals), _dt(vals), rows.shape[0], x.shape[1],
+                                       x.shape[0], _p(self.err_flag(x.device)), self._stream())
+        self._ok(rc, "scatter_rows")
+
+    # ------------------------------------------------------------------ norm
+    def add_rmsnorm(self, x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                    out_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+        """residual <- residual + x (or x), fp32, in place when given; returns (norm(residual)*w, residual)."""
+        _cuda_contig("x", x)
+        _cuda_contig("weight", weight)
+        _check(x.dim() == 2 and weight.shape == (x.shape[1],), "add_rmsnorm: x [T,H], weight [H]")
+        T, H = x.shape
+        if residual is None:
+            res_out = torch.empty((T, H), dtype=torch.float32, device=x.device)
+            res_in = None
+        else:
+            _cuda_contig("residual", residual, torch.float32)
+            _check(residual.shape == x.shape, "add_rmsnorm: residual must match x")
+            res_out = res_in = residual
+        y = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_add_rmsnorm(_p(y), _dt(y), _p(res_out), _p(res_in), _p(x), _dt(x), _p(weight), _dt(weight),
+                                      ctypes.c_float(eps), T, H, _p(None), self._stream())
+        self._ok(rc, "add_rmsnorm")
+        return y, res_out
+
+    def add_rmsnorm_rows(self, x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                         rows: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """norm(residual[rows] + x[rows]) * w for the given rows; nothing is written back."""
+        _cuda_contig("x", x)
+        _cuda_contig("weight", weight)
+        _cuda_contig("rows", rows, torch.int32)
+        if residual is not None:
+            _cuda_contig("residual", residual, torch.float32)
+            _check(residual.shape == x.shape, "add_rmsnorm_rows: residual must match x")
+        R, H = rows.shape[0], x.shape[1]
+        y = torch.empty((R, H), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_add_rmsnorm(_p(y), _dt(y), _p(None), _p(residual), _p(x), _dt(x), _p(weight), _dt(weight),
+                                      ctypes.c_float(eps), R, H, _p(rows), self._stream())
+        self._ok(rc, "add_rmsnorm_rows")
+        return y
+
+    # ------------------------------------------------------------------ matrix product
+    def linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
+               ) -> torch.Tensor:
+        """y[M,N] = x[M,K] @ w[N,K]^T (+ bias), fp32 accumulation."""
+        _cuda_contig("x", x)
+        _cuda_contig("w", w)
+        _check(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], "linear: x [M,K], w [N,K]")
+        if bias is not None:
+            _cuda_contig("bias", bias)
+            _check(bias.shape == (w.shape[0],), "linear: bias [N]")
+        M, K = x.shape
+        N = w.shape[0]
+        if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            return self._linear_bf16(x, w, bias, out_dtype)
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_gemm_simt(_p(y), _dt(y), _p(x), _dt(x), _p(w), _dt(w), _p(bias),
+                                    _dt(bias) if bias is not None else 0, M, N, K, self._stream())
+        self._ok(rc, "gemm_simt")
+        return y
+
+    def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
+                  ) -> torch.Tensor:
+        """The CUDA-core product for any operand types (the 32-bit path's GEMM)."""
+        M, K = x.shape
+        N = w.shape[0]
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_gemm_simt(_p(y), _dt(y), _p(x), _dt(x), _p(w), _dt(w), _p(bias),
+                                    _dt(bias) if bias is not None else 0, M, N, K, self._stream())
+        self._ok(rc, "gemm_simt")
+        return y
+
+    def _linear_bf16(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
+                     ) -> torch.Tensor:
+        M, K = x.shape
+        N = w.shape[0]
+        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and hasattr(self.lib, "osb_gemm_skinny_bf16"):
+            y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+            rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias),
+                                               _dt(bias) if bias is not None else 0, M, N, K, self._stream())
+            if rc != 10003:
+                self._ok(rc, "gemm_skinny_bf16")
+                return y
+        if K % 8 == 0 and N % 8 == 0:
+            # Library GEMM on the tensor cores (fp32 accumulation inside).
+            if out_dtype == torch.bfloat16:
+                if bias is not None and bias.dtype == torch.bfloat16:
+                    return torch.addmm(bias, x, w.t())
+                y = torch.mm(x, w.t())
+                if bias is not None:
+                    y += bias.to(torch.bfloat16)
+                return y
+            y = torch.mm(x, w.t(), out_dtype=torch.float32)
+            if bias is not None:
+                y += bias.float()
+            return y
+        return self.gemm_simt(x, w, bias, out_dtype)
+
+    # ------------------------------------------------------------------ rotary + cache write
+    def rope_tables(self, positions: torch.Tensor, pos_mode: torch.Tensor, tok_seq: torch.Tensor,
+                    cu_q: torch.Tensor, state_slot: torch.Tensor, cursor: torch.Tensor, inv_freq: torch.Tensor,
+                    axis_of: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        for n, t in (("positions", positions), ("pos_mode", pos_mode), ("tok_seq", tok_seq), ("cu_q", cu_q),
+                     ("state_slot", state_slot), ("cursor", cursor), ("axis_of", axis_of)):
+            _cuda_contig(n, t, torch.int32)
+        _cuda_contig("inv_freq", inv_freq, torch.float32)
+        T = tok_seq.shape[0]
+        half = inv_freq.shape[0]
+        _check(positions.shape == (3, T) and axis_of.shape == (half,), "rope_tables: positions [3,T], axis_of [half]")
+        cos = torch.empty((T, half), dtype=torch.float32, device=tok_seq.device)
+        sin = torch.empty_like(cos)
+        rc = self.lib.osb_rope_tables(_p(cos), _p(sin), _p(positions), _p(pos_mode), _p(tok_seq), _p(cu_q),
+                                      _p(state_slot), _p(cursor), _p(inv_freq), _p(axis_of), T, half, self._stream())
+        self._ok(rc, "rope_tables")
+        return cos, sin
+
+    def advance_cursor(self, cursor: torch.Tensor, state_slot: torch.Tensor, cu_q: torch.Tensor) -> None:
+        _cuda_contig("cursor", cursor, torch.int32)
+        rc = self.lib.osb_advance_cursor(_p(cursor), _p(state_slot), _p(cu_q), state_slot.shape[0], self._stream())
+        self._ok(rc, "advance_cursor")
+
+    def rope_kv_write(self, qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                      k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                      slot_map: Optional[torch.Tensor], nh: int, nkv: int, hd: int, rot: int) -> None:
+        """Rotate q (in place in ``qkv``) and k, write k/v into their pages. slot_map None: no write."""
+        _cuda_contig("qkv", qkv)
+        T = qkv.shape[0]
+        _check(qkv.dim() == 2 and qkv.shape[1] == (nh + 2 * nkv) * hd, "rope_kv_write: qkv [T,(nh+2nkv)*hd]")
+        if rot > 0:
+            _cuda_contig("cos", cos, torch.float32)
+            _cuda_contig("sin", sin, torch.float32)
+            _check(cos.shape == (T, rot // 2) and sin.shape == (T, rot // 2), "rope_kv_write: cos/sin [T, rot/2]")
+        page_size = num_slots = 0
+        cache_dt = _dt(qkv)
+        if slot_map is not None:
+            _cuda_contig("slot_map", slot_map, torch.int32)
+            _cuda_contig("k_cache", k_cache)
+            _cuda_contig("v_cache", v_cache)
+            _check(k_cache.dim() == 4 and k_cache.shape[1] == nkv and k_cache.shape[3] == hd
+                   and v_cache.shape == k_cache.shape and v_cache.dtype == k_cache.dtype,
+                   "rope_kv_write: caches [pages, nkv, page_size, hd]")
+            page_size = k_cache.shape[2]
+            num_slots = k_cache.shape[0] * page_size
+            cache_dt = _dt(k_cache)
+        rc = self.lib.osb_rope_kv_write(_p(qkv), _dt(qkv), _p(cos), _p(sin), _p(k_cache), _p(v_cache), cache_dt,
+                                        _p(slot_map), T, nh, nkv, hd, rot, page_size, num_slots,
+                                        _p(self.err_flag(qkv.device)), self._stream())
+        self._ok(rc, "rope_kv_write")
+
+    # ------------------------------------------------------------------ attention
+    def paged_attention(self, qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        block_table: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor, tok_seq: torch.Tensor,
+                        nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
+                        max_q_len: int, max_kv_len: int, out_dtype: torch.dtype,
+                        exact: bool = False) -> torch.Tensor:
+        """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache."""
+        _cuda_contig("qkv", qkv)
+        _cuda_contig("k_cache", k_cache)
+        _cuda_contig("v_cache", v_cache)
+        for n, t in (("block_table", block_table), ("cu_q", cu_q), ("seq_lens", seq_lens), ("tok_seq", tok_seq)):
+            _cuda_contig(n, t, torch.int32)
+        T = qkv.shape[0]
+        _check(qkv.shape[1] >= nh * hd, "paged_attention: q columns missing")
+        _check(k_cache.dim() == 4 and k_cache.shape[1] == nkv and k_cache.shape[3] == hd
+               and v_cache.shape == k_cache.shape, "paged_attention: caches [pages, nkv, page_size, hd]")
+        _check(block_table.dim() == 2 and block_table.shape[0] == seq_lens.shape[0], "paged_attention: block_table [S,*]")
+        out = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
+        win = int(window) if window else 0
+        rc = self.lib.osb_paged_attn_generic(
+            _p(out), _dt(out), _p(qkv), _dt(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _dt(k_cache),
+            _p(block_table), block_table.shape[1], _p(cu_q), _p(seq_lens), _p(tok_seq), T, nh, nkv, hd,
+            k_cache.shape[2], k_cache.shape[0], ctypes.c_float(scale), win, _p(self.err_flag(qkv.device)),
+            self._stream())
+        self._ok(rc, "paged_attn_generic")
+        return out
+
+    # ------------------------------------------------------------------ activation
+    def silu_mul(self, gu: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        _cuda_contig("gu", gu)
+        _check(gu.dim() == 2 and gu.shape[1] % 2 == 0, "silu_mul: gu [T, 2I]")
+        T, I2 = gu.shape
+        out = torch.empty((T, I2 // 2), dtype=out_dtype, device=gu.device)
+        rc = self.lib.osb_silu_mul(_p(out), _dt(out), _p(gu), _dt(gu), T, I2 // 2, self._stream())
+        self._ok(rc, "silu_mul")
+        return out
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor]
+               ) -> torch.Tensor:
+        """Token ids [R] int32: argmax where temperature <= 0, else inverse-CDF draw with the given uniforms."""
+        _cuda_contig("logits", logits, torch.float32)
+        R, V = logits.shape
+        if temperature is not None:
+            _cuda_contig("temperature", temperature, torch.float32)
+            _cuda_contig("uniform", uniform, torch.float32)
+            _check(temperature.shape == (R,) and uniform.shape == (R,), "sample: temperature/uniform [R]")
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        rc = self.lib.osb_sample(_p(out), _p(logits), _p(temperature), _p(uniform), R, V, self._stream())
+        self._ok(rc, "sample")
+        return out
+
+
+_KERNELS = None
+
+
+def kernels():
+    """The process-wide kernel object; builds and loads the CUDA library at first use."""
+    global _KERNELS
+    if _KERNELS is None:
+        if not torch.cuda.is_available():
+            raise KernelLibraryError(
+                "omniserver_b200 runs on a CUDA device (sm_100a) only; no GPU is visible to this process")
+        _KERNELS = CudaKernels()
+    return _KERNELS
+
+
+__all__ = ["kernels", "CudaKernels", "KernelError", "KernelLibraryError", "library"]

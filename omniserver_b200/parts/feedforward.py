@@ -1,0 +1,36 @@
+"""Feed-forward parts. SwiGLU: down( silu(gate(x)) * up(x) ), no biases
+(omniserve/model/qwen2_llm.py:116-134; gate and up fused into one product, gate first,
+omniserve/model/qwen2_llm.py:215-216)."""
+
+from __future__ import annotations
+
+from typing import Any, List
+
+import torch
+
+from .. import ops
+from .base import FeedForward, ParamSpec, register_feed_forward
+from .linear import Linear
+
+
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.prefix = prefix
+        self.gate_up = Linear("gate_up", hidden_size, (intermediate_size, intermediate_size), ("gate_proj", "up_proj"))
+        self.down = Linear("down", intermediate_size, (hidden_size,), ("down_proj",))
+
+    def param_specs(self) -> List[ParamSpec]:
+        return self.gate_up.param_specs() + self.down.param_specs()
+
+    def bind(self, tensors) -> None:
+        self.gate_up.bind(tensors)
+        self.down.bind(tensors)
+
+    def forward(self, ctx: Any, x: torch.Tensor) -> torch.Tensor:
+        gu = self.gate_up(x, ctx.act_dtype)
+        m = ops.kernels().silu_mul(gu, ctx.act_dtype)
+        return self.down(m, ctx.act_dtype)
+
+
+register_feed_forward("swiglu", SwiGLU)

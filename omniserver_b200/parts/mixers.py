@@ -1,0 +1,60 @@
+"""Mixers. Grouped-query attention over the paged cache.
+
+Per layer, as the reference computes it (omniserve/model/qwen2_llm.py:75-113): one fused
+projection to q, k, v (all three biased), rotary encoding of q and k, the rotated keys and
+the values appended to the cache, causal attention of the new queries over all cached keys
+of the same request (scale head_dim^-1/2, query head h reads kv head h // (nh/nkv)), and
+an output projection without bias.  A window (keys p-w+1..p) is a parameter of the part.
+"""
+
+from __future__ import annotations
+
+from typing import Any, List, Optional
+
+import torch
+
+from .. import ops
+from .base import CacheBinding, KVCacheNeed, Mixer, ParamSpec, PositionEncoding, register_mixer
+from .linear import Linear
+
+
+class GQAAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, prefix: str,
+                 position: Optional[PositionEncoding] = None, qkv_bias: bool = True, out_bias: bool = False,
+                 window: Optional[int] = None, scale: Optional[float] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        self.hidden_size, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.prefix = prefix
+        self.position = position
+        self.window = int(window) if window else None
+        self.scale = float(scale) if scale is not None else self.hd ** -0.5
+        self.qkv = Linear("qkv", hidden_size, (self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd),
+                          ("q_proj", "k_proj", "v_proj"), bias=qkv_bias)
+        self.out = Linear("o", self.nh * self.hd, (hidden_size,), ("o_proj",), bias=out_bias)
+
+    def param_specs(self) -> List[ParamSpec]:
+        return self.qkv.param_specs() + self.out.param_specs()
+
+    def bind(self, tensors) -> None:
+        self.qkv.bind(tensors)
+        self.out.bind(tensors)
+
+    def cache_needs(self) -> List[object]:
+        return [KVCacheNeed(self.nkv, self.hd, self.window)]
+
+    def forward(self, ctx: Any, x: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
+        k = ops.kernels()
+        qkv = self.qkv(x, ctx.act_dtype)
+        tables = ctx.position_tables(self.position) if self.position is not None else None
+        g = binding.group
+        k.rope_kv_write(qkv, tables.cos if tables else None, tables.sin if tables else None,
+                        binding.k_cache, binding.v_cache, ctx.slot_maps[g] if binding.writes else None,
+                        self.nh, self.nkv, self.hd, tables.rot_dim if tables else 0)
+        a = k.paged_attention(qkv, binding.k_cache, binding.v_cache, ctx.block_tables[g], ctx.cu_q, ctx.seq_lens,
+                              ctx.tok_seq, self.nh, self.nkv, self.hd, self.scale, self.window,
+                              ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype)
+        return self.out(a, ctx.act_dtype)
+
+
+register_mixer("gqa_attention", GQAAttention)
