@@ -1,0 +1,184 @@
+"""LLMEngine: the Python entry point. Names and meanings follow omniserve/engine.py:27-92
+(add_request, step, has_unfinished, abort, sequences, run_until_complete, StepDelta).
+
+A step is: schedule -> one forward of the whole mixed batch -> sample -> retire.  The reference
+runs up to two forwards per step (packed prefill, then decode or chunk+decode, engine.py:57-65);
+here the scheduler's entries always run as one batch.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from ..config import EngineConfig, resolve, resolve_dir
+from ..config.model_config import read_config_dict
+from ..sampling import Sampler
+from .request import Request, SamplingParams, Sequence, Status
+from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput
+from .step import ModelRunner, StepEntry
+
+
+@dataclass
+class StepDelta:
+    """What one request produced in one step. ``text`` is filled when a tokenizer is attached."""
+
+    request_id: str
+    new_token_ids: List[int]
+    finished: bool
+    text: str = ""
+
+
+def build_runner(model_dir: Optional[str] = None, engine_config: Optional[EngineConfig] = None,
+                 config: Optional[dict] = None, seed: int = 0, init_std: float = 0.02, norm_noise: float = 0.0,
+                 random_on_device: bool = False, allocate: bool = True) -> ModelRunner:
+    """Model + weights + cache + step function from a model folder, or from a configuration
+    dictionary and a seed (random weights)."""
+    from ..cache import CacheManager
+    from ..models import DecoderModel
+    from ..weights import fill_random, load_weights
+
+    ec = engine_config or EngineConfig()
+    dtype = ec.torch_dtype
+    device = torch.device(ec.device)
+    if model_dir is not None:
+        cfg, spec = resolve_dir(model_dir)
+    elif config is not None:
+        cfg, spec = resolve(config)
+    else:
+        raise ValueError("give a model folder or a configuration")
+    model = DecoderModel(spec)
+    if model_dir is not None:
+        load_weights(model, model_dir, dtype, device)
+    else:
+        fill_random(model, seed, dtype, device, std=init_std, norm_noise=norm_noise, on_device=random_on_device)
+    num_pages = (ec.max_cache_tokens + ec.page_size - 1) // ec.page_size
+    cache = CacheManager(model.entry_needs(), model.shared_state_needs(), ec.page_size, num_pages, ec.max_requests,
+                         dtype, device, allocate=allocate)
+    runner = ModelRunner(model, cache, dtype, device, check_device_errors=ec.check_device_errors)
+    runner.model_config = cfg
+    return runner
+
+
+class LLMEngine:
+    def __init__(self, runner: ModelRunner, sched_config: Optional[SchedulerConfig] = None, seed: int = 0,
+                 eos_token_id: Optional[int] = None, detokenize=None):
+        self.runner = runner
+        self.scheduler = Scheduler(sched_config or SchedulerConfig(), runner.cache,
+                                   on_admit=lambda s: runner.start_request(s.request_id, s.rope_delta),
+                                   on_release=lambda s: runner.end_request(s.request_id))
+        self.sampler = Sampler(seed)
+        cfg = getattr(runner, "model_config", None)
+        self.eos_token_id = eos_token_id if eos_token_id is not None else getattr(cfg, "eos_token_id", None)
+        self._detokenize = detokenize
+        self._seqs: Dict[str, Sequence] = {}
+        self._history: Dict[str, Sequence] = {}
+        self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_model_dir(cls, model_dir: str, engine_config: Optional[EngineConfig] = None,
+                       sched_config: Optional[SchedulerConfig] = None, seed: int = 0) -> "LLMEngine":
+        return cls(build_runner(model_dir=model_dir, engine_config=engine_config), sched_config, seed)
+
+    @classmethod
+    def from_random(cls, config: dict, seed: int = 0, engine_config: Optional[EngineConfig] = None,
+                    sched_config: Optional[SchedulerConfig] = None, **init) -> "LLMEngine":
+        return cls(build_runner(config=config, seed=seed, engine_config=engine_config, **init), sched_config, seed)
+
+    # ------------------------------------------------------------------ requests (omniserve/engine.py:35-51)
+    def add_request(self, request: Request) -> str:
+        seq = Sequence(request=request)
+        if request.request_id in self._seqs:
+            raise ValueError(f"request id {request.request_id!r} is already in use")
+        sp = request.sampling
+        if self.eos_token_id is not None and not sp.ignore_eos and self.eos_token_id not in sp.stop_token_ids:
+            sp.stop_token_ids.append(self.eos_token_id)   # omniserve/runners/multimodal.py:53-56
+        self.scheduler.add(seq)
+        self._seqs[seq.request_id] = seq
+        self._history[seq.request_id] = seq
+        return seq.request_id
+
+    def sequences(self) -> List[Sequence]:
+        return list(self._history.values())
+
+    def abort(self, request_id: str) -> None:
+        self.scheduler.abort(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ the step (omniserve/engine.py:53-84)
+    def step(self) -> List[StepDelta]:
+        out = self.scheduler.schedule()
+        deltas: List[StepDelta] = []
+        self.counters["preemptions"] += len(out.preempted)
+        for seq in out.aborted:
+            self._seqs.pop(seq.request_id, None)
+            deltas.append(StepDelta(seq.request_id, [], True))
+        if out.entries:
+            entries = []
+            wanting: List[Sequence] = []
+            for e in out.entries:
+                seq = e.seq
+                stop = e.start + e.count
+                rows = vals = None
+                req = seq.request
+                if req.embed_rows is not None and e.start < seq.num_prompt_tokens:
+                    pick = [i for i, r in enumerate(req.embed_rows) if e.start <= r < stop]
+                    if pick:
+                        rows = [req.embed_rows[i] - e.start for i in pick]
+                        vals = req.embed_values[pick]
+                entries.append(StepEntry(seq.request_id, seq.tokens(e.start, stop),
+                                         want=[e.count - 1] if e.wants_logits else [],
+                                         positions=seq.positions_for(e.start, stop), embed_rows=rows, embed_values=vals))
+                if e.wants_logits:
+                    wanting.append(seq)
+                self.counters["decode_tokens" if e.is_decode else "prefill_tokens"] += e.count
+            logits = self.runner.step(entries)
+            new_tokens = self.sampler.sample(logits, wanting)
+            for e in out.entries:
+                e.seq.num_computed += e.count
+                e.seq.scheduled = 0
+            for seq, tok in zip(wanting, new_tokens):
+                seq.append_token(tok)
+                seq.maybe_finish()
+            for e in out.entries:
+                seq = e.seq
+                new_ids = seq.output_token_ids[seq.num_streamed:]
+                if new_ids:
+                    seq.num_streamed = seq.num_output_tokens
+                    text = self._detokenize(new_ids) if self._detokenize else ""
+                    deltas.append(StepDelta(seq.request_id, list(new_ids), seq.status != Status.RUNNING, text))
+        self.counters["steps"] += 1
+        for seq in self.scheduler.free_finished():
+            self._seqs.pop(seq.request_id, None)
+        return deltas
+
+    def run_until_complete(self) -> Dict[str, List[int]]:
+        """Runs until every request has ended; returns the generated token ids per request."""
+        outs: Dict[str, List[int]] = {rid: [] for rid in self._seqs}
+        while self.has_unfinished():
+            for d in self.step():
+                outs.setdefault(d.request_id, []).extend(d.new_token_ids)
+        return outs
+
+    def generate(self, prompts: Seq[Seq[int]], sampling: Optional[SamplingParams] = None) -> List[List[int]]:
+        """Convenience: token-id prompts in, generated token ids out, in the prompts' order."""
+        ids = []
+        for p in prompts:
+            sp = SamplingParams(**{**sampling.__dict__, "stop_token_ids": list(sampling.stop_token_ids)}) \
+                if sampling else SamplingParams()
+            ids.append(self.add_request(Request(prompt=list(p), sampling=sp)))
+        outs = self.run_until_complete()
+        return [outs.get(i, []) for i in ids]
+
+    def stats(self) -> Dict[str, int]:
+        c = dict(self.counters)
+        c["pages_in_use"] = sum(self.runner.cache.pages_in_use())
+        c["running"] = len(self.scheduler.running)
+        c["waiting"] = len(self.scheduler.waiting)
+        return c

@@ -1,0 +1,234 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+The reference has four entry points for what is one computation — packed whole prompts, one
+chunk, decode tokens plus one chunk, decode only (omniserve/runners/base.py:31-49,
+omniserve/runners/multimodal.py:79-304); each appends ``new_len`` tokens per request at its cache
+length and attends causally over that request's cache (omniserve/cache/kv_prealloc.py:110-146).
+Here there is one: any number of requests, each bringing one or more tokens (a decoded token, a
+portion of a prompt cut anywhere, a whole prompt), flattened into one varlen batch.  It runs only
+the tokens it is given and returns fp32 logits at the wanted places.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager
+from ..models.decoder import DecoderModel
+from ..parts.positions import ROPE_STATE
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens in one step.
+
+    ``want``: places among ``tokens`` whose logits are wanted (may be empty).
+    ``positions``: int array [3, n] of (t, h, w) positions; None means the tokens continue the
+    request: cursor + rope_delta + offset on all axes.
+    ``embed_rows``/``embed_values``: places among ``tokens`` whose looked-up embedding is replaced
+    by the given rows [len(embed_rows), hidden] (the hook the vision tower's output uses).
+    """
+
+    request_id: str
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+    positions: Optional[np.ndarray] = None
+    embed_rows: Optional[Sequence[int]] = None
+    embed_values: Optional[torch.Tensor] = None
+
+
+class StepContext:
+    """Device-side description of one step, shared by all layers."""
+
+    def __init__(self) -> None:
+        self.device: torch.device = None
+        self.act_dtype: torch.dtype = None
+        self.T = self.S = self.num_logit_rows = 0
+        self.token_ids = self.cu_q = self.seq_lens = self.tok_seq = self.state_slot = None
+        self.positions = self.pos_mode = self.logit_rows = None
+        self.block_tables: List[torch.Tensor] = []
+        self.slot_maps: List[torch.Tensor] = []
+        self.override_rows: Optional[torch.Tensor] = None
+        self.override_vals: Optional[torch.Tensor] = None
+        self.max_q_len = self.max_kv_len = 0
+        self.q_lens: List[int] = []
+        self.kv_lens: List[int] = []
+        self.page_size = 0
+        self._model: Optional[DecoderModel] = None
+        self._tables: Dict[int, Any] = {}
+
+    def bind_model(self, model: DecoderModel) -> None:
+        self._model = model
+        self._tables = {}
+
+    def position_tables(self, position: Any) -> Any:
+        """Per-step tables of a position encoding, computed once and shared by the layers using it."""
+        k = id(position)
+        if k not in self._tables:
+            self._tables[k] = position.prepare(self, self._model.shared_state)
+        return self._tables[k]
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    """Owns the model, its cache and the step function."""
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, act_dtype: torch.dtype, device,
+                 check_device_errors: bool = True):
+        self.model = model
+        self.cache = cache
+        self.act_dtype = act_dtype
+        self.device = torch.device(device)
+        self.check_device_errors = check_device_errors
+        self.vocab_size = model.spec.vocab_size
+        self.hidden_size = model.spec.hidden_size
+        self.steps = 0
+        model.attach_cache(cache.bindings(), cache.shared_state())
+        self._has_rope_state = ROPE_STATE in cache.state.fields
+
+    # ------------------------------------------------------------------ request life
+    def start_request(self, request_id: str, rope_delta: int = 0) -> None:
+        rc = self.cache.begin(request_id)
+        if self._has_rope_state and self.cache.state.tensors:
+            self.cache.state.write(ROPE_STATE, rc.slot, [0, int(rope_delta)])
+
+    def end_request(self, request_id: str) -> None:
+        self.cache.finish(request_id)
+
+    def reset_request(self, request_id: str, rope_delta: int = 0) -> None:
+        self.cache.reset(request_id)
+        if self._has_rope_state and self.cache.state.tensors:
+            self.cache.state.write(ROPE_STATE, self.cache.requests[request_id].slot, [0, int(rope_delta)])
+
+    # ------------------------------------------------------------------ the step
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        cache = self.cache
+        S = len(entries)
+        if S == 0:
+            raise ValueError("a step needs at least one entry")
+        rids = [e.request_id for e in entries]
+        if len(set(rids)) != S:
+            raise ValueError("a request may appear once in a step")
+        q_lens = [len(e.tokens) for e in entries]
+        if min(q_lens) <= 0:
+            raise ValueError("every entry of a step brings at least one token")
+        T = int(sum(q_lens))
+        for e in entries:
+            if not cache.has(e.request_id):
+                raise KeyError(f"request {e.request_id!r} was not started")
+        if not cache.can_reserve(list(zip(rids, q_lens))):
+            from ..cache.page_pool import OutOfPages
+            raise OutOfPages(f"the step needs more pages than are free ({cache.free_pages()} free)")
+        for r, n in zip(rids, q_lens):
+            cache.reserve(r, n)
+
+        cu_q = np.zeros(S + 1, dtype=np.int32)
+        cu_q[1:] = np.cumsum(q_lens)
+        cursors = [cache.requests[r].cursor for r in rids]
+        kv_lens = [c + n for c, n in zip(cursors, q_lens)]
+        token_ids = np.empty(T, dtype=np.int32)
+        tok_seq = np.empty(T, dtype=np.int32)
+        positions = np.zeros((3, T), dtype=np.int32)
+        pos_mode = np.ones(S, dtype=np.int32)
+        logit_rows: List[int] = []
+        ov_rows: List[int] = []
+        ov_vals: List[torch.Tensor] = []
+        V = self.vocab_size
+        for i, e in enumerate(entries):
+            a, b = int(cu_q[i]), int(cu_q[i + 1])
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.min() < 0 or toks.max() >= V:
+                raise ValueError(f"request {e.request_id!r}: token id outside [0, {V})")
+            token_ids[a:b] = toks
+            tok_seq[a:b] = i
+            if e.positions is not None:
+                p = np.asarray(e.positions)
+                if p.shape != (3, b - a):
+                    raise ValueError(f"request {e.request_id!r}: positions must be [3, {b - a}], got {p.shape}")
+                positions[:, a:b] = p
+                pos_mode[i] = 0
+            for w in e.want:
+                if not (0 <= w < b - a):
+                    raise ValueError(f"request {e.request_id!r}: wanted place {w} outside its {b - a} tokens")
+                logit_rows.append(a + int(w))
+            if e.embed_rows is not None and len(e.embed_rows):
+                rows = [int(r) for r in e.embed_rows]
+                if min(rows) < 0 or max(rows) >= b - a:
+                    raise ValueError(f"request {e.request_id!r}: embedding row outside its tokens")
+                if e.embed_values.shape != (len(rows), self.hidden_size):
+                    raise ValueError(f"request {e.request_id!r}: embed_values must be [{len(rows)}, {self.hidden_size}]")
+                ov_rows += [a + r for r in rows]
+                ov_vals.append(e.embed_values)
+        slots = np.asarray([cache.requests[r].slot for r in rids], dtype=np.int32)
+        G = len(cache.groups)
+        bts = [cache.block_table(g, rids) for g in range(G)]
+        sms = [cache.slot_map(g, rids, q_lens) for g in range(G)]
+
+        # one staging buffer, one host-to-device copy
+        segs: List[Tuple[str, np.ndarray]] = [
+            ("token_ids", token_ids), ("cu_q", cu_q), ("seq_lens", np.asarray(kv_lens, dtype=np.int32)),
+            ("tok_seq", tok_seq), ("state_slot", slots), ("positions", positions.reshape(-1)),
+            ("pos_mode", pos_mode), ("logit_rows", np.asarray(logit_rows, dtype=np.int32)),
+            ("override_rows", np.asarray(ov_rows, dtype=np.int32)),
+        ]
+        for g in range(G):
+            segs.append((f"bt{g}", bts[g].reshape(-1)))
+            segs.append((f"sm{g}", sms[g]))
+        offs, total = {}, 0
+        for name, arr in segs:
+            offs[name] = (total, arr.size)
+            total += _align4(arr.size)
+        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        hv = host.numpy()
+        for name, arr in segs:
+            o, n = offs[name]
+            hv[o:o + n] = arr
+        dev = host.to(self.device, non_blocking=True)
+
+        def seg(name: str) -> torch.Tensor:
+            o, n = offs[name]
+            return dev[o:o + n]
+
+        ctx = StepContext()
+        ctx.device, ctx.act_dtype = self.device, self.act_dtype
+        ctx.T, ctx.S, ctx.num_logit_rows = T, S, len(logit_rows)
+        ctx.token_ids, ctx.cu_q, ctx.seq_lens = seg("token_ids"), seg("cu_q"), seg("seq_lens")
+        ctx.tok_seq, ctx.state_slot = seg("tok_seq"), seg("state_slot")
+        ctx.positions = seg("positions").view(3, T)
+        ctx.pos_mode, ctx.logit_rows = seg("pos_mode"), seg("logit_rows")
+        ctx.block_tables = [seg(f"bt{g}").view(S, bts[g].shape[1]) for g in range(G)]
+        ctx.slot_maps = [seg(f"sm{g}") for g in range(G)]
+        if ov_rows:
+            ctx.override_rows = seg("override_rows")
+            ctx.override_vals = torch.cat([v.to(self.device) for v in ov_vals], dim=0).contiguous()
+        ctx.q_lens, ctx.kv_lens = q_lens, kv_lens
+        ctx.max_q_len, ctx.max_kv_len = max(q_lens), max(kv_lens)
+        ctx.page_size = cache.page_size
+        ctx.h2d_bytes = total * 4
+        return ctx
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries as one batch; returns fp32 logits [wanted, vocab] in the order of the
+        entries and of their ``want``. The requests' tokens are in the cache afterwards."""
+        ctx = self.build_context(entries)
+        try:
+            logits = self.model.forward(ctx)
+        except Exception:
+            # the cache is in an undefined state for these requests; give the reservations back
+            for e in entries:
+                self.cache.requests[e.request_id].reserved = 0
+            raise
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps += 1
+        if self.check_device_errors:
+            ops.kernels().check_device_errors()
+        return logits

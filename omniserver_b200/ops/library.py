@@ -130,7 +130,7 @@ def build(verbose: bool = True, force: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=workers) as ex:
         objs = list(ex.map(compile_one, srcs))
     tmp = out + f".tmp{os.getpid()}"
-    p = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-lcuda"], stdout=subprocess.PIPE,
+    p = subprocess.run([nvcc, "-shared", "-o", tmp, *objs], stdout=subprocess.PIPE,
                        stderr=subprocess.STDOUT, text=True)
     if p.returncode != 0:
         raise KernelLibraryError(f"linking the kernel library failed:\n{p.stdout}")

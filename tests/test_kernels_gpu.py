@@ -1,0 +1,293 @@
+"""Each CUDA kernel alone against its plain reference (tests/plain/kernels.py), at sizes other
+than the engine's tiny models: widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd head counts and groups, in float32 and bfloat16."""
+
+import math
+
+import pytest
+import torch
+
+from plain.kernels import PlainKernels
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+REF = PlainKernels()
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from omniserver_b200 import ops
+    return ops.kernels()
+
+
+def tol(dtype):
+    # one rounding of the output: 2^-24 vs 2^-9 relative, plus accumulation-order noise
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=2e-3)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,T", [(1000, 96, 7), (777, 1536, 33), (50, 20, 1)])
+def test_embed_lookup_and_scatter(dtype, V, H, T):
+    table = rnd(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32)
+    got = K().embed_lookup(table.to(DEV), ids.to(DEV), dtype)
+    assert torch.equal(got.cpu(), REF.embed_lookup(table, ids, dtype))
+    rows = torch.tensor(sorted(set([0, T - 1, T // 2])), dtype=torch.int32)
+    vals = rnd(len(rows), H, seed=5)
+    K().scatter_rows(got, rows.to(DEV), vals.to(DEV))
+    want = REF.embed_lookup(table, ids, dtype)
+    REF.scatter_rows(want, rows, vals)
+    assert torch.equal(got.cpu(), want)
+    K().check_device_errors()
+
+
+def test_embed_lookup_reports_bad_id():
+    from omniserver_b200.ops import KernelError
+    table = rnd(10, 8)
+    ids = torch.tensor([1, 10], dtype=torch.int32)
+    K().embed_lookup(table.to(DEV), ids.to(DEV), torch.float32)
+    with pytest.raises(KernelError, match="outside the vocabulary"):
+        K().check_device_errors()
+
+
+@pytest.mark.parametrize("xdt", DTYPES)
+@pytest.mark.parametrize("wdt", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(5, 96, 1e-5), (3, 1536, 1e-6), (2, 5000, 1e-6), (1, 17, 1e-3)])
+def test_add_rmsnorm(xdt, wdt, T, H, eps):
+    x = rnd(T, H, dtype=xdt, scale=3.0)
+    res = rnd(T, H, seed=1, scale=5.0)
+    w = (1 + 0.1 * rnd(H, seed=2)).to(wdt)
+    for residual in (None, res):
+        r_dev = residual.clone().to(DEV) if residual is not None else None
+        y, r_out = K().add_rmsnorm(x.to(DEV), r_dev, w.to(DEV), eps, xdt)
+        r_ref = residual.clone() if residual is not None else None
+        y_ref, r_ref_out = REF.add_rmsnorm(x, r_ref, w, eps, xdt)
+        assert torch.allclose(r_out.cpu(), r_ref_out, rtol=0, atol=0)
+        assert torch.allclose(y.float().cpu(), y_ref.float(), **tol(xdt))
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32)
+    y = K().add_rmsnorm_rows(x.to(DEV), res.to(DEV), w.to(DEV), eps, rows.to(DEV), xdt)
+    y_ref = REF.add_rmsnorm_rows(x, res, w, eps, rows, xdt)
+    assert torch.allclose(y.float().cpu(), y_ref.float(), **tol(xdt))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K_", [(1, 200, 96), (7, 1000, 96), (33, 130, 200), (70, 64, 1536), (128, 257, 77)])
+def test_gemm_simt(dtype, M, N, K_):
+    x, w, b = rnd(M, K_, dtype=dtype), rnd(N, K_, dtype=dtype, seed=1, scale=0.05), rnd(N, dtype=dtype, seed=2)
+    for bias in (None, b):
+        got = K().gemm_simt(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, torch.float32)
+        want = REF.linear(x.double(), w.double(), bias.double() if bias is not None else None, torch.float64)
+        assert torch.allclose(got.cpu().double(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    x, w = rnd(70, 200), rnd(130, 200, seed=1)
+    whole = K().gemm_simt(x.to(DEV), w.to(DEV), None, torch.float32)
+    for a, b in [(0, 1), (5, 7), (63, 70)]:
+        part = K().gemm_simt(x[a:b].contiguous().to(DEV), w.to(DEV), None, torch.float32)
+        assert torch.equal(part, whole[a:b])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K_", [(1, 200, 96), (8, 1536, 1536), (64, 1000, 256), (200, 264, 1536), (3, 17920, 64)])
+def test_linear_bf16_and_f32(dtype, M, N, K_):
+    x, w, b = rnd(M, K_, dtype=dtype), rnd(N, K_, dtype=dtype, seed=1, scale=0.05), rnd(N, dtype=dtype, seed=2)
+    for bias in (None, b):
+        for out_dtype in (dtype, torch.float32):
+            got = K().linear(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out_dtype)
+            want = REF.linear(x, w, bias, torch.float32)
+            assert got.dtype == out_dtype
+            assert torch.allclose(got.float().cpu(), want, **tol(out_dtype if dtype == torch.float32 else dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    gu = rnd(5, 2 * 200, dtype=dtype, scale=3.0)
+    got = K().silu_mul(gu.to(DEV), dtype)
+    assert torch.allclose(got.float().cpu(), REF.silu_mul(gu, dtype).float(), **tol(dtype))
+
+
+def _rope_inputs(T, S, half, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    q_lens = [T // S] * S
+    q_lens[-1] += T - sum(q_lens)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(q_lens)])
+    positions = torch.randint(0, 5000, (3, T), generator=g, dtype=torch.int32)
+    pos_mode = torch.tensor([i % 2 for i in range(S)], dtype=torch.int32)
+    state_slot = torch.tensor([(3 * i + 1) % 8 for i in range(S)], dtype=torch.int32)
+    cursor = torch.randint(0, 3000, (8, 2), generator=g, dtype=torch.int32)
+    cursor[:, 1] -= 1500
+    cursor[:, 0] += 1500
+    return positions, pos_mode, tok_seq, cu_q, state_slot, cursor
+
+
+@pytest.mark.parametrize("hd,theta,sections", [(16, 1e4, (2, 3, 3)), (128, 1e6, (16, 24, 24)), (48, 5e4, (10, 7, 7))])
+def test_rope_tables(hd, theta, sections):
+    from omniserver_b200.parts import MRope
+    T, S = 37, 4
+    mr = MRope(hd, theta, sections)
+    inv, axis = mr._inv_freq_cpu, mr._axis_cpu
+    args = _rope_inputs(T, S, hd // 2)
+    cos, sin = K().rope_tables(*[a.to(DEV) for a in args], inv.to(DEV), axis.to(DEV))
+    cos_r, sin_r = REF.rope_tables(*args, inv, axis)
+    assert torch.allclose(cos.cpu(), cos_r, rtol=0, atol=3e-7)
+    assert torch.allclose(sin.cpu(), sin_r, rtol=0, atol=3e-7)
+    cur = args[5].clone().to(DEV)
+    K().advance_cursor(cur, args[4].to(DEV), args[3].to(DEV))
+    cur_r = args[5].clone()
+    REF.advance_cursor(cur_r, args[4], args[3])
+    assert torch.equal(cur.cpu(), cur_r)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 48, 16), (12, 2, 128, 128, 16),
+                                              (2, 2, 64, 32, 4)])
+def test_rope_kv_write(dtype, nh, nkv, hd, rot, ps):
+    T, pages = 21, 9
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype)
+    ang = rnd(T, rot // 2, seed=3, scale=3.0)
+    cos, sin = ang.cos(), ang.sin()
+    slot_map = torch.randperm(pages * ps)[:T].to(torch.int32)
+    kc, vc = torch.zeros(pages, nkv, ps, hd, dtype=dtype), torch.zeros(pages, nkv, ps, hd, dtype=dtype)
+    q_dev, kc_dev, vc_dev = qkv.clone().to(DEV), kc.clone().to(DEV), vc.clone().to(DEV)
+    K().rope_kv_write(q_dev, cos.to(DEV), sin.to(DEV), kc_dev, vc_dev, slot_map.to(DEV), nh, nkv, hd, rot)
+    q_ref = qkv.clone()
+    REF.rope_kv_write(q_ref, cos, sin, kc, vc, slot_map, nh, nkv, hd, rot)
+    t = tol(dtype)
+    assert torch.allclose(q_dev[:, :nh * hd].float().cpu(), q_ref[:, :nh * hd].float(), **t)
+    assert torch.allclose(kc_dev.float().cpu(), kc.float(), **t)
+    assert torch.equal(vc_dev.cpu(), vc)
+    # an entry that borrows a cache writes nothing
+    q2, kc2 = qkv.clone().to(DEV), torch.zeros_like(kc_dev)
+    K().rope_kv_write(q2, cos.to(DEV), sin.to(DEV), None, None, None, nh, nkv, hd, rot)
+    assert torch.equal(q2[:, :nh * hd], q_dev[:, :nh * hd]) and not kc2.any()
+    K().check_device_errors()
+
+
+def _paged_case(q_lens, kv_lens, nh, nkv, hd, ps, dtype, seed=0, pages_extra=3):
+    """Random q and a paged cache with shuffled pages for the given requests."""
+    g = torch.Generator().manual_seed(seed)
+    S, T = len(q_lens), sum(q_lens)
+    n_pages = sum(-(-kv // ps) for kv in kv_lens) + pages_extra
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-kv // ps) for kv in kv_lens)
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    for s, kv in enumerate(kv_lens):
+        for i in range(-(-kv // ps)):
+            bt[s, i] = perm.pop()
+    kc = (torch.randn(n_pages, nkv, ps, hd, generator=g)).to(dtype)
+    vc = (torch.randn(n_pages, nkv, ps, hd, generator=g)).to(dtype)
+    qkv = (torch.randn(T, (nh + 2 * nkv) * hd, generator=g)).to(dtype)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(q_lens)])
+    seq_lens = torch.tensor(kv_lens, dtype=torch.int32)
+    return qkv, kc, vc, bt, cu_q, seq_lens, tok_seq
+
+
+def _run_attn(case, nh, nkv, hd, window, dtype):
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = case
+    scale = hd ** -0.5
+    mq, mk = int((cu_q[1:] - cu_q[:-1]).max()), int(seq_lens.max())
+    got = K().paged_attention(qkv.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu_q.to(DEV), seq_lens.to(DEV),
+                              tok_seq.to(DEV), nh, nkv, hd, scale, window, mq, mk, dtype)
+    want = REF.paged_attention(qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, scale, window, mq, mk,
+                               torch.float32)
+    K().check_device_errors()
+    return got.float().cpu(), want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 16), (3, 1, 32, 16), (6, 3, 48, 8), (12, 2, 128, 16), (5, 5, 80, 32)])
+@pytest.mark.parametrize("window", [None, 20])
+def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, ps, window):
+    # a whole prompt, a decode token deep into a long context, a 2-token portion, a portion ending on a page edge
+    q_lens, kv_lens = [33, 1, 2, 16, 1], [33, 300, 47, 64, 1]
+    got, want = _run_attn(_paged_case(q_lens, kv_lens, nh, nkv, hd, ps, dtype), nh, nkv, hd, window, dtype)
+    assert torch.allclose(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 24])
+def test_paged_attention_finds_one_key_that_matters(dtype, window):
+    """Random keys give near-uniform softmax, which hides a missed key among hundreds. Here one key
+    is made to dominate: its score is ~25 above the rest, its value is distinctive. Placed at the
+    first key, at both sides of page edges, at the window's edge and just outside it, and at the
+    query itself, the output must be that value or, when the key is not visible, must not change."""
+    nh, nkv, hd, ps = 4, 2, 32, 16
+    kv_len, q_len = 200, 3
+    for qi in range(q_len):
+        p = kv_len - q_len + qi
+        spots = [0, 15, 16, 17, p - 1, p, p + 1 if p + 1 < kv_len else p]
+        if window:
+            spots += [p - window + 1, p - window, p - window + 2]
+        for j in spots:
+            case = list(_paged_case([q_len], [kv_len], nh, nkv, hd, ps, dtype, seed=j + 7))
+            qkv, kc, vc, bt = case[0], case[1], case[2], case[3]
+            t = qi
+            for kvh in range(nkv):
+                # the key at j is aligned with the queries of the heads of this group
+                qh = qkv[t, (kvh * (nh // nkv)) * hd:(kvh * (nh // nkv) + 1) * hd].float()
+                for h in range(kvh * (nh // nkv), (kvh + 1) * (nh // nkv)):
+                    qkv[t, h * hd:(h + 1) * hd] = qh.to(dtype)
+                kvec = qh / qh.norm() ** 2 * 25.0 * math.sqrt(hd)
+                page = int(bt[0, j // ps])
+                kc[page, kvh, j % ps] = kvec.to(dtype)
+                vc[page, kvh, j % ps] = 7.0
+            got, want = _run_attn(tuple(case), nh, nkv, hd, window, dtype)
+            visible = j <= p and (not window or j > p - window)
+            assert torch.allclose(got, want, **tol(dtype)), f"key {j}, query at {p}"
+            if visible:
+                assert got[t].mean() > 6.5, f"key {j} should dominate the query at {p}"
+            else:
+                assert got[t].abs().mean() < 2.0, f"key {j} must be invisible to the query at {p}"
+
+
+def test_paged_attention_fp32_is_independent_of_the_batch():
+    """In 32-bit the kernel's sums run in an order fixed by absolute key positions: a request's
+    output is bitwise the same alone, cut into portions, or beside other requests."""
+    nh, nkv, hd, ps = 6, 3, 48, 16
+    full = _paged_case([70], [70], nh, nkv, hd, ps, torch.float32, seed=11)
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = full
+    whole, _ = _run_attn(full, nh, nkv, hd, None, torch.float32)
+    # last 5 tokens as a portion beside another request's decode token
+    other = _paged_case([1], [40], nh, nkv, hd, ps, torch.float32, seed=12)
+    n_pages = kc.shape[0]
+    kc2, vc2 = torch.cat([kc, other[1]]), torch.cat([vc, other[2]])
+    bt2 = torch.full((2, bt.shape[1]), -1, dtype=torch.int32)
+    bt2[1] = bt[0]
+    bt2[0, :other[3].shape[1]] = other[3][0] + n_pages
+    qkv2 = torch.cat([other[0], qkv[65:70]])
+    case = (qkv2, kc2, vc2, bt2, torch.tensor([0, 1, 6], dtype=torch.int32), torch.tensor([40, 70], dtype=torch.int32),
+            torch.tensor([0, 1, 1, 1, 1, 1], dtype=torch.int32))
+    part, _ = _run_attn(case, nh, nkv, hd, None, torch.float32)
+    assert torch.equal(part[1:], whole[65:70])
+
+
+@pytest.mark.parametrize("V", [512, 1000, 151936])
+def test_sample_greedy_and_temperature(V):
+    R = 5
+    logits = rnd(R, V, scale=2.0)
+    logits[1, 7] = logits[1, 900 % V] = logits[1].max() + 1   # a tie: the lowest index wins
+    got = K().sample(logits.to(DEV), None, None).cpu()
+    assert torch.equal(got, REF.sample(logits, None, None))
+    temps = torch.tensor([0.8, 0.0, 1.5, 0.3, 1.0])
+    for trial in range(8):
+        u = torch.rand(R, generator=torch.Generator().manual_seed(trial))
+        got = K().sample(logits.to(DEV), temps.to(DEV), u.to(DEV)).cpu()
+        for r in range(R):
+            if temps[r] == 0:
+                assert got[r] == logits[r].argmax() or logits[r, got[r]] == logits[r].max()
+                continue
+            # the chosen index's CDF interval must hold u up to float32 rounding of the running sum
+            p = torch.softmax(logits[r].double() / float(temps[r]), -1)
+            cdf = torch.cumsum(p, 0)
+            i = int(got[r])
+            lo = float(cdf[i - 1]) if i > 0 else 0.0
+            assert lo - 1e-4 <= float(u[r]) <= float(cdf[i]) + 1e-4, f"row {r}: u={float(u[r])} not in [{lo}, {float(cdf[i])}]"

@@ -1,0 +1,176 @@
+"""Replay on the GPU against the plain implementation: each request alone and whole; most of it
+in one step and the last 32 tokens one by one; in portions of changing size down to two tokens;
+and mixed, up to four live requests with so few pages that they are used again — in 32-bit and in
+bfloat16, in process and through bin/trace_run."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import replay_cases as rc
+from helpers import make_model_dir, plain_model
+from plain import model as pm
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+FAMILIES = {"whole": rc.whole, "tail": rc.tail_decode, "portions": rc.portions, "mixed": rc.mixed}
+# 32-bit: sums in another order than the plain implementation's, nothing else.
+# bfloat16: activations are rounded to 8 bits of mantissa between kernels; logits are O(1).
+TOL = {"float32": dict(max_abs=6e-5, rel_fro=2e-5), "bfloat16": dict(max_abs=6e-2, rel_fro=2.5e-2)}
+
+
+def check(got, want, dtype, what):
+    err = (got.double() - want.double())
+    max_abs = err.abs().max().item()
+    rel = (err.norm() / want.double().norm()).item()
+    t = TOL[dtype]
+    assert max_abs < t["max_abs"] * max(1.0, want.abs().max().item()) and rel < t["rel_fro"], \
+        f"{what}: max abs {max_abs:.3e}, relative {rel:.3e}"
+
+
+def requests_for(vocab, lens=(5, 17, 33, 70, 100, 41), seed=3):
+    g = torch.Generator().manual_seed(seed)
+    return {f"r{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(lens)}
+
+
+def runner_for(model_dir, dtype, max_tokens, page_size=16, poison=True):
+    from omniserver_b200 import EngineConfig, build_runner
+    ec = EngineConfig(dtype=dtype, page_size=page_size, max_cache_tokens=max_tokens, max_requests=8)
+    r = build_runner(model_dir=model_dir, engine_config=ec)
+    r.cache.poison_freed = poison   # a read of a page that was given back shows up as NaN
+    return r
+
+
+def replay_in_process(runner, steps):
+    from omniserver_b200.replay import TraceReplayer
+    rp, outs = TraceReplayer(runner), {}
+    with torch.inference_mode():
+        for st in steps:
+            lg = rp.run_step(st)
+            if lg is not None:
+                outs[st["step"]] = lg.float().cpu()
+            runner.cache.check_invariants()
+    assert not runner.cache.requests and all(p == 0 for p in runner.cache.pages_in_use())
+    return outs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_replay_matches_plain(dtype, name, family, tmp_path):
+    store = "float32" if dtype == "float32" else "bfloat16"
+    d = make_model_dir(tmp_path, name, store)
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V)
+    steps = FAMILIES[family](reqs)
+    runner = runner_for(d, dtype, rc.max_live_tokens(steps))
+    got = rc.collect(steps, replay_in_process(runner, steps))
+    for rid, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        assert torch.isfinite(got[rid]).all(), f"{family}/{rid}: non-finite logits (a stale page was read?)"
+        check(got[rid], want, dtype, f"{name}/{family}/{rid}")
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
+def test_fp32_logits_do_not_depend_on_the_cut(name, tmp_path):
+    """In 32-bit every kernel sums in an order fixed by the element, so whole, token by token,
+    portions and mixed batches give bitwise the same logits."""
+    d = make_model_dir(tmp_path, name, "float32")
+    cfg, _ = plain_model(d)
+    reqs = requests_for(cfg.V)
+    base = None
+    for family, make in FAMILIES.items():
+        steps = make(reqs)
+        got = rc.collect(steps, replay_in_process(runner_for(d, "float32", rc.max_live_tokens(steps)), steps))
+        if base is None:
+            base = got
+        else:
+            for rid in reqs:
+                assert torch.equal(got[rid], base[rid]), f"{family}/{rid} differs from whole"
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_long_decoding_and_first_tokens(page_size, tmp_path):
+    """A request decoded one token at a time from its first token on, over many pages."""
+    d = make_model_dir(tmp_path, "tiny_c", "float32")
+    cfg, w = plain_model(d)
+    toks = requests_for(cfg.V, (300,), seed=9)["r0"]
+    steps = [{"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": ["x"] if i == len(toks) - 1 else []}
+             for i, t in enumerate(toks)]
+    got = rc.collect(steps, replay_in_process(runner_for(d, "float32", 320, page_size), steps))
+    check(got["x"], pm.forward(cfg, w, torch.tensor(toks)), "float32", "long decode")
+
+
+def test_positions_and_embeddings_given_with_the_prompt(tmp_path):
+    """A prompt with a 24-token span whose embeddings are given and whose positions run over a
+    4 x 6 grid; text after it resumes at max + 1. Cut into portions of 16 that split the span."""
+    d = make_model_dir(tmp_path, "tiny_b", "float32")
+    cfg, w = plain_model(d)
+    L, start = 100, 10
+    toks = requests_for(cfg.V, (L,), seed=5)["r0"]
+    pos, delta = pm.image_span_positions(L, start, 1, 4, 6)
+    rows = torch.arange(start, start + 24)
+    vals = torch.randn(24, cfg.H, generator=torch.Generator().manual_seed(2))
+    want = pm.forward(cfg, w, torch.tensor(toks), pos, rows, vals)
+    steps = []
+    for i, a in enumerate(range(0, L, 16)):
+        b = min(a + 16, L)
+        pick = [r for r in range(a, b) if start <= r < start + 24]
+        e = {"id": "img", "tokens": toks[a:b], "want": list(range(b - a)), "positions": pos[:, a:b].tolist()}
+        if pick:
+            e["embeds"] = {"rows": [r - a for r in pick], "values": vals[[r - start for r in pick]].tolist()}
+        steps.append({"step": i, "entries": [e], "end": []})
+    # then decoded tokens continue at cursor + rope_delta on all axes
+    extra = requests_for(cfg.V, (6,), seed=6)["r0"]
+    runner = runner_for(d, "float32", 128)
+    from omniserver_b200.engine.step import StepEntry
+    with torch.inference_mode():
+        runner.start_request("img", rope_delta=delta)
+        outs = []
+        for st in steps:
+            e = st["entries"][0]
+            emb = e.get("embeds")
+            outs.append(runner.step([StepEntry("img", e["tokens"], e["want"], np.asarray(e["positions"]),
+                                               emb["rows"] if emb else None,
+                                               torch.tensor(emb["values"]) if emb else None)]).cpu())
+        for t in extra:
+            outs.append(runner.step([StepEntry("img", [t], [0])]).cpu())
+        runner.end_request("img")
+    got = torch.cat(outs)
+    full = toks + extra
+    pos_full = pm.extend_positions(pos, delta, len(full))
+    want_full = pm.forward(cfg, w, torch.tensor(full), pos_full, rows, vals)
+    check(got, want_full, "float32", "image span")
+    assert delta == -18
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """The program itself: JSON lines in, <step>.f32 files and 'done <step>' lines out."""
+    d = make_model_dir(tmp_path, "tiny_b", "float32" if dtype == "float32" else "bfloat16")
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V, (40, 9, 64, 100, 23), seed=8)
+    steps = rc.mixed(reqs, seed=4)
+    steps.append({"step": len(steps), "entries": [{"id": "nolog", "tokens": [1, 2, 3], "want": []}], "end": ["nolog"]})
+    out = tmp_path / "out"
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(rc.max_live_tokens(steps))],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    assert not (out / f"{len(steps) - 1}.f32").exists()
+    outputs = {}
+    for st in steps[:-1]:
+        n = sum(len(e["want"]) for e in st["entries"])
+        arr = np.fromfile(out / f"{st['step']}.f32", dtype="<f4")
+        assert arr.size == n * cfg.V
+        outputs[st["step"]] = torch.from_numpy(arr.reshape(n, cfg.V).copy())
+    got = rc.collect(steps[:-1], outputs)
+    for rid, toks in reqs.items():
+        check(got[rid], pm.forward(cfg, w, torch.tensor(toks)), dtype, f"trace_run/{rid}")
