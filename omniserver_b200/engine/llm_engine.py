@@ -32,6 +32,7 @@ class StepDelta:
     text: str = ""
 
 
+@torch.inference_mode(False)   # weights, caches and state outlive any inference-mode block of the caller
 def build_runner(model_dir: Optional[str] = None, engine_config: Optional[EngineConfig] = None,
                  config: Optional[dict] = None, seed: int = 0, init_std: float = 0.02, norm_noise: float = 0.0,
                  random_on_device: bool = False, allocate: bool = True) -> ModelRunner:

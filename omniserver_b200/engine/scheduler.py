@@ -164,9 +164,10 @@ class Scheduler:
                 grant(seq, n)
                 budget -= n
 
-        # 3) admit new requests while there is room for them to start
+        # 3) admit new requests while there is room for them to start (never in a step that had to
+        #    preempt: the pages just won back are for the requests that are running)
         admitted = 0
-        while (self.waiting and len(self.running) < cfg.max_running and admitted < cfg.max_prefill_per_step
+        while (not out.preempted and self.waiting and len(self.running) < cfg.max_running and admitted < cfg.max_prefill_per_step
                and budget > 0 and cache.state.num_free > 0 and all(f > 0 for f in free)):
             seq = self.waiting.popleft()
             if seq.status == Status.ABORTED:

@@ -215,6 +215,7 @@ class ModelRunner:
         ctx.h2d_bytes = total * 4
         return ctx
 
+    @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries as one batch; returns fp32 logits [wanted, vocab] in the order of the
         entries and of their ``want``. The requests' tokens are in the cache afterwards."""

@@ -83,7 +83,8 @@ class CudaKernels:
     def err_flag(self, device: torch.device) -> torch.Tensor:
         idx = device.index if device.index is not None else torch.cuda.current_device()
         if idx not in self._err:
-            self._err[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+            with torch.inference_mode(False):  # a lasting tensor: must stay writable outside inference mode
+                self._err[idx] = torch.zeros(1, dtype=torch.int32, device=device)
         return self._err[idx]
 
     def _ok(self, rc: int, what: str) -> None:

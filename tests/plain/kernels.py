@@ -45,9 +45,10 @@ class PlainKernels:
 
     # -- matrix product
     def linear(self, x, w, bias, out_dtype):
-        y = x.float() @ w.float().T
+        acc = torch.float64 if x.dtype == torch.float64 else torch.float32
+        y = x.to(acc) @ w.to(acc).T
         if bias is not None:
-            y = y + bias.float()
+            y = y + bias.to(acc)
         return y.to(out_dtype)
 
     gemm_simt = linear

@@ -101,9 +101,11 @@ def test_linear_bf16_and_f32(dtype, M, N, K_):
     for bias in (None, b):
         for out_dtype in (dtype, torch.float32):
             got = K().linear(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out_dtype)
-            want = REF.linear(x, w, bias, torch.float32)
+            want = REF.linear(x.double(), w.double(), bias.double() if bias is not None else None, torch.float64)
             assert got.dtype == out_dtype
-            assert torch.allclose(got.float().cpu(), want, **tol(out_dtype if dtype == torch.float32 else dtype))
+            # against a float64 reference: fp32 accumulation over K in another order, then one rounding of the output
+            t = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else tol(dtype)
+            assert torch.allclose(got.double().cpu(), want, **t)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
