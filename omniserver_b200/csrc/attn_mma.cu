@@ -1,0 +1,563 @@
+// bf16 attention over the paged cache on the tensor cores (m16n8k16 MMA, fp32 scores, softmax and
+// accumulators), for the serving path.
+//
+//  * attn_prefill_kernel: requests that bring two or more tokens (prompt portions, whole prompts).
+//    One CTA = 64 query rows of one (request, query head); keys and values stream through shared
+//    memory in tiles of 64 keys gathered page by page with cp.async; online softmax.
+//  * attn_decode_kernel: requests that bring exactly one token. One CTA = one (request, kv head,
+//    split of the keys); the query heads of the group share every key/value load; the four warps
+//    take different keys of each tile and are merged at the end. Splits of the key range end at
+//    fixed absolute boundaries; their partial results (unnormalised output, running max, sum) go
+//    to scratch memory and attn_decode_reduce_kernel merges them in split order.
+//
+// Semantics as in attn_generic.cu (omniserve/model/qwen2_llm.py:96-112, omniserve/cache/kv_prealloc.py:138-142):
+// scale on the scores, query at absolute position p sees keys max(0, p-window+1)..p of its own
+// request, query head h reads kv head h / (nh/nkv).
+// Cache layout: [pages, kv_heads, page_size, head_dim]; a page id < 0 marks a page given back (its
+// keys are outside every window and are read as zeros, then masked).
+#include "mma_utils.cuh"
+
+namespace {
+constexpr int TILE_N = 64;
+constexpr int NTHREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// Copies keys [key0, key0 + TILE_N) of one kv head into a shared tile [TILE_N][hd + 8].
+__device__ __forceinline__ void load_kv_tile_async(bf16* tile, const bf16* __restrict__ cache,
+                                                   const int* __restrict__ bt, int kvh, int nkv, int ps, int hd,
+                                                   int key0, int kv_end, int num_pages, int tid) {
+  const int cpr = hd >> 3;  // 16-byte chunks per row
+  const int stride = hd + 8;
+  int r = tid / cpr, c = tid - r * cpr;
+  const int dr = NTHREADS / cpr, dc = NTHREADS - dr * cpr;
+  while (r < TILE_N) {
+    const int key = key0 + r;
+    bool valid = key < kv_end;
+    const bf16* src = cache;
+    if (valid) {
+      const int pi = key / ps;
+      const int page = bt[pi];
+      valid = page >= 0 && page < num_pages;
+      if (valid) src = cache + (((size_t)page * nkv + kvh) * ps + (key - pi * ps)) * hd + c * 8;
+    }
+    cp_async16(tile + r * stride + c * 8, src, valid);
+    r += dr;
+    c += dc;
+    if (c >= cpr) {
+      c -= cpr;
+      ++r;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prefill: 64 query rows per CTA, 16 per warp.
+template <int HD_MAX>
+__global__ void __launch_bounds__(NTHREADS) attn_prefill_kernel(
+    bf16* __restrict__ out, const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ kc,
+    const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
+    const int* __restrict__ seq_lens, int nh, int nkv, int hd, int ps, int num_pages, float scale_log2, int window,
+    int skip_single) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int stride = hd + 8;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [64][stride]
+  bf16* kvs = qs + 64 * stride;                  // 2 stages x (K, V) x [TILE_N][stride]
+  const int tile_elems = TILE_N * stride;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m_tile = gridDim.x - 1 - blockIdx.x;  // long tiles first
+  const int h = blockIdx.y, s = blockIdx.z;
+  const int q0 = cu_q[s], q_len = cu_q[s + 1] - q0;
+  if (q_len <= 0 || (skip_single && q_len == 1)) return;
+  const int m0 = m_tile * 64;
+  if (m0 >= q_len) return;
+  const int g = nh / nkv, kvh = h / g;
+  const int kv_len = seq_lens[s];
+  const int rows_here = min(64, q_len - m0);
+  const int p_first = kv_len - q_len + m0;
+  const int p_last = p_first + rows_here - 1;
+  const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int tile_begin = lo / TILE_N, tile_end = p_last / TILE_N;  // inclusive
+  const int* bt = block_table + (size_t)s * bt_stride;
+  const int kv_end = p_last + 1;
+
+  {  // Q tile
+    const int cpr = hd >> 3;
+    for (int i = tid; i < 64 * cpr; i += NTHREADS) {
+      const int r = i / cpr, c = i - r * cpr;
+      const bool valid = r < rows_here;
+      const bf16* src = valid ? q + (size_t)(q0 + m0 + r) * q_row_stride + (size_t)h * hd + c * 8 : q;
+      cp_async16(qs + r * stride + c * 8, src, valid);
+    }
+  }
+  load_kv_tile_async(kvs, kc, bt, kvh, nkv, ps, hd, tile_begin * TILE_N, kv_end, num_pages, tid);
+  load_kv_tile_async(kvs + tile_elems, vc, bt, kvh, nkv, ps, hd, tile_begin * TILE_N, kv_end, num_pages, tid);
+  cp_async_commit();
+
+  constexpr int KS = HD_MAX / 16;  // k-steps of QK^T, pairs of n-tiles of PV
+  const int ks_n = hd >> 4;
+  unsigned qf[KS][4];
+  float o[KS * 2][4];
+#pragma unroll
+  for (int i = 0; i < KS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const int g0 = lane >> 2, c2 = (lane & 3) * 2;
+  const int row_l[2] = {warp * 16 + g0, warp * 16 + g0 + 8};
+  int p_row[2], lo_row[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    p_row[hh] = row_l[hh] < rows_here ? p_first + row_l[hh] : -1;
+    lo_row[hh] = (window > 0 && p_row[hh] - window + 1 > 0) ? p_row[hh] - window + 1 : 0;
+  }
+  const bool warp_active = warp * 16 < rows_here;
+  const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix index and row within it
+
+  for (int t = tile_begin; t <= tile_end; ++t) {
+    const int st = (t - tile_begin) & 1;
+    if (t + 1 <= tile_end) {
+      bf16* nk = kvs + (st ^ 1) * 2 * tile_elems;
+      load_kv_tile_async(nk, kc, bt, kvh, nkv, ps, hd, (t + 1) * TILE_N, kv_end, num_pages, tid);
+      load_kv_tile_async(nk + tile_elems, vc, bt, kvh, nkv, ps, hd, (t + 1) * TILE_N, kv_end, num_pages, tid);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* ks = kvs + st * 2 * tile_elems;
+    const bf16* vs = ks + tile_elems;
+    if (t == tile_begin) {
+#pragma unroll
+      for (int k = 0; k < KS; ++k)
+        if (k < ks_n)
+          ldmatrix_x4(qf[k][0], qf[k][1], qf[k][2], qf[k][3],
+                      qs + (warp * 16 + lr + (lm & 1) * 8) * stride + k * 16 + (lm >> 1) * 8);
+    }
+    // a warp whose rows all lie before this tile's first key has nothing to do here
+    const int key0 = t * TILE_N;
+    if (warp_active && key0 <= p_first + min(warp * 16 + 15, rows_here - 1)) {
+      float sc[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        if (k < ks_n) {
+#pragma unroll
+          for (int np = 0; np < 4; ++np) {
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, ks + (np * 16 + lr + (lm >> 1) * 8) * stride + k * 16 + (lm & 1) * 8);
+            mma_bf16_16816(sc[np * 2], qf[k], b0, b1);
+            mma_bf16_16816(sc[np * 2 + 1], qf[k], b2, b3);
+          }
+        }
+      }
+      // scale, mask, online softmax
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + n * 8 + c2 + e;
+            float v = sc[n][hh * 2 + e] * scale_log2;
+            if (key > p_row[hh] || key < lo_row[hh]) v = -INFINITY;
+            sc[n][hh * 2 + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[hh], mx);
+        const float alpha = (m_run[hh] == -INFINITY) ? 0.0f : fast_exp2(m_run[hh] - m_new);
+        float sum = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float v = sc[n][hh * 2 + e];
+            const float p = (v == -INFINITY) ? 0.0f : fast_exp2(v - m_new);
+            sc[n][hh * 2 + e] = p;
+            sum += p;
+          }
+        }
+        l_run[hh] = l_run[hh] * alpha + sum;
+        m_run[hh] = m_new;
+#pragma unroll
+        for (int i = 0; i < KS * 2; ++i) {
+          o[i][hh * 2] *= alpha;
+          o[i][hh * 2 + 1] *= alpha;
+        }
+      }
+      // O += P V
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        unsigned pa[4];
+        pa[0] = pack_bf16(sc[kk * 2][0], sc[kk * 2][1]);
+        pa[1] = pack_bf16(sc[kk * 2][2], sc[kk * 2][3]);
+        pa[2] = pack_bf16(sc[kk * 2 + 1][0], sc[kk * 2 + 1][1]);
+        pa[3] = pack_bf16(sc[kk * 2 + 1][2], sc[kk * 2 + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < KS; ++dp) {
+          if (dp < ks_n) {
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + lr + (lm & 1) * 8) * stride + dp * 16 + (lm >> 1) * 8);
+            mma_bf16_16816(o[dp * 2], pa, b0, b1);
+            mma_bf16_16816(o[dp * 2 + 1], pa, b2, b3);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  if (!warp_active) return;
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    float l = l_run[hh];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (row_l[hh] >= rows_here) continue;
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    bf16* op = out + ((size_t)(q0 + m0 + row_l[hh]) * nh + h) * hd;
+#pragma unroll
+    for (int i = 0; i < KS * 2; ++i) {
+      const int d = i * 8 + c2;
+      if (d < hd)
+        *reinterpret_cast<__nv_bfloat162*>(op + d) = __floats2bfloat162_rn(o[i][hh * 2] * inv, o[i][hh * 2 + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode: one token per request. grid = (splits, kv heads x head tiles, requests).
+template <int HD_MAX, int STAGES>
+__global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+    int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+    const int* __restrict__ decode_index, int nh, int nkv, int hd, int ps, int num_pages, float scale_log2,
+    int window, int chunk, int nsplits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int stride = hd + 8;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [16][stride]; later the warps' (max, sum)
+  bf16* kvs = qs + 16 * stride;                  // STAGES x (K, V) x [TILE_N][stride]; later the warps' outputs
+  const int tile_elems = TILE_N * stride;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, s = blockIdx.z;
+  const int g = nh / nkv;
+  const int head_tiles = (g + 15) >> 4;
+  const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
+  const int q0 = cu_q[s];
+  if (cu_q[s + 1] - q0 != 1) return;
+  const int rows = min(16, g - ht * 16);
+  const int head0 = kvh * g + ht * 16;
+  const int kv_len = seq_lens[s];
+  const int p = kv_len - 1;
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int first_split = lo / chunk, last_split = p / chunk;
+  if (split < first_split || split > last_split) return;
+  const int k_begin = max(split * chunk, (lo / TILE_N) * TILE_N);
+  const int k_end = min((split + 1) * chunk, kv_len);
+  const int ntiles = (k_end - k_begin + TILE_N - 1) / TILE_N;
+  const int* bt = block_table + (size_t)s * bt_stride;
+
+  {  // the group's query rows
+    const int cpr = hd >> 3;
+    for (int i = tid; i < 16 * cpr; i += NTHREADS) {
+      const int r = i / cpr, c = i - r * cpr;
+      const bool valid = r < rows;
+      const bf16* src = valid ? q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * hd + c * 8 : q;
+      cp_async16(qs + r * stride + c * 8, src, valid);
+    }
+  }
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < ntiles) {
+      bf16* dst = kvs + st * 2 * tile_elems;
+      load_kv_tile_async(dst, kc, bt, kvh, nkv, ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
+      load_kv_tile_async(dst + tile_elems, vc, bt, kvh, nkv, ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
+    }
+    cp_async_commit();
+  }
+
+  constexpr int KS = HD_MAX / 16;
+  const int ks_n = hd >> 4;
+  unsigned qf[KS][4];
+  float o[KS * 2][4];
+#pragma unroll
+  for (int i = 0; i < KS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const int g0 = lane >> 2, c2 = (lane & 3) * 2;
+  const int lm = lane >> 3, lr = lane & 7;
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int st = t % STAGES;
+    {
+      const int tn = t + STAGES - 1;
+      if (tn < ntiles) {
+        bf16* dst = kvs + (tn % STAGES) * 2 * tile_elems;
+        load_kv_tile_async(dst, kc, bt, kvh, nkv, ps, hd, k_begin + tn * TILE_N, k_end, num_pages, tid);
+        load_kv_tile_async(dst + tile_elems, vc, bt, kvh, nkv, ps, hd, k_begin + tn * TILE_N, k_end, num_pages, tid);
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+    const bf16* ks = kvs + st * 2 * tile_elems;
+    const bf16* vs = ks + tile_elems;
+    if (t == 0) {
+#pragma unroll
+      for (int k = 0; k < KS; ++k)
+        if (k < ks_n)
+          ldmatrix_x4(qf[k][0], qf[k][1], qf[k][2], qf[k][3], qs + (lr + (lm & 1) * 8) * stride + k * 16 + (lm >> 1) * 8);
+    }
+    const int kbase = k_begin + t * TILE_N + warp * 16;  // this warp's 16 keys of the tile
+    if (kbase < k_end && kbase + 15 >= lo) {
+      float sc[2][4];
+      sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = 0.0f;
+      sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.0f;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        if (k < ks_n) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3, ks + (warp * 16 + lr + (lm >> 1) * 8) * stride + k * 16 + (lm & 1) * 8);
+          mma_bf16_16816(sc[0], qf[k], b0, b1);
+          mma_bf16_16816(sc[1], qf[k], b2, b3);
+        }
+      }
+      // every row is the same query position: the mask depends on the key only
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = kbase + n * 8 + c2 + e;
+          const bool vis = key < k_end && key >= lo;
+          const float v0 = vis ? sc[n][e] * scale_log2 : -INFINITY;
+          const float v1 = vis ? sc[n][2 + e] * scale_log2 : -INFINITY;
+          sc[n][e] = v0;
+          sc[n][2 + e] = v1;
+          mx0 = fmaxf(mx0, v0);
+          mx1 = fmaxf(mx1, v1);
+        }
+      }
+      float mx[2] = {mx0, mx1};
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float v = mx[hh];
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        const float m_new = fmaxf(m_run[hh], v);
+        const float alpha = (m_run[hh] == -INFINITY) ? 0.0f : fast_exp2(m_run[hh] - m_new);
+        float sum = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float x = sc[n][hh * 2 + e];
+            const float pe = (x == -INFINITY) ? 0.0f : fast_exp2(x - m_new);
+            sc[n][hh * 2 + e] = pe;
+            sum += pe;
+          }
+        }
+        l_run[hh] = l_run[hh] * alpha + sum;
+        m_run[hh] = m_new;
+#pragma unroll
+        for (int i = 0; i < KS * 2; ++i) {
+          o[i][hh * 2] *= alpha;
+          o[i][hh * 2 + 1] *= alpha;
+        }
+      }
+      unsigned pa[4];
+      pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+      pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+      pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+      pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < KS; ++dp) {
+        if (dp < ks_n) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, vs + (warp * 16 + lr + (lm & 1) * 8) * stride + dp * 16 + (lm >> 1) * 8);
+          mma_bf16_16816(o[dp * 2], pa, b0, b1);
+          mma_bf16_16816(o[dp * 2 + 1], pa, b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps (each saw different keys) in warp order
+  float* wml = reinterpret_cast<float*>(qs);   // [4][16][2]
+  float* wo = reinterpret_cast<float*>(kvs);   // [4][16][hd]
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    float l = l_run[hh];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int r = g0 + hh * 8;
+    if ((lane & 3) == 0) {
+      wml[(warp * 16 + r) * 2] = m_run[hh];
+      wml[(warp * 16 + r) * 2 + 1] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < KS * 2; ++i) {
+      const int d = i * 8 + c2;
+      if (d < hd) {
+        wo[(warp * 16 + r) * hd + d] = o[i][hh * 2];
+        wo[(warp * 16 + r) * hd + d + 1] = o[i][hh * 2 + 1];
+      }
+    }
+  }
+  __syncthreads();
+  const bool direct = first_split == last_split;
+  const int drow = decode_index[s];
+  for (int idx = tid; idx < rows * hd; idx += NTHREADS) {
+    const int r = idx / hd, d = idx - r * hd;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, wml[(w * 16 + r) * 2]);
+    float L = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = wml[(w * 16 + r) * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - M);
+      L += wml[(w * 16 + r) * 2 + 1] * f;
+      acc += wo[(w * 16 + r) * hd + d] * f;
+    }
+    const int head = head0 + r;
+    if (direct) {
+      out[((size_t)q0 * nh + head) * hd + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+    } else {
+      const size_t prow = ((size_t)drow * nh + head) * nsplits + split;
+      part_o[prow * hd + d] = acc;
+      if (d == 0) {
+        part_ml[prow * 2] = M;
+        part_ml[prow * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Merges the splits of every decode row in split order. One warp per (request, head).
+__global__ void __launch_bounds__(128) attn_decode_reduce_kernel(
+    bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+    const int* __restrict__ cu_q, const int* __restrict__ seq_lens, const int* __restrict__ decode_index, int S,
+    int nh, int hd, int window, int chunk, int nsplits) {
+  const int wid = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (wid >= S * nh) return;
+  const int s = wid / nh, head = wid - s * nh;
+  const int q0 = cu_q[s];
+  if (cu_q[s + 1] - q0 != 1) return;
+  const int p = seq_lens[s] - 1;
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int first_split = lo / chunk, last_split = p / chunk;
+  if (first_split == last_split) return;  // written directly by the attention kernel
+  const size_t prow = ((size_t)decode_index[s] * nh + head) * nsplits;
+  float M = -INFINITY;
+  for (int sp = first_split; sp <= last_split; ++sp) M = fmaxf(M, part_ml[(prow + sp) * 2]);
+  float L = 0.0f;
+  for (int sp = first_split; sp <= last_split; ++sp) {
+    const float ms = part_ml[(prow + sp) * 2];
+    L += (ms == -INFINITY) ? 0.0f : part_ml[(prow + sp) * 2 + 1] * fast_exp2(ms - M);
+  }
+  const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+  for (int d = lane; d < hd; d += 32) {
+    float acc = 0.0f;
+    for (int sp = first_split; sp <= last_split; ++sp) {
+      const float ms = part_ml[(prow + sp) * 2];
+      if (ms != -INFINITY) acc += part_o[(prow + sp) * hd + d] * fast_exp2(ms - M);
+    }
+    out[((size_t)q0 * nh + head) * hd + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int HD_MAX>
+int launch_prefill(bf16* out, const bf16* q, int q_row_stride, const bf16* kc, const bf16* vc, const int* bt,
+                   int bt_stride, const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int hd, int ps,
+                   int num_pages, float scale_log2, int window, int max_q_len, int skip_single, cudaStream_t stream) {
+  const size_t smem = (size_t)(64 + 4 * TILE_N) * (hd + 8) * sizeof(bf16);
+  auto k = attn_prefill_kernel<HD_MAX>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const dim3 grid((max_q_len + 63) / 64, nh, S);
+  k<<<grid, NTHREADS, smem, stream>>>(out, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens, nh, nkv, hd, ps,
+                                      num_pages, scale_log2, window, skip_single);
+  return osb_last_error();
+}
+
+template <int HD_MAX, int STAGES>
+int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_stride, const bf16* kc,
+                  const bf16* vc, const int* bt, int bt_stride, const int* cu_q, const int* seq_lens,
+                  const int* decode_index, int S, int nh, int nkv, int hd, int ps, int num_pages, float scale_log2,
+                  int window, int chunk, int nsplits, cudaStream_t stream) {
+  const size_t smem = (size_t)(16 + STAGES * 2 * TILE_N) * (hd + 8) * sizeof(bf16);
+  auto k = attn_decode_kernel<HD_MAX, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int g = nh / nkv;
+  const dim3 grid(nsplits, nkv * ((g + 15) / 16), S);
+  k<<<grid, NTHREADS, smem, stream>>>(out, part_o, part_ml, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens,
+                                      decode_index, nh, nkv, hd, ps, num_pages, scale_log2, window, chunk, nsplits);
+  int rc = osb_last_error();
+  if (rc != 0 || nsplits == 1) return rc;
+  attn_decode_reduce_kernel<<<(S * nh + 3) / 4, 128, 0, stream>>>(out, part_o, part_ml, cu_q, seq_lens, decode_index,
+                                                                S, nh, hd, window, chunk, nsplits);
+  return osb_last_error();
+}
+}  // namespace
+
+// Scratch needed by the decode path: floats of part_o and of part_ml for n_decode requests.
+OSB_API void osb_attn_decode_scratch(int n_decode, int nh, int hd, int nsplits, long long* o_floats,
+                                     long long* ml_floats) {
+  *o_floats = (long long)n_decode * nh * nsplits * hd;
+  *ml_floats = (long long)n_decode * nh * nsplits * 2;
+}
+
+// out [T, nh*hd] bf16. Requests with one token run through the split-key decode kernel when
+// n_decode > 0 (decode_index[s] = index among them, part_o/part_ml sized by osb_attn_decode_scratch,
+// chunk a multiple of 64, nsplits = ceil(max_kv_len / chunk)); all others (and all, when n_decode == 0)
+// through the prefill kernel.
+OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
+                                const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
+                                const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
+                                float scale, int window, int max_q_len, int n_decode, int n_multi, float* part_o,
+                                float* part_ml, int chunk, int nsplits, cudaStream_t stream) {
+  if (S <= 0) return OSB_OK;
+  if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
+  if (n_decode > 0 && (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0)) return OSB_ERR_BAD_SHAPE;
+  if (n_decode > 0 && nsplits > 1 && (part_o == nullptr || part_ml == nullptr)) return OSB_ERR_BAD_SHAPE;
+  const float scale_log2 = scale * LOG2E;
+  bf16* o = (bf16*)out;
+  const bf16 *qq = (const bf16*)q, *kc = (const bf16*)k_cache, *vc = (const bf16*)v_cache;
+  int rc = OSB_OK;
+  if (n_multi > 0 || n_decode == 0) {
+    const int skip = n_decode > 0 ? 1 : 0;
+    if (hd <= 64)
+      rc = launch_prefill<64>(o, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, hd,
+                              page_size, num_pages, scale_log2, window, max_q_len, skip, stream);
+    else if (hd <= 128)
+      rc = launch_prefill<128>(o, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, hd,
+                               page_size, num_pages, scale_log2, window, max_q_len, skip, stream);
+    else
+      rc = launch_prefill<256>(o, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, hd,
+                               page_size, num_pages, scale_log2, window, max_q_len, skip, stream);
+    if (rc != 0) return rc;
+  }
+  if (n_decode > 0) {
+    if (hd <= 64)
+      rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                                decode_index, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk, nsplits,
+                                stream);
+    else if (hd <= 128)
+      rc = launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                                 decode_index, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 nsplits, stream);
+    else
+      rc = launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                                 decode_index, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 nsplits, stream);
+  }
+  return rc;
+}

@@ -59,6 +59,9 @@ class StepContext:
         self.q_lens: List[int] = []
         self.kv_lens: List[int] = []
         self.page_size = 0
+        self.decode_index: Optional[torch.Tensor] = None   # [S]: index among requests bringing one token, else -1
+        self.n_decode = self.n_multi = 0
+        self.scratch: Dict[str, torch.Tensor] = {}         # per-step scratch buffers shared by the layers
         self._model: Optional[DecoderModel] = None
         self._tables: Dict[int, Any] = {}
 
@@ -91,6 +94,7 @@ class ModelRunner:
         self.vocab_size = model.spec.vocab_size
         self.hidden_size = model.spec.hidden_size
         self.steps = 0
+        self._scratch: Dict[str, torch.Tensor] = {}
         model.attach_cache(cache.bindings(), cache.shared_state())
         self._has_rope_state = ROPE_STATE in cache.state.fields
 
@@ -179,6 +183,10 @@ class ModelRunner:
             ("pos_mode", pos_mode), ("logit_rows", np.asarray(logit_rows, dtype=np.int32)),
             ("override_rows", np.asarray(ov_rows, dtype=np.int32)),
         ]
+        ql = np.asarray(q_lens)
+        single = ql == 1
+        decode_index = np.where(single, np.cumsum(single) - 1, -1).astype(np.int32)
+        segs.append(("decode_index", decode_index))
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
             segs.append((f"sm{g}", sms[g]))
@@ -212,6 +220,10 @@ class ModelRunner:
         ctx.q_lens, ctx.kv_lens = q_lens, kv_lens
         ctx.max_q_len, ctx.max_kv_len = max(q_lens), max(kv_lens)
         ctx.page_size = cache.page_size
+        ctx.decode_index = seg("decode_index")
+        ctx.n_decode = int(single.sum())
+        ctx.n_multi = S - ctx.n_decode
+        ctx.scratch = self._scratch
         ctx.h2d_bytes = total * 4
         return ctx
 

@@ -274,20 +274,50 @@ class CudaKernels:
                         block_table: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor, tok_seq: torch.Tensor,
                         nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
                         max_q_len: int, max_kv_len: int, out_dtype: torch.dtype,
-                        exact: bool = False) -> torch.Tensor:
-        """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache."""
+                        decode_index: Optional[torch.Tensor] = None, n_decode: int = 0, n_multi: int = 0,
+                        exact: bool = False, scratch: Optional[dict] = None) -> torch.Tensor:
+        """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache.
+
+        bfloat16 operands run on the tensor cores (one kernel for requests bringing several tokens,
+        a split-key kernel for requests bringing one: ``decode_index`` [S] numbers those, -1 for the
+        others). float32 operands, ``exact=True`` and head sizes that are no multiple of 16 run
+        through the kernel whose sums have a fixed order.
+        """
         _cuda_contig("qkv", qkv)
         _cuda_contig("k_cache", k_cache)
         _cuda_contig("v_cache", v_cache)
         for n, t in (("block_table", block_table), ("cu_q", cu_q), ("seq_lens", seq_lens), ("tok_seq", tok_seq)):
             _cuda_contig(n, t, torch.int32)
         T = qkv.shape[0]
+        S = seq_lens.shape[0]
         _check(qkv.shape[1] >= nh * hd, "paged_attention: q columns missing")
         _check(k_cache.dim() == 4 and k_cache.shape[1] == nkv and k_cache.shape[3] == hd
                and v_cache.shape == k_cache.shape, "paged_attention: caches [pages, nkv, page_size, hd]")
-        _check(block_table.dim() == 2 and block_table.shape[0] == seq_lens.shape[0], "paged_attention: block_table [S,*]")
+        _check(block_table.dim() == 2 and block_table.shape[0] == S, "paged_attention: block_table [S,*]")
+        _check(nh % nkv == 0, "paged_attention: heads must be a multiple of kv heads")
         out = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
         win = int(window) if window else 0
+        fast = (not exact and qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+                and out_dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and decode_index is not None)
+        if fast:
+            _cuda_contig("decode_index", decode_index, torch.int32)
+            part_o = part_ml = None
+            chunk, nsplits = 64, 1
+            if n_decode > 0:
+                chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len)
+                if nsplits > 1:
+                    n_o, n_ml = n_decode * nh * nsplits * hd, n_decode * nh * nsplits * 2
+                    part_o = self._scratch(scratch, "attn_part_o", n_o, qkv.device)
+                    part_ml = self._scratch(scratch, "attn_part_ml", n_ml, qkv.device)
+            rc = self.lib.osb_paged_attn_bf16(
+                _p(out), _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
+                _p(cu_q), _p(seq_lens), _p(decode_index), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
+                ctypes.c_float(scale), win, max_q_len, n_decode, n_multi, _p(part_o), _p(part_ml), chunk, nsplits,
+                self._stream())
+            self._ok(rc, "paged_attn_bf16")
+            self.launches += (1 if n_multi > 0 or n_decode == 0 else 0) + (1 if n_decode > 0 and nsplits > 1 else 0) \
+                + (1 if n_decode > 0 else 0) - 1
+            return out
         rc = self.lib.osb_paged_attn_generic(
             _p(out), _dt(out), _p(qkv), _dt(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _dt(k_cache),
             _p(block_table), block_table.shape[1], _p(cu_q), _p(seq_lens), _p(tok_seq), T, nh, nkv, hd,
@@ -295,6 +325,26 @@ class CudaKernels:
             self._stream())
         self._ok(rc, "paged_attn_generic")
         return out
+
+    @staticmethod
+    def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 444):
+        """(chunk, nsplits) of the split-key decode kernel: enough CTAs to fill the GPU, splits ending
+        at multiples of ``chunk`` keys (a multiple of 64)."""
+        per_split = max(1, n_decode * nkv * ((group + 15) // 16))
+        want = max(1, -(-target_ctas // per_split))
+        chunk = -(-max(1, max_kv_len) // want)
+        chunk = max(128, -(-chunk // 64) * 64)
+        return chunk, max(1, -(-max_kv_len // chunk))
+
+    @staticmethod
+    def _scratch(pool: Optional[dict], name: str, numel: int, device) -> torch.Tensor:
+        if pool is None:
+            return torch.empty(numel, dtype=torch.float32, device=device)
+        t = pool.get(name)
+        if t is None or t.numel() < numel:
+            t = torch.empty(numel, dtype=torch.float32, device=device)
+            pool[name] = t
+        return t
 
     # ------------------------------------------------------------------ activation
     def silu_mul(self, gu: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

@@ -53,7 +53,8 @@ class GQAAttention(Mixer):
                         self.nh, self.nkv, self.hd, tables.rot_dim if tables else 0)
         a = k.paged_attention(qkv, binding.k_cache, binding.v_cache, ctx.block_tables[g], ctx.cu_q, ctx.seq_lens,
                               ctx.tok_seq, self.nh, self.nkv, self.hd, self.scale, self.window,
-                              ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype)
+                              ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype, decode_index=ctx.decode_index,
+                              n_decode=ctx.n_decode, n_multi=ctx.n_multi, scratch=ctx.scratch)
         return self.out(a, ctx.act_dtype)
 
 

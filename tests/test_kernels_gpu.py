@@ -193,12 +193,17 @@ def _paged_case(q_lens, kv_lens, nh, nkv, hd, ps, dtype, seed=0, pages_extra=3):
     return qkv, kc, vc, bt, cu_q, seq_lens, tok_seq
 
 
-def _run_attn(case, nh, nkv, hd, window, dtype):
+def _run_attn(case, nh, nkv, hd, window, dtype, exact=False):
     qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = case
     scale = hd ** -0.5
     mq, mk = int((cu_q[1:] - cu_q[:-1]).max()), int(seq_lens.max())
+    ql = (cu_q[1:] - cu_q[:-1])
+    single = ql == 1
+    decode_index = torch.where(single, torch.cumsum(single.int(), 0) - 1, torch.full_like(ql, -1)).to(torch.int32)
     got = K().paged_attention(qkv.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu_q.to(DEV), seq_lens.to(DEV),
-                              tok_seq.to(DEV), nh, nkv, hd, scale, window, mq, mk, dtype)
+                              tok_seq.to(DEV), nh, nkv, hd, scale, window, mq, mk, dtype,
+                              decode_index=decode_index.to(DEV), n_decode=int(single.sum()),
+                              n_multi=int((~single).sum()), exact=exact)
     want = REF.paged_attention(qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, scale, window, mq, mk,
                                torch.float32)
     K().check_device_errors()
@@ -213,6 +218,47 @@ def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, ps, window):
     q_lens, kv_lens = [33, 1, 2, 16, 1], [33, 300, 47, 64, 1]
     got, want = _run_attn(_paged_case(q_lens, kv_lens, nh, nkv, hd, ps, dtype), nh, nkv, hd, window, dtype)
     assert torch.allclose(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(12, 2, 128, 16), (28, 4, 128, 16), (6, 3, 48, 8), (4, 4, 64, 64), (40, 2, 32, 16),
+                                          (8, 1, 256, 16)])
+@pytest.mark.parametrize("window", [None, 300])
+def test_decode_attention_long_contexts_split_keys(nh, nkv, hd, ps, window):
+    """Single-token requests with long and uneven contexts: the keys are split over CTAs and merged."""
+    kv_lens = [2048, 1, 777, 64, 65, 3000, 128, 129]
+    case = _paged_case([1] * len(kv_lens), kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=3)
+    got, want = _run_attn(case, nh, nkv, hd, window, torch.bfloat16)
+    assert torch.allclose(got, want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("window", [None, 100])
+def test_decode_attention_finds_one_key_that_matters(window):
+    """As below, for the split-key decode kernel: one key dominates, placed at tile, split and window edges."""
+    nh, nkv, hd, ps, dtype = 12, 2, 128, 16, torch.bfloat16
+    kv_len = 1500
+    p = kv_len - 1
+    spots = [0, 63, 64, 127, 128, 255, 256, 1023, 1024, p - 1, p]
+    if window:
+        spots = [p - window, p - window + 1, p - window + 2, 1407, 1408, p]
+    for j in spots:
+        case = list(_paged_case([1, 1], [kv_len, 900], nh, nkv, hd, ps, dtype, seed=j + 1))
+        qkv, kc, vc, bt = case[0], case[1], case[2], case[3]
+        g = nh // nkv
+        for kvh in range(nkv):
+            qh = qkv[0, kvh * g * hd:(kvh * g + 1) * hd].float()
+            for h in range(kvh * g, (kvh + 1) * g):
+                qkv[0, h * hd:(h + 1) * hd] = qh.to(dtype)
+            kvec = qh / qh.norm() ** 2 * 30.0 * math.sqrt(hd)
+            page = int(bt[0, j // ps])
+            kc[page, kvh, j % ps] = kvec.to(dtype)
+            vc[page, kvh, j % ps] = 7.0
+        got, want = _run_attn(tuple(case), nh, nkv, hd, window, dtype)
+        assert torch.allclose(got, want, **tol(dtype)), f"key {j}"
+        visible = not window or j > p - window
+        if visible:
+            assert got[0].mean() > 6.5, f"key {j} should dominate"
+        else:
+            assert got[0].abs().mean() < 2.0, f"key {j} must be invisible"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
