@@ -223,8 +223,9 @@ class CacheManager:
             t[rc.slot].zero_()
 
     # ------------------------------------------------------------------ per-step tables
-    def block_table(self, group: int, request_ids: Sequence[str]) -> np.ndarray:
+    def block_table(self, group: int, request_ids: Sequence[str], round_to: int = 1) -> np.ndarray:
         width = max(1, max((len(self.requests[r].tables[group]) for r in request_ids), default=1))
+        width = -(-width // round_to) * round_to
         bt = np.full((len(request_ids), width), -1, dtype=np.int32)
         for i, r in enumerate(request_ids):
             t = self.requests[r].tables[group]

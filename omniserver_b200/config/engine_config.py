@@ -35,6 +35,7 @@ class EngineConfig:
     max_requests: int = 64
     device: str = "cuda:0"
     check_device_errors: bool = True
+    cuda_graphs: bool = True          # replay pure decode steps from CUDA graphs
 
     @property
     def torch_dtype(self) -> torch.dtype:

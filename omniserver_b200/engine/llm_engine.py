@@ -59,7 +59,8 @@ def build_runner(model_dir: Optional[str] = None, engine_config: Optional[Engine
     num_pages = (ec.max_cache_tokens + ec.page_size - 1) // ec.page_size
     cache = CacheManager(model.entry_needs(), model.shared_state_needs(), ec.page_size, num_pages, ec.max_requests,
                          dtype, device, allocate=allocate)
-    runner = ModelRunner(model, cache, dtype, device, check_device_errors=ec.check_device_errors)
+    runner = ModelRunner(model, cache, dtype, device, check_device_errors=ec.check_device_errors,
+                         use_graphs=ec.cuda_graphs)
     runner.model_config = cfg
     return runner
 

@@ -62,6 +62,7 @@ class StepContext:
         self.decode_index: Optional[torch.Tensor] = None   # [S]: index among requests bringing one token, else -1
         self.n_decode = self.n_multi = 0
         self.scratch: Dict[str, torch.Tensor] = {}         # per-step scratch buffers shared by the layers
+        self.advance_state = True                          # False: a dry run that must not move cursors
         self._model: Optional[DecoderModel] = None
         self._tables: Dict[int, Any] = {}
 
@@ -85,7 +86,7 @@ class ModelRunner:
     """Owns the model, its cache and the step function."""
 
     def __init__(self, model: DecoderModel, cache: CacheManager, act_dtype: torch.dtype, device,
-                 check_device_errors: bool = True):
+                 check_device_errors: bool = True, use_graphs: bool = False):
         self.model = model
         self.cache = cache
         self.act_dtype = act_dtype
@@ -95,6 +96,11 @@ class ModelRunner:
         self.hidden_size = model.spec.hidden_size
         self.steps = 0
         self._scratch: Dict[str, torch.Tensor] = {}
+        #: replay pure decode steps from CUDA graphs (one per batch size and block-table width)
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.graph_max_batch = 256
+        self.graph_bt_round = 32          # block-table width is rounded up to this many pages
+        self._graphs: Dict[Any, Dict[str, Any]] = {}
         model.attach_cache(cache.bindings(), cache.shared_state())
         self._has_rope_state = ROPE_STATE in cache.state.fields
 
@@ -113,7 +119,8 @@ class ModelRunner:
             self.cache.state.write(ROPE_STATE, self.cache.requests[request_id].slot, [0, int(rope_delta)])
 
     # ------------------------------------------------------------------ the step
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _plan(self, entries: Sequence[StepEntry], bt_round: int = 1) -> Dict[str, Any]:
+        """Validates the entries, takes their pages and lays out the step's host-side metadata."""
         cache = self.cache
         S = len(entries)
         if S == 0:
@@ -173,33 +180,35 @@ class ModelRunner:
                 ov_vals.append(e.embed_values)
         slots = np.asarray([cache.requests[r].slot for r in rids], dtype=np.int32)
         G = len(cache.groups)
-        bts = [cache.block_table(g, rids) for g in range(G)]
+        bts = [cache.block_table(g, rids, bt_round) for g in range(G)]
         sms = [cache.slot_map(g, rids, q_lens) for g in range(G)]
-
-        # one staging buffer, one host-to-device copy
+        ql = np.asarray(q_lens)
+        single = ql == 1
+        decode_index = np.where(single, np.cumsum(single) - 1, -1).astype(np.int32)
         segs: List[Tuple[str, np.ndarray]] = [
             ("token_ids", token_ids), ("cu_q", cu_q), ("seq_lens", np.asarray(kv_lens, dtype=np.int32)),
             ("tok_seq", tok_seq), ("state_slot", slots), ("positions", positions.reshape(-1)),
             ("pos_mode", pos_mode), ("logit_rows", np.asarray(logit_rows, dtype=np.int32)),
-            ("override_rows", np.asarray(ov_rows, dtype=np.int32)),
+            ("override_rows", np.asarray(ov_rows, dtype=np.int32)), ("decode_index", decode_index),
         ]
-        ql = np.asarray(q_lens)
-        single = ql == 1
-        decode_index = np.where(single, np.cumsum(single) - 1, -1).astype(np.int32)
-        segs.append(("decode_index", decode_index))
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
             segs.append((f"sm{g}", sms[g]))
+        return dict(S=S, T=T, segs=segs, q_lens=q_lens, kv_lens=kv_lens, bt_widths=[b.shape[1] for b in bts],
+                    n_logit_rows=len(logit_rows), ov_vals=ov_vals, n_decode=int(single.sum()),
+                    explicit_positions=bool((pos_mode == 0).any()))
+
+    @staticmethod
+    def _layout(segs: List[Tuple[str, np.ndarray]]) -> Tuple[Dict[str, Tuple[int, int]], int]:
         offs, total = {}, 0
         for name, arr in segs:
             offs[name] = (total, arr.size)
             total += _align4(arr.size)
-        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
-        hv = host.numpy()
-        for name, arr in segs:
-            o, n = offs[name]
-            hv[o:o + n] = arr
-        dev = host.to(self.device, non_blocking=True)
+        return offs, max(total, 4)
+
+    def _context(self, plan: Dict[str, Any], dev: torch.Tensor, offs: Dict[str, Tuple[int, int]]) -> StepContext:
+        S, T = plan["S"], plan["T"]
+        G = len(self.cache.groups)
 
         def seg(name: str) -> torch.Tensor:
             o, n = offs[name]
@@ -207,23 +216,36 @@ class ModelRunner:
 
         ctx = StepContext()
         ctx.device, ctx.act_dtype = self.device, self.act_dtype
-        ctx.T, ctx.S, ctx.num_logit_rows = T, S, len(logit_rows)
+        ctx.T, ctx.S, ctx.num_logit_rows = T, S, plan["n_logit_rows"]
         ctx.token_ids, ctx.cu_q, ctx.seq_lens = seg("token_ids"), seg("cu_q"), seg("seq_lens")
         ctx.tok_seq, ctx.state_slot = seg("tok_seq"), seg("state_slot")
         ctx.positions = seg("positions").view(3, T)
         ctx.pos_mode, ctx.logit_rows = seg("pos_mode"), seg("logit_rows")
-        ctx.block_tables = [seg(f"bt{g}").view(S, bts[g].shape[1]) for g in range(G)]
+        ctx.block_tables = [seg(f"bt{g}").view(S, plan["bt_widths"][g]) for g in range(G)]
         ctx.slot_maps = [seg(f"sm{g}") for g in range(G)]
-        if ov_rows:
+        if plan["ov_vals"]:
             ctx.override_rows = seg("override_rows")
-            ctx.override_vals = torch.cat([v.to(self.device) for v in ov_vals], dim=0).contiguous()
-        ctx.q_lens, ctx.kv_lens = q_lens, kv_lens
-        ctx.max_q_len, ctx.max_kv_len = max(q_lens), max(kv_lens)
-        ctx.page_size = cache.page_size
+            ctx.override_vals = torch.cat([v.to(self.device) for v in plan["ov_vals"]], dim=0).contiguous()
+        ctx.q_lens, ctx.kv_lens = plan["q_lens"], plan["kv_lens"]
+        ctx.max_q_len, ctx.max_kv_len = max(plan["q_lens"]), max(plan["kv_lens"])
+        ctx.page_size = self.cache.page_size
         ctx.decode_index = seg("decode_index")
-        ctx.n_decode = int(single.sum())
+        ctx.n_decode = plan["n_decode"]
         ctx.n_multi = S - ctx.n_decode
         ctx.scratch = self._scratch
+        return ctx
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        plan = self._plan(entries)
+        offs, total = self._layout(plan["segs"])
+        # one staging buffer, one host-to-device copy
+        host = torch.empty(total, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        hv = host.numpy()
+        for name, arr in plan["segs"]:
+            o, n = offs[name]
+            hv[o:o + n] = arr
+        dev = host.to(self.device, non_blocking=True)
+        ctx = self._context(plan, dev, offs)
         ctx.h2d_bytes = total * 4
         return ctx
 
@@ -231,6 +253,8 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries as one batch; returns fp32 logits [wanted, vocab] in the order of the
         entries and of their ``want``. The requests' tokens are in the cache afterwards."""
+        if self.use_graphs and self._graphable(entries):
+            return self._graph_step(entries)
         ctx = self.build_context(entries)
         try:
             logits = self.model.forward(ctx)
@@ -239,9 +263,76 @@ class ModelRunner:
             for e in entries:
                 self.cache.requests[e.request_id].reserved = 0
             raise
+        self._after_step(entries)
+        return logits
+
+    def _after_step(self, entries: Sequence[StepEntry]) -> None:
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
         if self.check_device_errors:
             ops.kernels().check_device_errors()
-        return logits
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    def _graphable(self, entries: Sequence[StepEntry]) -> bool:
+        """Pure decode steps (one token and one wanted row per request, positions from the state
+        slot, no given embeddings) have a fixed launch sequence for a given batch size."""
+        if self.device.type != "cuda" or len(entries) > self.graph_max_batch:
+            return False
+        for e in entries:
+            if len(e.tokens) != 1 or e.positions is not None or e.embed_rows is not None or list(e.want) != [0]:
+                return False
+        return True
+
+    def _graph_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A decode step replayed from a CUDA graph: the launch-bound inner loop of generation.
+
+        One graph per (batch size, block-table width bucket). The step's metadata goes into a
+        buffer at a fixed address (one host-to-device copy); everything the kernels need that
+        changes from step to step is read from that buffer or from the state slots.
+        """
+        k = ops.kernels()
+        round_to = self.graph_bt_round
+        plan = self._plan(entries, bt_round=round_to)
+        key = (plan["S"], tuple(plan["bt_widths"]))
+        slot = self._graphs.get(key)
+        if slot is None:
+            offs, total = self._layout(plan["segs"])
+            with torch.inference_mode(False):
+                host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+                dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+            slot = {"offs": offs, "host": host, "dev": dev, "graph": None, "logits": None, "launches": 0,
+                    "copied": torch.cuda.Event()}
+            self._graphs[key] = slot
+        else:
+            slot["copied"].synchronize()      # the previous copy out of the pinned buffer has finished
+        hv = slot["host"].numpy()
+        for name, arr in plan["segs"]:
+            o, n = slot["offs"][name]
+            hv[o:o + n] = arr
+        slot["dev"].copy_(slot["host"], non_blocking=True)
+        slot["copied"].record()
+        try:
+            if slot["graph"] is None:
+                ctx = self._context(plan, slot["dev"], slot["offs"])
+                # the kernels' grids must not depend on this step's lengths: size them for the bucket
+                ctx.max_kv_len = max(plan["bt_widths"]) * self.cache.page_size
+                ctx.advance_state = False
+                self.model.forward(ctx)                      # warm-up; same cache writes as the real run
+                torch.cuda.synchronize()
+                ctx.advance_state = True
+                g = torch.cuda.CUDAGraph()
+                l0 = k.launches
+                with torch.cuda.graph(g):
+                    slot["logits"] = self.model.forward(ctx)
+                slot["launches"] = k.launches - l0
+                slot["graph"] = g
+                k.launches = l0
+            slot["graph"].replay()
+            k.launches += slot["launches"]
+        except Exception:
+            for e in entries:
+                self.cache.requests[e.request_id].reserved = 0
+            raise
+        self._after_step(entries)
+        return slot["logits"].clone()

@@ -107,8 +107,9 @@ class DecoderModel:
         residual = None
         for e, binding in zip(self.spec.schedule, self.bindings):
             x, residual = self.blocks[e.layer].forward(ctx, x, residual, binding)
-        for pos in self.positions.values():
-            pos.finish_step(ctx, self.shared_state)
+        if getattr(ctx, "advance_state", True):
+            for pos in self.positions.values():
+                pos.finish_step(ctx, self.shared_state)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         h = self.final_norm.forward_add_rows(x, residual, ctx.logit_rows, ctx.act_dtype)

@@ -199,7 +199,7 @@ class CudaKernels:
         if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and hasattr(self.lib, "osb_gemm_skinny_bf16"):
             y = torch.empty((M, N), dtype=out_dtype, device=x.device)
             rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias),
-                                               _dt(bias) if bias is not None else 0, M, N, K, self._stream())
+                                               _dt(bias) if bias is not None else 0, M, N, K, 0, self._stream())
             if rc != 10003:
                 self._ok(rc, "gemm_skinny_bf16")
                 return y
@@ -217,6 +217,26 @@ class CudaKernels:
                 y += bias.float()
             return y
         return self.gemm_simt(x, w, bias, out_dtype)
+
+    def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].
+
+        For few bf16 rows one kernel streams W once and applies the activation in its epilogue;
+        otherwise the product and the activation are two kernels.
+        """
+        _cuda_contig("x", x)
+        _cuda_contig("w", w)
+        _check(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and w.shape[0] % 2 == 0,
+               "gate_up_silu: x [M,K], w [2I,K]")
+        M, K = x.shape
+        N = w.shape[0]
+        if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= self.SKINNY_MAX_ROWS and K % 8 == 0
+                and out_dtype in (torch.bfloat16, torch.float32)):
+            y = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
+            rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(None), 0, M, N, K, 1, self._stream())
+            self._ok(rc, "gemm_skinny_bf16(swiglu)")
+            return y
+        return self.silu_mul(self.linear(x, w, None, x.dtype if x.dtype == w.dtype else torch.float32), out_dtype)
 
     # ------------------------------------------------------------------ rotary + cache write
     def rope_tables(self, positions: torch.Tensor, pos_mode: torch.Tensor, tok_seq: torch.Tensor,

@@ -28,8 +28,7 @@ class SwiGLU(FeedForward):
         self.down.bind(tensors)
 
     def forward(self, ctx: Any, x: torch.Tensor) -> torch.Tensor:
-        gu = self.gate_up(x, ctx.act_dtype)
-        m = ops.kernels().silu_mul(gu, ctx.act_dtype)
+        m = ops.kernels().gate_up_silu(x, self.gate_up.weight, ctx.act_dtype)
         return self.down(m, ctx.act_dtype)
 
 

@@ -53,6 +53,10 @@ class PlainKernels:
 
     gemm_simt = linear
 
+    def gate_up_silu(self, x, w, out_dtype):
+        mid = x.dtype if x.dtype == w.dtype else torch.float32
+        return self.silu_mul(self.linear(x, w, None, mid), out_dtype)
+
     # -- rotary
     def rope_tables(self, positions, pos_mode, tok_seq, cu_q, state_slot, cursor, inv_freq, axis_of):
         T = tok_seq.shape[0]

@@ -109,6 +109,31 @@ def test_linear_bf16_and_f32(dtype, M, N, K_):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,I,K_", [(1, 200, 96), (8, 8960, 1536), (33, 176, 80), (64, 128, 64), (100, 200, 96)])
+def test_gate_up_silu(dtype, M, I, K_):
+    x, w = rnd(M, K_, dtype=dtype), rnd(2 * I, K_, dtype=dtype, seed=1, scale=0.1)
+    got = K().gate_up_silu(x.to(DEV), w.to(DEV), dtype)
+    want = REF.gate_up_silu(x, w, torch.float32)
+    assert got.shape == (M, I)
+    assert torch.allclose(got.float().cpu(), want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=4e-3)))
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 1536, 1536), (8, 2048, 1536), (8, 1536, 8960), (64, 17920, 1536), (5, 151936, 1536),
+                                    (17, 40, 72), (64, 1000, 200)])
+def test_skinny_gemm_bf16(M, N, K_):
+    """The weight-streaming product at the decode step's shapes and at ragged ones (N not a multiple
+    of 16, K not a multiple of 64)."""
+    x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(N, K_, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = rnd(N, dtype=torch.bfloat16, seed=2)
+    for bias in (None, b, b.float()):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            got = K().linear(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out_dtype)
+            want = REF.linear(x.double(), w.double(), bias.double() if bias is not None else None, torch.float64)
+            t = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else tol(torch.bfloat16)
+            assert torch.allclose(got.double().cpu(), want, **t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(dtype):
     gu = rnd(5, 2 * 200, dtype=dtype, scale=3.0)
     got = K().silu_mul(gu.to(DEV), dtype)
