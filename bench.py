@@ -148,7 +148,7 @@ def run_ours(args):
     ctx_total = CONTEXT + NEW_TOKENS
     pool_tokens = max_batch * (-(-ctx_total // 64) * 64) + 4096
     ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=pool_tokens, max_requests=max_batch + 2,
-                      check_device_errors=False)
+                      check_device_errors=False, cuda_graphs=not args.no_graphs)
     t0 = time.time()
     runner = build_runner(config=cfg, seed=SEED, engine_config=ec, random_on_device=True)
     torch.cuda.synchronize()
@@ -166,19 +166,21 @@ def run_ours(args):
         return lg
 
     with torch.inference_mode():
-        for i in range(3):
+        for i in range(0 if args.only == "decode" else 3):
             prefill_once(f"pw{i}")
             runner.end_request(f"pw{i}")
         torch.cuda.synchronize()
         times = []
-        for i in range(5):
+        for i in range(1 if args.only == "decode" else 5):
             toks = new_prompt(CONTEXT)
+            torch.cuda.nvtx.range_push("timed_prefill")
             runner.start_request(f"p{i}")
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             runner.step([StepEntry(f"p{i}", toks, want=[CONTEXT - 1])])
             e1.record()
             torch.cuda.synchronize()
+            torch.cuda.nvtx.range_pop()
             times.append(e0.elapsed_time(e1))
             runner.end_request(f"p{i}")
         pre_ms = statistics.median(times)
@@ -207,12 +209,14 @@ def run_ours(args):
             l0 = K.launches
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            torch.cuda.nvtx.range_push("timed_decode")
             e0.record()
             for _ in range(steps):
                 lg = runner.step([StepEntry(r, [t], want=[0]) for r, t in zip(rids, last)])
                 last = K.sample(lg, None, None).tolist()
             e1.record()
             torch.cuda.synchronize()
+            torch.cuda.nvtx.range_pop()
             ms = e0.elapsed_time(e1) / steps
             launches = K.launches - l0
             ck = clocks.stop() if clocks else None
@@ -229,17 +233,19 @@ def run_ours(args):
                 "frac": round(achieved / hbm_peak, 4), "bytes_per_step": int(step_bytes), "of": peak_src}
 
     points = {}
-    if not args.no_points:
+    if not args.no_points and args.only == "all":
         for B in (1, 64):
             pms, _, _, _ = decode_run(B, max(8, args.steps // 2), max(3, args.warmup // 2))
             points[f"decode_b{B}"] = round(B / (pms / 1e3), 1)
 
     # ------------------------------------------------------------------ end to end through LLMEngine
+    e2e = None
     with torch.inference_mode():
+        # all prompts enter in one step, so that every request decodes in every timed step
         eng = LLMEngine(runner, SchedulerConfig(max_running=args.batch, max_prefill_per_step=args.batch,
-                                                max_prefill_tokens=CONTEXT, max_seq_len=4096), seed=SEED)
+                                                max_prefill_tokens=CONTEXT * args.batch, max_seq_len=4096), seed=SEED)
         n_new = args.warmup + args.steps + 1
-        for i in range(args.batch):
+        for i in range(args.batch if args.only == "all" else 0):
             eng.add_request(Request(prompt=new_prompt(CONTEXT),
                                     sampling=SamplingParams(max_new_tokens=n_new, ignore_eos=True)))
         while any(s.num_output_tokens < 1 + args.warmup for s in eng.sequences()):
@@ -251,7 +257,7 @@ def run_ours(args):
             eng.step()
             n_steps += 1
         torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t1
+        e2e_s = max(time.perf_counter() - t1, 1e-9)
     e2e_tokens = n_steps * args.batch
     # per step: token ids, cu_q, seq_lens, tok_seq, slots, positions(3), pos_mode, logit rows, block table, slot map
     bt_w = -(-(CONTEXT + NEW_TOKENS) // 16)
@@ -294,6 +300,9 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host")
+    ap.add_argument("--only", default="all", choices=["all", "decode"],
+                    help="'decode': skip the prefill repeats, the points and the end-to-end run (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -128,7 +128,8 @@ class PlainKernels:
     # -- activation
     def silu_mul(self, gu, out_dtype):
         n = gu.shape[1] // 2
-        g, u = gu[:, :n].float(), gu[:, n:].float()
+        acc = torch.float64 if gu.dtype == torch.float64 else torch.float32
+        g, u = gu[:, :n].to(acc), gu[:, n:].to(acc)
         return ((g * torch.sigmoid(g)) * u).to(out_dtype)
 
     # -- sampling

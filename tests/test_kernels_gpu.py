@@ -113,9 +113,12 @@ def test_linear_bf16_and_f32(dtype, M, N, K_):
 def test_gate_up_silu(dtype, M, I, K_):
     x, w = rnd(M, K_, dtype=dtype), rnd(2 * I, K_, dtype=dtype, seed=1, scale=0.1)
     got = K().gate_up_silu(x.to(DEV), w.to(DEV), dtype)
-    want = REF.gate_up_silu(x, w, torch.float32)
+    if dtype == torch.float32:
+        want = REF.silu_mul(REF.linear(x.double(), w.double(), None, torch.float64), torch.float64)
+    else:   # the product is rounded to bf16 before the activation, as in the two-kernel path
+        want = REF.gate_up_silu(x, w, torch.float32).double()
     assert got.shape == (M, I)
-    assert torch.allclose(got.float().cpu(), want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=4e-3)))
+    assert torch.allclose(got.double().cpu(), want, **(dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=4e-3)))
 
 
 @pytest.mark.parametrize("M,N,K_", [(1, 1536, 1536), (8, 2048, 1536), (8, 1536, 8960), (64, 17920, 1536), (5, 151936, 1536),
