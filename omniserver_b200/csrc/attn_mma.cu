@@ -234,9 +234,10 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
-    const int* __restrict__ decode_index, int nh, int nkv, int hd, int ps, int num_pages, float scale_log2,
-    int window, int chunk, int nsplits) {
+    const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int hd, int ps, int num_pages,
+    float scale_log2, int window, int chunk, int nsplits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int s_last;
   const int stride = hd + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [16][stride]; later the warps' (max, sum)
   bf16* kvs = qs + 16 * stride;                  // STAGES x (K, V) x [TILE_N][stride]; later the warps' outputs
@@ -438,38 +439,45 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
       }
     }
   }
-}
+  if (direct) return;
 
-// Merges the splits of every decode row in split order. One warp per (request, head).
-__global__ void __launch_bounds__(128) attn_decode_reduce_kernel(
-    bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-    const int* __restrict__ cu_q, const int* __restrict__ seq_lens, const int* __restrict__ decode_index, int S,
-    int nh, int hd, int window, int chunk, int nsplits) {
-  const int wid = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (wid >= S * nh) return;
-  const int s = wid / nh, head = wid - s * nh;
-  const int q0 = cu_q[s];
-  if (cu_q[s + 1] - q0 != 1) return;
-  const int p = seq_lens[s] - 1;
-  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-  const int first_split = lo / chunk, last_split = p / chunk;
-  if (first_split == last_split) return;  // written directly by the attention kernel
-  const size_t prow = ((size_t)decode_index[s] * nh + head) * nsplits;
-  float M = -INFINITY;
-  for (int sp = first_split; sp <= last_split; ++sp) M = fmaxf(M, part_ml[(prow + sp) * 2]);
-  float L = 0.0f;
-  for (int sp = first_split; sp <= last_split; ++sp) {
-    const float ms = part_ml[(prow + sp) * 2];
-    L += (ms == -INFINITY) ? 0.0f : part_ml[(prow + sp) * 2 + 1] * fast_exp2(ms - M);
+  // The CTA that finishes last among this (request, kv head) group's splits merges them, in split
+  // order, so the result does not depend on which CTA that is. The counter returns to zero.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* cnt = counters + (size_t)drow * gridDim.y + blockIdx.y;
+    const int prev = atomicAdd(cnt, 1);
+    s_last = (prev == last_split - first_split);
+    if (s_last) *cnt = 0;
   }
-  const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-  for (int d = lane; d < hd; d += 32) {
-    float acc = 0.0f;
-    for (int sp = first_split; sp <= last_split; ++sp) {
-      const float ms = part_ml[(prow + sp) * 2];
-      if (ms != -INFINITY) acc += part_o[(prow + sp) * hd + d] * fast_exp2(ms - M);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int nv = last_split - first_split + 1;
+  float* sml = reinterpret_cast<float*>(kvs);  // [rows][nv][2]
+  for (int idx = tid; idx < rows * nv; idx += NTHREADS) {
+    const int r = idx / nv, sp = idx - r * nv;
+    const size_t prow = ((size_t)drow * nh + head0 + r) * nsplits + first_split + sp;
+    sml[idx * 2] = __ldcg(part_ml + prow * 2);
+    sml[idx * 2 + 1] = __ldcg(part_ml + prow * 2 + 1);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * hd; idx += NTHREADS) {
+    const int r = idx / hd, d = idx - r * hd;
+    const float* ml = sml + (size_t)r * nv * 2;
+    float M = -INFINITY;
+    for (int sp = 0; sp < nv; ++sp) M = fmaxf(M, ml[sp * 2]);
+    const float* po = part_o + (((size_t)drow * nh + head0 + r) * nsplits + first_split) * hd + d;
+    float L = 0.0f, acc = 0.0f;
+#pragma unroll 4
+    for (int sp = 0; sp < nv; ++sp) {
+      const float ms = ml[sp * 2];
+      const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
+      L += ml[sp * 2 + 1] * f;
+      acc += __ldcg(po + (size_t)sp * hd) * f;
     }
-    out[((size_t)q0 * nh + head) * hd + d] = __float2bfloat16_rn(acc * inv);
+    out[((size_t)q0 * nh + head0 + r) * hd + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
   }
 }
 
@@ -490,8 +498,8 @@ int launch_prefill(bf16* out, const bf16* q, int q_row_stride, const bf16* kc, c
 template <int HD_MAX, int STAGES>
 int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_stride, const bf16* kc,
                   const bf16* vc, const int* bt, int bt_stride, const int* cu_q, const int* seq_lens,
-                  const int* decode_index, int S, int nh, int nkv, int hd, int ps, int num_pages, float scale_log2,
-                  int window, int chunk, int nsplits, cudaStream_t stream) {
+                  const int* decode_index, int* counters, int S, int nh, int nkv, int hd, int ps, int num_pages,
+                  float scale_log2, int window, int chunk, int nsplits, cudaStream_t stream) {
   const size_t smem = (size_t)(16 + STAGES * 2 * TILE_N) * (hd + 8) * sizeof(bf16);
   auto k = attn_decode_kernel<HD_MAX, STAGES>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -499,35 +507,38 @@ int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q
   const int g = nh / nkv;
   const dim3 grid(nsplits, nkv * ((g + 15) / 16), S);
   k<<<grid, NTHREADS, smem, stream>>>(out, part_o, part_ml, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens,
-                                      decode_index, nh, nkv, hd, ps, num_pages, scale_log2, window, chunk, nsplits);
-  int rc = osb_last_error();
-  if (rc != 0 || nsplits == 1) return rc;
-  attn_decode_reduce_kernel<<<(S * nh + 3) / 4, 128, 0, stream>>>(out, part_o, part_ml, cu_q, seq_lens, decode_index,
-                                                                S, nh, hd, window, chunk, nsplits);
+                                      decode_index, counters, nh, nkv, hd, ps, num_pages, scale_log2, window, chunk,
+                                      nsplits);
   return osb_last_error();
 }
 }  // namespace
 
 // Scratch needed by the decode path: floats of part_o and of part_ml for n_decode requests.
-OSB_API void osb_attn_decode_scratch(int n_decode, int nh, int hd, int nsplits, long long* o_floats,
-                                     long long* ml_floats) {
+OSB_API void osb_attn_decode_scratch(int n_decode, int nh, int nkv, int hd, int nsplits, long long* o_floats,
+                                     long long* ml_floats, long long* counter_ints) {
   *o_floats = (long long)n_decode * nh * nsplits * hd;
   *ml_floats = (long long)n_decode * nh * nsplits * 2;
+  *counter_ints = (long long)n_decode * nkv * ((nh / nkv + 15) / 16);
 }
 
+constexpr int MAX_SPLITS = 128;  // the merging CTA keeps (max, sum) of 16 rows x splits in shared memory
+
 // out [T, nh*hd] bf16. Requests with one token run through the split-key decode kernel when
-// n_decode > 0 (decode_index[s] = index among them, part_o/part_ml sized by osb_attn_decode_scratch,
-// chunk a multiple of 64, nsplits = ceil(max_kv_len / chunk)); all others (and all, when n_decode == 0)
-// through the prefill kernel.
+// n_decode > 0 (decode_index[s] = index among them; part_o/part_ml/counters sized by
+// osb_attn_decode_scratch, counters all zero before the first use (the kernel leaves them zero);
+// chunk a multiple of 64, nsplits = ceil(max_kv_len / chunk) <= 128); all others (and all, when
+// n_decode == 0) through the prefill kernel.
 OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
                                 const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
                                 float scale, int window, int max_q_len, int n_decode, int n_multi, float* part_o,
-                                float* part_ml, int chunk, int nsplits, cudaStream_t stream) {
+                                float* part_ml, int* counters, int chunk, int nsplits, cudaStream_t stream) {
   if (S <= 0) return OSB_OK;
   if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
-  if (n_decode > 0 && (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0)) return OSB_ERR_BAD_SHAPE;
-  if (n_decode > 0 && nsplits > 1 && (part_o == nullptr || part_ml == nullptr)) return OSB_ERR_BAD_SHAPE;
+  if (n_decode > 0 && (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0 || nsplits > MAX_SPLITS))
+    return OSB_ERR_BAD_SHAPE;
+  if (n_decode > 0 && nsplits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr))
+    return OSB_ERR_BAD_SHAPE;
   const float scale_log2 = scale * LOG2E;
   bf16* o = (bf16*)out;
   const bf16 *qq = (const bf16*)q, *kc = (const bf16*)k_cache, *vc = (const bf16*)v_cache;
@@ -548,15 +559,15 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
   if (n_decode > 0) {
     if (hd <= 64)
       rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                decode_index, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk, nsplits,
-                                stream);
+                                decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                nsplits, stream);
     else if (hd <= 128)
       rc = launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                 decode_index, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
                                  nsplits, stream);
     else
       rc = launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                 decode_index, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
                                  nsplits, stream);
   }
   return rc;

@@ -176,8 +176,9 @@ int launch_nt(int nt, void* y, int y_is_f32, const bf16* x, const bf16* w, const
 
 // y: bf16 (y_dtype 1) or fp32 (0); bias may be null. mode 0: y[M,N]. mode 1 (SwiGLU): w is [2I, K],
 // N must be 2I, y is [M, I], bias must be null. Refuses (OSB_ERR_UNSUPPORTED) M > 64 and K not a multiple of 8.
+// warps: 0 picks the number of warps per CTA (the split of K) from the shape; 4, 8 or 16 force it.
 OSB_API int osb_gemm_skinny_bf16(void* y, int y_dtype, const void* x, const void* w, const void* bias,
-                                 int bias_dtype, int M, int N, int K, int mode, cudaStream_t stream) {
+                                 int bias_dtype, int M, int N, int K, int mode, int warps_req, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return OSB_OK;
   if (M > 64 || K <= 0 || (K & 7)) return OSB_ERR_UNSUPPORTED;
   int I = 0;
@@ -190,6 +191,7 @@ OSB_API int osb_gemm_skinny_bf16(void* y, int y_dtype, const void* x, const void
   const int ctas = mode == 1 ? (I + 7) / 8 : (N + 15) / 16;
   const int nblocks = (K + 63) / 64;
   int warps = ctas >= 148 * 6 ? 4 : (ctas >= 148 * 2 ? 8 : 16);
+  if (warps_req == 4 || warps_req == 8 || warps_req == 16) warps = warps_req;
   while (warps > 4 && warps > nblocks) warps >>= 1;
   const int nt = (M + 7) / 8;
   const int yf = y_dtype == OSB_F32, bf = bias_dtype == OSB_F32;

@@ -104,7 +104,90 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
   __syncthreads();
   if (threadIdx.x == 0) out[r] = chosen >= 0 ? chosen : amax;
 }
+
+// Greedy over many CTAs: each block takes a slice of the row, the last step combines the slices.
+constexpr int ARGMAX_SLICES = 32;
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi,
+                                                             const float* __restrict__ logits, int V) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int r = blockIdx.y, sl = blockIdx.x;
+  const int per = (((V + ARGMAX_SLICES - 1) / ARGMAX_SLICES) + 3) & ~3;
+  const int lo = sl * per, hi = min(V, lo + per);
+  const float* row = logits + (size_t)r * V;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  const bool vec = ((V & 3) == 0);  // rows stay 16-byte aligned
+  if (vec) {
+    for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      if (!(v.x != v.x)) argmax_combine(bv, bi, v.x, i);
+      if (!(v.y != v.y)) argmax_combine(bv, bi, v.y, i + 1);
+      if (!(v.z != v.z)) argmax_combine(bv, bi, v.z, i + 2);
+      if (!(v.w != v.w)) argmax_combine(bv, bi, v.w, i + 3);
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float v = row[i];
+      if (!(v != v)) argmax_combine(bv, bi, v, i);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_combine(bv, bi, ov, oi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = bv;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = blockDim.x >> 5;
+    bv = lane < nwarps ? sv[lane] : -INFINITY;
+    bi = lane < nwarps ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      argmax_combine(bv, bi, ov, oi);
+    }
+    if (lane == 0) {
+      pv[r * ARGMAX_SLICES + sl] = bv;
+      pi[r * ARGMAX_SLICES + sl] = bi;
+    }
+  }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const int* __restrict__ pi) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float bv = pv[r * ARGMAX_SLICES + lane];
+  int bi = pi[r * ARGMAX_SLICES + lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_combine(bv, bi, ov, oi);
+  }
+  if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+}
 }  // namespace
+
+// Greedy for all rows with the row spread over 32 CTAs. scratch: R*32 floats and R*32 ints.
+OSB_API int osb_argmax(int* out, const float* logits, float* scratch_v, int* scratch_i, int R, int V,
+                       cudaStream_t stream) {
+  if (R <= 0) return OSB_OK;
+  if (V <= 0) return OSB_ERR_BAD_SHAPE;
+  static_assert(ARGMAX_SLICES == 32, "the final step is one warp");
+  argmax_partial_kernel<<<dim3(ARGMAX_SLICES, R), 256, 0, stream>>>(scratch_v, scratch_i, logits, V);
+  int rc = osb_last_error();
+  if (rc) return rc;
+  argmax_final_kernel<<<R, 32, 0, stream>>>(out, scratch_v, scratch_i);
+  return osb_last_error();
+}
 
 // out[R] int32; logits [R,V] fp32; temperature/uniform [R] fp32 (temperature may be null: all greedy).
 OSB_API int osb_sample(int* out, const float* logits, const float* temperature, const float* uniform, int R, int V,

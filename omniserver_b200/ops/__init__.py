@@ -75,6 +75,7 @@ class CudaKernels:
         self.lib = library.load()
         self._err: Dict[int, torch.Tensor] = {}
         self.launches = 0  # kernels of this library launched so far
+        self.skinny_warps = 0  # 0: the skinny GEMM picks its K split from the shape
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> ctypes.c_void_p:
@@ -199,7 +200,7 @@ class CudaKernels:
         if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and hasattr(self.lib, "osb_gemm_skinny_bf16"):
             y = torch.empty((M, N), dtype=out_dtype, device=x.device)
             rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias),
-                                               _dt(bias) if bias is not None else 0, M, N, K, 0, self._stream())
+                                               _dt(bias) if bias is not None else 0, M, N, K, 0, self.skinny_warps, self._stream())
             if rc != 10003:
                 self._ok(rc, "gemm_skinny_bf16")
                 return y
@@ -233,7 +234,8 @@ class CudaKernels:
         if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= self.SKINNY_MAX_ROWS and K % 8 == 0
                 and out_dtype in (torch.bfloat16, torch.float32)):
             y = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
-            rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(None), 0, M, N, K, 1, self._stream())
+            rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(None), 0, M, N, K, 1, self.skinny_warps,
+                                               self._stream())
             self._ok(rc, "gemm_skinny_bf16(swiglu)")
             return y
         return self.silu_mul(self.linear(x, w, None, x.dtype if x.dtype == w.dtype else torch.float32), out_dtype)
@@ -321,7 +323,7 @@ class CudaKernels:
                 and out_dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and decode_index is not None)
         if fast:
             _cuda_contig("decode_index", decode_index, torch.int32)
-            part_o = part_ml = None
+            part_o = part_ml = counters = None
             chunk, nsplits = 64, 1
             if n_decode > 0:
                 chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len)
@@ -329,14 +331,15 @@ class CudaKernels:
                     n_o, n_ml = n_decode * nh * nsplits * hd, n_decode * nh * nsplits * 2
                     part_o = self._scratch(scratch, "attn_part_o", n_o, qkv.device)
                     part_ml = self._scratch(scratch, "attn_part_ml", n_ml, qkv.device)
+                    counters = self._scratch(scratch, "attn_counters", n_decode * nkv * ((nh // nkv + 15) // 16),
+                                             qkv.device, zero_int=True)
             rc = self.lib.osb_paged_attn_bf16(
                 _p(out), _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
                 _p(cu_q), _p(seq_lens), _p(decode_index), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
-                ctypes.c_float(scale), win, max_q_len, n_decode, n_multi, _p(part_o), _p(part_ml), chunk, nsplits,
-                self._stream())
+                ctypes.c_float(scale), win, max_q_len, n_decode, n_multi, _p(part_o), _p(part_ml), _p(counters), chunk,
+                nsplits, self._stream())
             self._ok(rc, "paged_attn_bf16")
-            self.launches += (1 if n_multi > 0 or n_decode == 0 else 0) + (1 if n_decode > 0 and nsplits > 1 else 0) \
-                + (1 if n_decode > 0 else 0) - 1
+            self.launches += (1 if n_multi > 0 or n_decode == 0 else 0) + (1 if n_decode > 0 else 0) - 1
             return out
         rc = self.lib.osb_paged_attn_generic(
             _p(out), _dt(out), _p(qkv), _dt(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _dt(k_cache),
@@ -354,15 +357,26 @@ class CudaKernels:
         want = max(1, -(-target_ctas // per_split))
         chunk = -(-max(1, max_kv_len) // want)
         chunk = max(128, -(-chunk // 64) * 64)
+        while -(-max_kv_len // chunk) > 128:      # the kernel merges at most 128 splits
+            chunk *= 2
         return chunk, max(1, -(-max_kv_len // chunk))
 
     @staticmethod
-    def _scratch(pool: Optional[dict], name: str, numel: int, device) -> torch.Tensor:
+    def _scratch(pool: Optional[dict], name: str, numel: int, device, zero_int: bool = False) -> torch.Tensor:
+        """A scratch buffer kept in ``pool`` across calls. ``zero_int``: int32 counters that start at
+        zero (the kernels that use them leave them zero)."""
+        def make(n):
+            with torch.inference_mode(False):
+                if zero_int:
+                    return torch.zeros(n, dtype=torch.int32, device=device)
+                return torch.empty(n, dtype=torch.float32, device=device)
         if pool is None:
-            return torch.empty(numel, dtype=torch.float32, device=device)
+            return make(numel)
         t = pool.get(name)
         if t is None or t.numel() < numel:
-            t = torch.empty(numel, dtype=torch.float32, device=device)
+            if t is not None:
+                pool.setdefault("_retired", []).append(t)   # a captured graph may still point at it
+            t = make(max(numel, 2 * t.numel() if t is not None else numel))
             pool[name] = t
         return t
 
@@ -387,6 +401,13 @@ class CudaKernels:
             _cuda_contig("uniform", uniform, torch.float32)
             _check(temperature.shape == (R,) and uniform.shape == (R,), "sample: temperature/uniform [R]")
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        if temperature is None and V >= 4096:
+            sv = torch.empty((R, 32), dtype=torch.float32, device=logits.device)
+            si = torch.empty((R, 32), dtype=torch.int32, device=logits.device)
+            rc = self.lib.osb_argmax(_p(out), _p(logits), _p(sv), _p(si), R, V, self._stream())
+            self._ok(rc, "argmax")
+            self.launches += 1
+            return out
         rc = self.lib.osb_sample(_p(out), _p(logits), _p(temperature), _p(uniform), R, V, self._stream())
         self._ok(rc, "sample")
         return out
