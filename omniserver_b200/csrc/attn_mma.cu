@@ -572,3 +572,72 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
   }
   return rc;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate (declared in attn_decode_noalloc.h).
+//
+// The split-key decode kernel above needs scratch memory for the splits' partial results. Some
+// hosts of this library have no way to provide it: a runtime that hands out all device memory at
+// start-up and forbids cudaMalloc afterwards, a plug-in running inside another process's memory
+// budget, code on a latency path where an allocator call is not allowed. For them this entry point
+// keeps the scratch inside the library, in a fixed array in device memory.
+namespace {
+constexpr long long NOALLOC_SCRATCH_FLOATS = 1ll << 20;  // 4 MiB per GPU that loads the library
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+OSB_API long long osb_attn_decode_noalloc_capacity() { return NOALLOC_SCRATCH_FLOATS; }
+
+OSB_API int osb_attn_decode_noalloc(void* out, const void* q, int q_row_stride, const void* k_cache,
+                                    const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
+                                    const int* seq_lens, const int* decode_index, int S, int nh, int nkv, int hd,
+                                    int page_size, int num_pages, float scale, int window, int n_decode, int chunk,
+                                    int nsplits, cudaStream_t stream) {
+  if (S <= 0 || n_decode <= 0) return OSB_OK;
+  if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
+  if (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0 || nsplits > MAX_SPLITS) return OSB_ERR_BAD_SHAPE;
+  long long o_floats, ml_floats, counter_ints;
+  osb_attn_decode_scratch(n_decode, nh, nkv, hd, nsplits, &o_floats, &ml_floats, &counter_ints);
+  // layout of the array: counters | part_o | part_ml, each starting on a 256-byte boundary
+  const long long o_offset = (counter_ints + 63) / 64 * 64;
+  const long long ml_offset = o_offset + (o_floats + 63) / 64 * 64;
+  if (nsplits > 1 && ml_offset + ml_floats > NOALLOC_SCRATCH_FLOATS) return OSB_ERR_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return OSB_ERR_UNSUPPORTED;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // In host code the array's name is not a device address; ask the runtime for the address on
+    // the current device, once per device.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  int* counters = reinterpret_cast<int*>(g_noalloc_ptr[dev]);
+  float* part_o = g_noalloc_ptr[dev] + o_offset;
+  float* part_ml = g_noalloc_ptr[dev] + ml_offset;
+  if (nsplits > 1) {
+    // The counters are the one part of the array that must start at zero. A completed call leaves
+    // them zero, but the array is shared and keeps whatever the last call left (an aborted launch,
+    // another shape), so they are cleared on the stream before every launch.
+    e = cudaMemsetAsync(counters, 0, (size_t)counter_ints * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const float scale_log2 = scale * LOG2E;
+  bf16* o = (bf16*)out;
+  const bf16 *qq = (const bf16*)q, *kc = (const bf16*)k_cache, *vc = (const bf16*)v_cache;
+  if (hd <= 64)
+    return launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                                decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                nsplits, stream);
+  if (hd <= 128)
+    return launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                                 decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 nsplits, stream);
+  return launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                               decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                               nsplits, stream);
+}
