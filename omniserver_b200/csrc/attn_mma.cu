@@ -22,25 +22,39 @@ constexpr int TILE_N = 64;
 constexpr int NTHREADS = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 
-// Copies keys [key0, key0 + TILE_N) of one kv head into a shared tile [TILE_N][hd + 8].
-__device__ __forceinline__ void load_kv_tile_async(bf16* tile, const bf16* __restrict__ cache,
-                                                   const int* __restrict__ bt, int kvh, int nkv, int ps, int hd,
-                                                   int key0, int kv_end, int num_pages, int tid) {
+// Copies keys [key0, key0 + TILE_N) of one kv head into the shared tiles ktile and vtile
+// ([TILE_N][hd + 8] each). The page size is a power of two; key0 is a multiple of TILE_N, so a tile
+// starts on a page boundary (or lies inside one page). The tile's page ids are fetched once per warp
+// (lane l holds page l of the tile) and handed to the rows by shuffle. Rows at or beyond kv_end and
+// rows of pages that were given back are zero-filled. Every thread runs the same number of
+// iterations (hd/16), so the shuffles are warp-uniform.
+__device__ __forceinline__ void load_kv_tiles_async(bf16* ktile, bf16* vtile, const bf16* __restrict__ kc,
+                                                    const bf16* __restrict__ vc, const int* __restrict__ bt, int kvh,
+                                                    int nkv, int log2ps, int hd, int key0, int kv_end, int num_pages,
+                                                    int tid) {
+  const int lane = tid & 31;
   const int cpr = hd >> 3;  // 16-byte chunks per row
   const int stride = hd + 8;
+  const int first_page = key0 >> log2ps;
+  const int npages = log2ps >= 6 ? 1 : (TILE_N >> log2ps);
+  int my_page = -1;
+  if (lane < npages && ((first_page + lane) << log2ps) < kv_end) {
+    my_page = bt[first_page + lane];
+    if (my_page >= num_pages) my_page = -1;
+  }
+  const size_t page_stride = ((size_t)nkv << log2ps) * hd;
+  const size_t head_off = ((size_t)kvh << log2ps) * hd;
+  const int ps_mask = (1 << log2ps) - 1;
   int r = tid / cpr, c = tid - r * cpr;
   const int dr = NTHREADS / cpr, dc = NTHREADS - dr * cpr;
-  while (r < TILE_N) {
+  const int iters = cpr >> 1;  // TILE_N * cpr / NTHREADS
+  for (int it = 0; it < iters; ++it) {
     const int key = key0 + r;
-    bool valid = key < kv_end;
-    const bf16* src = cache;
-    if (valid) {
-      const int pi = key / ps;
-      const int page = bt[pi];
-      valid = page >= 0 && page < num_pages;
-      if (valid) src = cache + (((size_t)page * nkv + kvh) * ps + (key - pi * ps)) * hd + c * 8;
-    }
-    cp_async16(tile + r * stride + c * 8, src, valid);
+    const int page = __shfl_sync(0xffffffffu, my_page, (key >> log2ps) - first_page);
+    const bool valid = key < kv_end && page >= 0;
+    const size_t off = valid ? (size_t)page * page_stride + head_off + (size_t)(key & ps_mask) * hd + c * 8 : 0;
+    cp_async16(ktile + r * stride + c * 8, kc + off, valid);
+    cp_async16(vtile + r * stride + c * 8, vc + off, valid);
     r += dr;
     c += dc;
     if (c >= cpr) {
@@ -56,8 +70,8 @@ template <int HD_MAX>
 __global__ void __launch_bounds__(NTHREADS) attn_prefill_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ kc,
     const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
-    const int* __restrict__ seq_lens, int nh, int nkv, int hd, int ps, int num_pages, float scale_log2, int window,
-    int skip_single) {
+    const int* __restrict__ seq_lens, int nh, int nkv, int hd, int log2ps, int num_pages, float scale_log2,
+    int window, int skip_single) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int stride = hd + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [64][stride]
@@ -90,8 +104,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_kernel(
       cp_async16(qs + r * stride + c * 8, src, valid);
     }
   }
-  load_kv_tile_async(kvs, kc, bt, kvh, nkv, ps, hd, tile_begin * TILE_N, kv_end, num_pages, tid);
-  load_kv_tile_async(kvs + tile_elems, vc, bt, kvh, nkv, ps, hd, tile_begin * TILE_N, kv_end, num_pages, tid);
+  load_kv_tiles_async(kvs, kvs + tile_elems, kc, vc, bt, kvh, nkv, log2ps, hd, tile_begin * TILE_N, kv_end, num_pages, tid);
   cp_async_commit();
 
   constexpr int KS = HD_MAX / 16;  // k-steps of QK^T, pairs of n-tiles of PV
@@ -116,8 +129,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_kernel(
     const int st = (t - tile_begin) & 1;
     if (t + 1 <= tile_end) {
       bf16* nk = kvs + (st ^ 1) * 2 * tile_elems;
-      load_kv_tile_async(nk, kc, bt, kvh, nkv, ps, hd, (t + 1) * TILE_N, kv_end, num_pages, tid);
-      load_kv_tile_async(nk + tile_elems, vc, bt, kvh, nkv, ps, hd, (t + 1) * TILE_N, kv_end, num_pages, tid);
+      load_kv_tiles_async(nk, nk + tile_elems, kc, vc, bt, kvh, nkv, log2ps, hd, (t + 1) * TILE_N, kv_end, num_pages, tid);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -234,8 +246,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
-    const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int hd, int ps, int num_pages,
-    float scale_log2, int window, int chunk, int nsplits) {
+    const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int hd, int log2ps,
+    int num_pages, float scale_log2, int window, int chunk, int nsplits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_last;
   const int stride = hd + 8;
@@ -275,8 +287,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   for (int st = 0; st < STAGES - 1; ++st) {
     if (st < ntiles) {
       bf16* dst = kvs + st * 2 * tile_elems;
-      load_kv_tile_async(dst, kc, bt, kvh, nkv, ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
-      load_kv_tile_async(dst + tile_elems, vc, bt, kvh, nkv, ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
+      load_kv_tiles_async(dst, dst + tile_elems, kc, vc, bt, kvh, nkv, log2ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
     }
     cp_async_commit();
   }
@@ -297,8 +308,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
       const int tn = t + STAGES - 1;
       if (tn < ntiles) {
         bf16* dst = kvs + (tn % STAGES) * 2 * tile_elems;
-        load_kv_tile_async(dst, kc, bt, kvh, nkv, ps, hd, k_begin + tn * TILE_N, k_end, num_pages, tid);
-        load_kv_tile_async(dst + tile_elems, vc, bt, kvh, nkv, ps, hd, k_begin + tn * TILE_N, k_end, num_pages, tid);
+        load_kv_tiles_async(dst, dst + tile_elems, kc, vc, bt, kvh, nkv, log2ps, hd, k_begin + tn * TILE_N, k_end, num_pages, tid);
       }
       cp_async_commit();
     }
@@ -463,34 +473,51 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     sml[idx * 2 + 1] = __ldcg(part_ml + prow * 2 + 1);
   }
   __syncthreads();
-  for (int idx = tid; idx < rows * hd; idx += NTHREADS) {
-    const int r = idx / hd, d = idx - r * hd;
+  // four output columns per thread; the loads of up to 8 splits are in flight together
+  const int hq = hd >> 2;
+  for (int idx = tid; idx < rows * hq; idx += NTHREADS) {
+    const int r = idx / hq, d = (idx - r * hq) * 4;
     const float* ml = sml + (size_t)r * nv * 2;
     float M = -INFINITY;
     for (int sp = 0; sp < nv; ++sp) M = fmaxf(M, ml[sp * 2]);
     const float* po = part_o + (((size_t)drow * nh + head0 + r) * nsplits + first_split) * hd + d;
-    float L = 0.0f, acc = 0.0f;
-#pragma unroll 4
-    for (int sp = 0; sp < nv; ++sp) {
-      const float ms = ml[sp * 2];
-      const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
-      L += ml[sp * 2 + 1] * f;
-      acc += __ldcg(po + (size_t)sp * hd) * f;
+    float L = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int sp0 = 0; sp0 < nv; sp0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (sp0 + u < nv) v[u] = __ldcg(reinterpret_cast<const float4*>(po + (size_t)(sp0 + u) * hd));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (sp0 + u < nv) {
+          const float ms = ml[(sp0 + u) * 2];
+          const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
+          L += ml[(sp0 + u) * 2 + 1] * f;
+          acc.x += v[u].x * f;
+          acc.y += v[u].y * f;
+          acc.z += v[u].z * f;
+          acc.w += v[u].w * f;
+        }
+      }
     }
-    out[((size_t)q0 * nh + head0 + r) * hd + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    bf16* op = out + ((size_t)q0 * nh + head0 + r) * hd + d;
+    *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
   }
 }
 
 template <int HD_MAX>
 int launch_prefill(bf16* out, const bf16* q, int q_row_stride, const bf16* kc, const bf16* vc, const int* bt,
-                   int bt_stride, const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int hd, int ps,
+                   int bt_stride, const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int hd, int log2ps,
                    int num_pages, float scale_log2, int window, int max_q_len, int skip_single, cudaStream_t stream) {
   const size_t smem = (size_t)(64 + 4 * TILE_N) * (hd + 8) * sizeof(bf16);
   auto k = attn_prefill_kernel<HD_MAX>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const dim3 grid((max_q_len + 63) / 64, nh, S);
-  k<<<grid, NTHREADS, smem, stream>>>(out, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens, nh, nkv, hd, ps,
+  k<<<grid, NTHREADS, smem, stream>>>(out, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens, nh, nkv, hd, log2ps,
                                       num_pages, scale_log2, window, skip_single);
   return osb_last_error();
 }
@@ -498,7 +525,7 @@ int launch_prefill(bf16* out, const bf16* q, int q_row_stride, const bf16* kc, c
 template <int HD_MAX, int STAGES>
 int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_stride, const bf16* kc,
                   const bf16* vc, const int* bt, int bt_stride, const int* cu_q, const int* seq_lens,
-                  const int* decode_index, int* counters, int S, int nh, int nkv, int hd, int ps, int num_pages,
+                  const int* decode_index, int* counters, int S, int nh, int nkv, int hd, int log2ps, int num_pages,
                   float scale_log2, int window, int chunk, int nsplits, cudaStream_t stream) {
   const size_t smem = (size_t)(16 + STAGES * 2 * TILE_N) * (hd + 8) * sizeof(bf16);
   auto k = attn_decode_kernel<HD_MAX, STAGES>;
@@ -507,7 +534,7 @@ int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q
   const int g = nh / nkv;
   const dim3 grid(nsplits, nkv * ((g + 15) / 16), S);
   k<<<grid, NTHREADS, smem, stream>>>(out, part_o, part_ml, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens,
-                                      decode_index, counters, nh, nkv, hd, ps, num_pages, scale_log2, window, chunk,
+                                      decode_index, counters, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                       nsplits);
   return osb_last_error();
 }
@@ -521,13 +548,25 @@ OSB_API void osb_attn_decode_scratch(int n_decode, int nh, int nkv, int hd, int 
   *counter_ints = (long long)n_decode * nkv * ((nh / nkv + 15) / 16);
 }
 
-constexpr int MAX_SPLITS = 128;  // the merging CTA keeps (max, sum) of 16 rows x splits in shared memory
+constexpr int MAX_SPLITS = 128;
+
+// log2 of a page size the tensor-core kernels take (a power of two from 2 up), else -1
+static inline int page_log2(int page_size) {
+  if (page_size < 2 || (page_size & (page_size - 1))) return -1;
+  int l = 0;
+  while ((1 << l) < page_size) ++l;
+  return l;
+}
+static int g_decode_stages = 3;  // the merging CTA keeps (max, sum) of 16 rows x splits in shared memory
 
 // out [T, nh*hd] bf16. Requests with one token run through the split-key decode kernel when
 // n_decode > 0 (decode_index[s] = index among them; part_o/part_ml/counters sized by
 // osb_attn_decode_scratch, counters all zero before the first use (the kernel leaves them zero);
 // chunk a multiple of 64, nsplits = ceil(max_kv_len / chunk) <= 128); all others (and all, when
 // n_decode == 0) through the prefill kernel.
+// Pipeline depth of the decode kernel for head sizes up to 128 (2 or 3 tiles in flight per CTA).
+OSB_API void osb_attn_set_decode_stages(int stages) { g_decode_stages = stages == 2 ? 2 : 3; }
+
 OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
                                 const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
@@ -535,6 +574,8 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
                                 float* part_ml, int* counters, int chunk, int nsplits, cudaStream_t stream) {
   if (S <= 0) return OSB_OK;
   if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
+  const int log2ps = page_log2(page_size);
+  if (log2ps < 0) return OSB_ERR_UNSUPPORTED;
   if (n_decode > 0 && (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0 || nsplits > MAX_SPLITS))
     return OSB_ERR_BAD_SHAPE;
   if (n_decode > 0 && nsplits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr))
@@ -547,27 +588,31 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
     const int skip = n_decode > 0 ? 1 : 0;
     if (hd <= 64)
       rc = launch_prefill<64>(o, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, hd,
-                              page_size, num_pages, scale_log2, window, max_q_len, skip, stream);
+                              log2ps, num_pages, scale_log2, window, max_q_len, skip, stream);
     else if (hd <= 128)
       rc = launch_prefill<128>(o, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, hd,
-                               page_size, num_pages, scale_log2, window, max_q_len, skip, stream);
+                               log2ps, num_pages, scale_log2, window, max_q_len, skip, stream);
     else
       rc = launch_prefill<256>(o, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, hd,
-                               page_size, num_pages, scale_log2, window, max_q_len, skip, stream);
+                               log2ps, num_pages, scale_log2, window, max_q_len, skip, stream);
     if (rc != 0) return rc;
   }
   if (n_decode > 0) {
     if (hd <= 64)
       rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                 nsplits, stream);
+    else if (hd <= 128 && g_decode_stages == 2)
+      rc = launch_decode<128, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
+                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
+                                 nsplits, stream);
     else if (hd <= 128)
       rc = launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                 decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                  nsplits, stream);
     else
       rc = launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                 decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                  nsplits, stream);
   }
   return rc;
@@ -598,6 +643,8 @@ OSB_API int osb_attn_decode_noalloc(void* out, const void* q, int q_row_stride, 
   if (S <= 0 || n_decode <= 0) return OSB_OK;
   if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
   if (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0 || nsplits > MAX_SPLITS) return OSB_ERR_BAD_SHAPE;
+  const int log2ps = page_log2(page_size);
+  if (log2ps < 0) return OSB_ERR_UNSUPPORTED;
   long long o_floats, ml_floats, counter_ints;
   osb_attn_decode_scratch(n_decode, nh, nkv, hd, nsplits, &o_floats, &ml_floats, &counter_ints);
   // layout of the array: counters | part_o | part_ml, each starting on a 256-byte boundary
@@ -631,13 +678,13 @@ OSB_API int osb_attn_decode_noalloc(void* out, const void* q, int q_row_stride, 
   const bf16 *qq = (const bf16*)q, *kc = (const bf16*)k_cache, *vc = (const bf16*)v_cache;
   if (hd <= 64)
     return launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                 nsplits, stream);
   if (hd <= 128)
     return launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                                 decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                  nsplits, stream);
   return launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
-                               decode_index, counters, S, nh, nkv, hd, page_size, num_pages, scale_log2, window, chunk,
+                               decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                nsplits, stream);
 }

@@ -320,7 +320,8 @@ class CudaKernels:
         out = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
         win = int(window) if window else 0
         fast = (not exact and qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-                and out_dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and decode_index is not None)
+                and out_dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and decode_index is not None
+                and k_cache.shape[2] >= 2 and (k_cache.shape[2] & (k_cache.shape[2] - 1)) == 0)
         if fast:
             _cuda_contig("decode_index", decode_index, torch.int32)
             part_o = part_ml = counters = None
@@ -350,11 +351,12 @@ class CudaKernels:
         return out
 
     @staticmethod
-    def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 444):
-        """(chunk, nsplits) of the split-key decode kernel: enough CTAs to fill the GPU, splits ending
-        at multiples of ``chunk`` keys (a multiple of 64)."""
+    def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 296):
+        """(chunk, nsplits) of the split-key decode kernel. ``target_ctas`` is the number of CTAs the
+        GPU holds at once (148 SMs x 2); the keys are cut so that the grid fills them but does not
+        spill into a second wave. Splits end at multiples of ``chunk`` keys (a multiple of 64)."""
         per_split = max(1, n_decode * nkv * ((group + 15) // 16))
-        want = max(1, -(-target_ctas // per_split))
+        want = max(1, target_ctas // per_split)
         chunk = -(-max(1, max_kv_len) // want)
         chunk = max(128, -(-chunk // 64) * 64)
         while -(-max_kv_len // chunk) > 128:      # the kernel merges at most 128 splits

@@ -1,0 +1,172 @@
+"""Times single kernels at the shapes of a decode or prefill step and prints achieved bandwidth.
+
+    python -m omniserver_b200.ops.microbench [--what gemm|attn_decode|attn_prefill|norm|all]
+        [--batch 1,8,64] [--ctx 2048] [--hidden 1536 --heads 12 --kv-heads 2 --head-dim 128 --inter 8960 --vocab 151936]
+
+Every timed call runs on its own copy of the weights or cache pages (enough copies to exceed the
+L2), and the calls are replayed from a CUDA graph so that host launch time is not measured.
+Times are CUDA-event times per call; GB/s counts the bytes the kernel has to read once.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Callable, List
+
+import torch
+
+from .. import ops
+
+
+def graph_time_us(fn: Callable[[int], None], n_rot: int, iters: int = 5) -> float:
+    """Mean time of fn(i) over i in range(n_rot), replayed from a CUDA graph."""
+    for i in range(n_rot):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n_rot):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (iters * n_rot)
+
+
+def peak_gbs() -> float:
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def bench_gemm(args, K, dev, peak) -> None:
+    H, I, V = args.hidden, args.inter, args.vocab
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    shapes = [("qkv", qkv, H, 0), ("o", H, args.heads * args.head_dim, 0), ("gate_up+silu", 2 * I, H, 1), ("down", H, I, 0),
+              ("head", V, H, 0)]
+    print("== projections: y[M,N] = x[M,K] W[N,K]^T  (us | GB/s of W | fraction of %.0f GB/s)" % peak)
+    for name, N, Kd, mode in shapes:
+        n_rot = max(3, int(300e6 // (N * Kd * 2)) + 1)
+        ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(n_rot)]
+        for M in args.batch:
+            x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+            out_dt = torch.float32 if name == "head" else torch.bfloat16
+            cols = []
+            for warps in args.warps:
+                K.skinny_warps = warps
+                if mode:
+                    us = graph_time_us(lambda i: K.gate_up_silu(x, ws[i], out_dt), n_rot)
+                else:
+                    us = graph_time_us(lambda i: K.linear(x, ws[i], None, out_dt), n_rot)
+                gbs = N * Kd * 2 / us / 1e3
+                cols.append(f"warps={warps}: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+            K.skinny_warps = 0
+            if not mode:
+                us = graph_time_us(lambda i: torch.mm(x, ws[i].t()), n_rot)
+                cols.append(f"library: {us:7.1f} us {N * Kd * 2 / us / 1e3:6.0f} GB/s")
+            print(f"{name:13s} M={M:3d} N={N:6d} K={Kd:5d} | " + " | ".join(cols), flush=True)
+
+
+def bench_attn_decode(args, K, dev, peak) -> None:
+    nh, nkv, hd, ps, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.ctx
+    print("== decode attention: one token per request over %d cached keys (us | GB/s of K,V | fraction)" % ctx)
+    for B in args.batch:
+        pages = B * (-(-ctx // ps))
+        n_rot = max(3, int(300e6 // (pages * nkv * ps * hd * 4)) + 1)
+        kc = [torch.randn(pages, nkv, ps, hd, device=dev, dtype=torch.bfloat16) for _ in range(n_rot)]
+        vc = [torch.randn(pages, nkv, ps, hd, device=dev, dtype=torch.bfloat16) for _ in range(n_rot)]
+        qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=dev, dtype=torch.bfloat16)
+        bt = torch.randperm(pages, device=dev).to(torch.int32).view(B, -1)
+        cu_q = torch.arange(B + 1, device=dev, dtype=torch.int32)
+        sl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+        ts = torch.arange(B, device=dev, dtype=torch.int32)
+        pool = {}
+        for target in args.target_ctas:
+            orig = ops.CudaKernels.decode_splits
+            ops.CudaKernels.decode_splits = staticmethod(
+                lambda n, k, g, m, target_ctas=target, _o=orig: _o(n, k, g, m, target_ctas))
+            try:
+                us = graph_time_us(lambda i: K.paged_attention(
+                    qkv, kc[i], vc[i], bt, cu_q, sl, ts, nh, nkv, hd, hd ** -0.5, None, 1, ctx, torch.bfloat16,
+                    decode_index=ts, n_decode=B, n_multi=0, scratch=pool), n_rot)
+            finally:
+                ops.CudaKernels.decode_splits = orig
+            gbs = B * ctx * nkv * hd * 2 * 2 / us / 1e3
+            chunk, nsp = orig(B, nkv, nh // nkv, ctx, target)
+            print(f"B={B:3d} chunk={chunk:5d} splits={nsp:3d} | {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}", flush=True)
+
+
+def bench_attn_prefill(args, K, dev, peak) -> None:
+    nh, nkv, hd, ps, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.ctx
+    pages = -(-ctx // ps)
+    kc = torch.randn(pages, nkv, ps, hd, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(pages, nkv, ps, hd, device=dev, dtype=torch.bfloat16)
+    qkv = torch.randn(ctx, (nh + 2 * nkv) * hd, device=dev, dtype=torch.bfloat16)
+    bt = torch.randperm(pages, device=dev).to(torch.int32).view(1, -1)
+    cu_q = torch.tensor([0, ctx], device=dev, dtype=torch.int32)
+    sl = torch.tensor([ctx], device=dev, dtype=torch.int32)
+    ts = torch.zeros(ctx, device=dev, dtype=torch.int32)
+    di = torch.full((1,), -1, device=dev, dtype=torch.int32)
+    us = graph_time_us(lambda i: K.paged_attention(qkv, kc, vc, bt, cu_q, sl, ts, nh, nkv, hd, hd ** -0.5, None, ctx, ctx,
+                                                   torch.bfloat16, decode_index=di, n_decode=0, n_multi=1), 3)
+    flops = 4 * nh * hd * (ctx * (ctx + 1) // 2)
+    print(f"== prefill attention: {ctx} tokens, causal: {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
+
+
+def bench_norm(args, K, dev, peak) -> None:
+    H = args.hidden
+    print("== add + RMSNorm, rotary + cache write")
+    for T in args.batch:
+        x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+        r = torch.randn(T, H, device=dev)
+        w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        us = graph_time_us(lambda i: K.add_rmsnorm(x, r, w, 1e-6, torch.bfloat16), 20)
+        print(f"add_rmsnorm T={T:3d} H={H}: {us:6.2f} us", flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--what", default="all", choices=["all", "gemm", "attn_decode", "attn_prefill", "norm"])
+    ap.add_argument("--batch", default="1,8,64")
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--hidden", type=int, default=1536)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--kv-heads", type=int, default=2)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--inter", type=int, default=8960)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--warps", default="0", help="K splits of the skinny GEMM to try (0 = its own choice)")
+    ap.add_argument("--stages", type=int, default=3, help="pipeline depth of the decode attention kernel (2 or 3)")
+    ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
+    args = ap.parse_args()
+    args.batch = [int(b) for b in args.batch.split(",")]
+    args.warps = [int(b) for b in args.warps.split(",")]
+    args.target_ctas = [int(b) for b in args.target_ctas.split(",")]
+    dev = torch.device("cuda:0")
+    K = ops.kernels()
+    K.lib.osb_attn_set_decode_stages(args.stages)
+    peak = peak_gbs()
+    with torch.inference_mode():
+        if args.what in ("all", "gemm"):
+            bench_gemm(args, K, dev, peak)
+        if args.what in ("all", "attn_decode"):
+            bench_attn_decode(args, K, dev, peak)
+        if args.what in ("all", "attn_prefill"):
+            bench_attn_prefill(args, K, dev, peak)
+        if args.what in ("all", "norm"):
+            bench_norm(args, K, dev, peak)
+
+
+if __name__ == "__main__":
+    main()
