@@ -56,10 +56,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
   const int b_end = (int)(((long long)(warp + 1) * nblocks) / WARPS);
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
-  // Blocks are processed in groups of PF with the next group's weights already in flight.
+  // Blocks are processed in groups of PF with the next group's weights (and, for few tokens, the
+  // next group's activations) already in flight.
   constexpr int PF = 2;
+  constexpr bool PFX = NT <= 2;  // activations of the next group fit in registers too
   uint4 cur_lo[PF][2], cur_hi[PF][2], nxt_lo[PF][2], nxt_hi[PF][2];
-  auto load_group = [&](int b0, uint4 (&lo)[PF][2], uint4 (&hi)[PF][2]) {
+  uint4 cur_x[PFX ? PF : 1][2][PFX ? NT : 1], nxt_x[PFX ? PF : 1][2][PFX ? NT : 1];
+  auto load_group = [&](int b0, uint4 (&lo)[PF][2], uint4 (&hi)[PF][2], uint4 (&xs)[PFX ? PF : 1][2][PFX ? NT : 1]) {
 #pragma unroll
     for (int u = 0; u < PF; ++u) {
 #pragma unroll
@@ -68,12 +71,20 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
         const bool ok = (b0 + u) < b_end && k < K;
         lo[u][hf] = (ok && row_a >= 0) ? ld_stream16(wa + k) : zero4;
         hi[u][hf] = (ok && row_b >= 0) ? ld_stream16(wb + k) : zero4;
+        if (PFX) {
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const int tok = j * 8 + g;
+            xs[PFX ? u : 0][hf][PFX ? j : 0] =
+                (ok && tok < M) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k) : zero4;
+          }
+        }
       }
     }
   };
-  load_group(b_begin, cur_lo, cur_hi);
+  load_group(b_begin, cur_lo, cur_hi, cur_x);
   for (int b = b_begin; b < b_end; b += PF) {
-    load_group(b + PF, nxt_lo, nxt_hi);
+    load_group(b + PF, nxt_lo, nxt_hi, nxt_x);
 #pragma unroll
     for (int u = 0; u < PF; ++u) {
       if (b + u < b_end) {
@@ -84,9 +95,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
           const unsigned a1[4] = {cur_lo[u][hf].z, cur_hi[u][hf].z, cur_lo[u][hf].w, cur_hi[u][hf].w};
 #pragma unroll
           for (int j = 0; j < NT; ++j) {
-            const int tok = j * 8 + g;
-            uint4 xv = zero4;
-            if (tok < M && k < K) xv = *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k);
+            uint4 xv;
+            if (PFX) {
+              xv = cur_x[PFX ? u : 0][hf][PFX ? j : 0];
+            } else {
+              const int tok = j * 8 + g;
+              xv = zero4;
+              if (tok < M && k < K) xv = *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k);
+            }
             mma_bf16_16816(acc[j], a0, xv.x, xv.y);
             mma_bf16_16816(acc[j], a1, xv.z, xv.w);
           }
@@ -99,6 +115,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
       for (int hf = 0; hf < 2; ++hf) {
         cur_lo[u][hf] = nxt_lo[u][hf];
         cur_hi[u][hf] = nxt_hi[u][hf];
+        if (PFX) {
+#pragma unroll
+          for (int j = 0; j < NT; ++j) cur_x[PFX ? u : 0][hf][PFX ? j : 0] = nxt_x[PFX ? u : 0][hf][PFX ? j : 0];
+        }
       }
     }
   }

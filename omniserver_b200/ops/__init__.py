@@ -69,7 +69,8 @@ class CudaKernels:
     """Launches the hand-written kernels. One instance per process."""
 
     #: rows up to which the bf16 weight-streaming GEMM is used instead of the tiled tensor-core GEMM
-    SKINNY_MAX_ROWS = 64
+    #: (measured on B200: it wins up to 16 rows, the library GEMM from 32 rows on)
+    SKINNY_MAX_ROWS = 16
 
     def __init__(self) -> None:
         self.lib = library.load()
