@@ -39,6 +39,9 @@ _DEVICE_ERR = {
     2: "an embedding-override row outside the step's tokens",
     3: "a cache slot outside the page pool in the key/value write",
     4: "a page index outside the page pool in attention",
+    101: "tcgen05 GEMM: the TMA producer waited too long for a free stage",
+    102: "tcgen05 GEMM: the MMA issuer waited too long for operands",
+    103: "tcgen05 GEMM: the epilogue waited too long for the accumulator",
 }
 
 
@@ -77,6 +80,9 @@ class CudaKernels:
         self._err: Dict[int, torch.Tensor] = {}
         self.launches = 0  # kernels of this library launched so far
         self.skinny_warps = 0  # 0: the skinny GEMM picks its K split from the shape
+        #: bf16 products with more rows than SKINNY_MAX_ROWS: the tcgen05/TMEM/TMA kernel (True) or the
+        #: vendor library's GEMM (False)
+        self.use_tcgen05 = True
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> ctypes.c_void_p:
@@ -205,6 +211,8 @@ class CudaKernels:
             if rc != 10003:
                 self._ok(rc, "gemm_skinny_bf16")
                 return y
+        if self.use_tcgen05 and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            return self.gemm_tcgen05(x, w, bias, out_dtype)
         if K % 8 == 0 and N % 8 == 0:
             # Library GEMM on the tensor cores (fp32 accumulation inside).
             if out_dtype == torch.bfloat16:
@@ -219,6 +227,21 @@ class CudaKernels:
                 y += bias.float()
             return y
         return self.gemm_simt(x, w, bias, out_dtype)
+
+    def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                     swiglu: bool = False) -> torch.Tensor:
+        """bf16 product on tcgen05 tensor cores with TMA-fed operands and the accumulator in TMEM.
+        ``swiglu``: w is [2I, K] (gate rows first) and the result is silu(x Wg^T) * (x Wu^T), [M, I]."""
+        _cuda_contig("x", x, torch.bfloat16)
+        _cuda_contig("w", w, torch.bfloat16)
+        M, K = x.shape
+        N = w.shape[0]
+        _check(w.shape[1] == K, "gemm_tcgen05: x [M,K], w [N,K]")
+        y = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_gemm_tcgen05_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
+                                            M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)), self._stream())
+        self._ok(rc, "gemm_tcgen05_bf16")
+        return y
 
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].
@@ -239,6 +262,9 @@ class CudaKernels:
                                                self._stream())
             self._ok(rc, "gemm_skinny_bf16(swiglu)")
             return y
+        if (self.use_tcgen05 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+                and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            return self.gemm_tcgen05(x, w, None, out_dtype, swiglu=True)
         return self.silu_mul(self.linear(x, w, None, x.dtype if x.dtype == w.dtype else torch.float32), out_dtype)
 
     # ------------------------------------------------------------------ rotary + cache write

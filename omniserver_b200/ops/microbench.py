@@ -77,6 +77,26 @@ def bench_gemm(args, K, dev, peak) -> None:
             print(f"{name:13s} M={M:3d} N={N:6d} K={Kd:5d} | " + " | ".join(cols), flush=True)
 
 
+def bench_gemm_prefill(args, K, dev, peak) -> None:
+    H, I = args.hidden, args.inter
+    qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
+    shapes = [("qkv", qkv, H, 0), ("o", H, args.heads * args.head_dim, 0), ("gate_up", 2 * I, H, 0), ("gate_up+silu", 2 * I, H, 1),
+              ("down", H, I, 0)]
+    print("== projections with many rows: tcgen05 kernel vs the vendor library (us | TFLOP/s)")
+    for M in args.rows:
+        for name, N, Kd, mode in shapes:
+            x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+            ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(3)]
+            fl = 2.0 * M * N * Kd
+            us = graph_time_us(lambda i: K.gemm_tcgen05(x, ws[i], None, torch.bfloat16, swiglu=bool(mode)), 3)
+            if mode:
+                lib = graph_time_us(lambda i: K.silu_mul(torch.mm(x, ws[i].t()), torch.bfloat16), 3)
+            else:
+                lib = graph_time_us(lambda i: torch.mm(x, ws[i].t()), 3)
+            print(f"M={M:5d} {name:13s} N={N:6d} K={Kd:5d} | tcgen05 {us:8.1f} us {fl / us / 1e6:7.1f} TF | "
+                  f"library {lib:8.1f} us {fl / lib / 1e6:7.1f} TF", flush=True)
+
+
 def bench_attn_decode(args, K, dev, peak) -> None:
     nh, nkv, hd, ps, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.ctx
     print("== decode attention: one token per request over %d cached keys (us | GB/s of K,V | fraction)" % ctx)
@@ -136,7 +156,8 @@ def bench_norm(args, K, dev, peak) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=["all", "gemm", "attn_decode", "attn_prefill", "norm"])
+    ap.add_argument("--what", default="all", choices=["all", "gemm", "gemm_prefill", "attn_decode", "attn_prefill", "norm"])
+    ap.add_argument("--rows", default="2048", help="row counts for --what gemm_prefill")
     ap.add_argument("--batch", default="1,8,64")
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--hidden", type=int, default=1536)
@@ -151,6 +172,7 @@ def main() -> None:
     ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
     args = ap.parse_args()
     args.batch = [int(b) for b in args.batch.split(",")]
+    args.rows = [int(b) for b in args.rows.split(",")]
     args.warps = [int(b) for b in args.warps.split(",")]
     args.target_ctas = [int(b) for b in args.target_ctas.split(",")]
     dev = torch.device("cuda:0")
@@ -160,6 +182,8 @@ def main() -> None:
     with torch.inference_mode():
         if args.what in ("all", "gemm"):
             bench_gemm(args, K, dev, peak)
+        if args.what in ("all", "gemm_prefill"):
+            bench_gemm_prefill(args, K, dev, peak)
         if args.what in ("all", "attn_decode"):
             bench_attn_decode(args, K, dev, peak)
         if args.what in ("all", "attn_prefill"):

@@ -113,11 +113,11 @@ def test_linear_bf16_and_f32(dtype, M, N, K_):
 def test_gate_up_silu(dtype, M, I, K_):
     x, w = rnd(M, K_, dtype=dtype), rnd(2 * I, K_, dtype=dtype, seed=1, scale=0.1)
     got = K().gate_up_silu(x.to(DEV), w.to(DEV), dtype)
-    if dtype == torch.float32:
-        want = REF.silu_mul(REF.linear(x.double(), w.double(), None, torch.float64), torch.float64)
-    else:   # the product is rounded to bf16 before the activation, as in the two-kernel path
-        want = REF.gate_up_silu(x, w, torch.float32).double()
     assert got.shape == (M, I)
+    if dtype == torch.bfloat16:   # the product is rounded to bf16 before the activation, as in the two-kernel path
+        assert_swiglu_close(got, x, w, I)
+        return
+    want = REF.silu_mul(REF.linear(x.double(), w.double(), None, torch.float64), torch.float64)
     # a product of two sums: its absolute error is the sums' error (~1e-6 after K fp32 additions)
     # times the other factor, which reaches a few tens here
     scale = float(want.abs().max())
@@ -140,11 +140,56 @@ def test_skinny_gemm_bf16(M, N, K_):
             assert torch.allclose(got.double().cpu(), want, **t)
 
 
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (17, 128, 64), (128, 128, 128), (2048, 2048, 1536), (200, 264, 1536), (130, 1000, 200),
+                                    (300, 1536, 8960), (33, 151936, 96), (129, 8, 72)])
+def test_gemm_tcgen05(M, N, K_):
+    """The TMA/tcgen05/TMEM product at tile-aligned shapes and at ragged ones (rows, columns and K
+    that are no multiples of the tile)."""
+    x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(N, K_, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = rnd(N, dtype=torch.bfloat16, seed=2)
+    want0 = REF.linear(x.double(), w.double(), None, torch.float64)
+    for bias in (None, b, b.float()):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            got = K().gemm_tcgen05(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out_dtype)
+            K().check_device_errors()
+            want = want0 if bias is None else want0 + bias.double()
+            # fp32 accumulation in the tensor core over K products: error grows with K and with the
+            # size of the partial sums, far below one bf16 rounding of the result
+            t = dict(rtol=1e-4, atol=2.5e-8 * K_ * float(want.abs().max()) + 1e-5) if out_dtype == torch.float32 \
+                else tol(torch.bfloat16)
+            assert torch.allclose(got.double().cpu(), want, **t)
+
+
+@pytest.mark.parametrize("M,I,K_", [(128, 64, 64), (2048, 8960, 1536), (100, 200, 96), (33, 176, 80)])
+def test_gemm_tcgen05_swiglu(M, I, K_):
+    x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(2 * I, K_, dtype=torch.bfloat16, seed=1, scale=0.1)
+    got = K().gemm_tcgen05(x.to(DEV), w.to(DEV), None, torch.bfloat16, swiglu=True)
+    K().check_device_errors()
+    assert got.shape == (M, I)
+    assert_swiglu_close(got, x, w, I)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(dtype):
     gu = rnd(5, 2 * 200, dtype=dtype, scale=3.0)
     got = K().silu_mul(gu.to(DEV), dtype)
     assert torch.allclose(got.float().cpu(), REF.silu_mul(gu, dtype).float(), **tol(dtype))
+
+
+def assert_swiglu_close(got, x, w, I):
+    """silu(g) * u with g and u rounded to bf16 before the activation and the result rounded to
+    bf16: the error allowed is one bf16 ulp (2^-8 relative) on g, on u and on the result, carried
+    through the derivative of silu (in its negative tail a relative error of g is amplified by ~|g|)."""
+    g = x.double() @ w[:I].double().T
+    u = x.double() @ w[I:].double().T
+    sig = torch.sigmoid(g)
+    silu = g * sig
+    dsilu = sig + g * sig * (1 - sig)
+    want = silu * u
+    ulp = 2.0 ** -8
+    bound = ulp * ((g * dsilu * u).abs() + 2 * want.abs()) + 1e-3
+    err = (got.double().cpu() - want).abs()
+    assert bool((err <= bound).all()), f"max excess {(err - bound).max().item():.3e}"
 
 
 def _rope_inputs(T, S, half, seed=0):
