@@ -109,21 +109,62 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// Stores 32 consecutive output columns of one row (fp32 values in r) as bf16 or fp32.
+__device__ __forceinline__ void store_row32(void* y, int y_is_f32, size_t row_off, int col, int ncols, const float* v,
+                                            bool vec_ok) {
+  if (y_is_f32) {
+    float* yp = (float*)y + row_off + col;
+    if (vec_ok && col + 32 <= ncols) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(yp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col + j < ncols) yp[j] = v[j];
+    }
+  } else {
+    bf16* yp = (bf16*)y + row_off + col;
+    if (vec_ok && col + 32 <= ncols) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 u;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+        h[0] = __floats2bfloat162_rn(v[j], v[j + 1]);
+        h[1] = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        h[2] = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        h[3] = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        *reinterpret_cast<uint4*>(yp + j) = u;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col + j < ncols) yp[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+// Persistent kernel: CTA c computes tiles c, c + gridDim.x, ... (tile t = column block t / m_blocks,
+// row block t % m_blocks, so that CTAs running together share weight tiles through the L2). The
+// accumulator is double-buffered in TMEM (2 x BN columns): the epilogue of a tile overlaps the
+// main loop of the next.
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ y,
-    int y_is_f32, const void* __restrict__ bias, int bias_is_f32, int M, int N, int K, int I, int* __restrict__ err) {
+    int y_is_f32, const void* __restrict__ bias, int bias_is_f32, int M, int N, int K, int I, int m_blocks,
+    int num_tiles, int* __restrict__ err) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;  // output columns per tile
+  constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;       // two accumulators; allocations are powers of two
   // 1024-byte alignment of every tile (required by the 128-byte swizzle)
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM;
-  const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN);  // first output column of this CTA
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -132,51 +173,57 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // TMEM: BN fp32 columns x 128 lanes
+  if (warp == 1) {  // TMEM: two accumulators of BN fp32 columns x 128 lanes
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = tmem_base_slot;
+  const uint32_t tmem_base = tmem_base_slot;
   volatile int* vabort = &abort_flag;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, vabort)) {
-          if (!*vabort) atomicExch(err, 101);
-          *vabort = 1;
-          break;
+      int issued = 0;  // k-blocks issued over all tiles
+      for (int tile = blockIdx.x; tile < num_tiles && !*vabort; tile += gridDim.x) {
+        const int m0 = (tile % m_blocks) * BM;
+        const int n0 = (tile / m_blocks) * OUT_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++issued) {
+          const int s = issued % STAGES;
+          const uint32_t ph = (uint32_t)(issued / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, vabort)) {
+            if (!*vabort) atomicExch(err, 101);
+            *vabort = 1;
+            break;
+          }
+          unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
+          unsigned char* b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
+          if (EPI == EPI_SWIGLU) {
+            tma_load_2d(b_dst, &map_b, &full_bar[s], kb * BK, n0);                    // gate rows
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, &full_bar[s], kb * BK, I + n0);  // up rows
+          } else {
+            tma_load_2d(b_dst, &map_b, &full_bar[s], kb * BK, n0);
+          }
         }
-        unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
-        unsigned char* b_dst = a_dst + A_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
-        if (EPI == EPI_SWIGLU) {
-          tma_load_2d(b_dst, &map_b, &full_bar[s], kb * BK, n0);                  // 64 gate rows
-          tma_load_2d(b_dst + B_BYTES / 2, &map_b, &full_bar[s], kb * BK, I + n0);  // 64 up rows
-        } else {
-          tma_load_2d(b_dst, &map_b, &full_bar[s], kb * BK, n0);
-        }
-        issued = kb + 1;
       }
       if (*vabort) {
         // copies already started still write into this CTA's shared memory: wait for them (bounded)
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-          const int s = kb % STAGES;
-          const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-          for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(&full_bar[s], ph); ++i) {
+        for (int i = max(0, issued - STAGES); i < issued; ++i) {
+          const int s = i % STAGES;
+          const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+          for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&full_bar[s], ph); ++w) {
           }
         }
       }
@@ -185,109 +232,107 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BM, BN);
+      int consumed = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, vabort)) {
-          if (!*vabort) atomicExch(err, 102);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t aph = (uint32_t)(local >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], aph ^ 1u, vabort)) {  // the epilogue has drained this accumulator
+          if (!*vabort) atomicExch(err, 104);
           *vabort = 1;
           ok = false;
           break;
         }
         tc_fence_after();
-        const unsigned char* a_src = tiles + (size_t)s * STAGE_BYTES;
-        const uint64_t adesc = make_smem_desc(a_src);
-        const uint64_t bdesc = make_smem_desc(a_src + A_BYTES);
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++consumed) {
+          const int s = consumed % STAGES;
+          const uint32_t ph = (uint32_t)(consumed / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, vabort)) {
+            if (!*vabort) atomicExch(err, 102);
+            *vabort = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned char* a_src = tiles + (size_t)s * STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(a_src);
+          const uint64_t bdesc = make_smem_desc(a_src + A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
-          umma_bf16(tmem_acc, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
+            umma_bf16(tmem_acc, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+        umma_commit(&acc_full[buf]);  // fires when every MMA issued so far has completed (also on the abort path)
       }
-      umma_commit(&acc_bar);  // fires when every MMA issued so far has completed (also on the abort path)
     }
   } else {
     // ------------------------------------------------------------------ epilogue: warps 2..5
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int row = m0 + q * 32 + lane;
-    bool ok = mbar_wait(&acc_bar, 0, vabort);
-    if (!ok && lane == 0) {
-      if (!*vabort) atomicExch(err, 103);
-      *vabort = 1;
-    }
-    ok = ok && !*vabort;
-    tc_fence_after();
-    if (ok) {
-      if (EPI == EPI_SWIGLU) {
-        constexpr int HALF = BN / 2;
-#pragma unroll 1
-        for (int c0 = 0; c0 < HALF; c0 += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, g);
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(HALF + c0), u);
-          tmem_ld_wait();
-          if (row < M) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const int col = n0 + c0 + j;
-              // the two-kernel path rounds gate and up to bf16 before the activation; keep that rounding
-              float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j])));
-              float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 1])));
-              float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j])));
-              float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 1])));
-              const float v0 = (g0 / (1.0f + __expf(-g0))) * u0;
-              const float v1 = (g1 / (1.0f + __expf(-g1))) * u1;
-              bf16* yp = (bf16*)y + (size_t)row * I + col;
-              if (col + 1 < I) {
-                *reinterpret_cast<__nv_bfloat162*>(yp) = __floats2bfloat162_rn(v0, v1);
-              } else if (col < I) {
-                yp[0] = __float2bfloat16_rn(v0);
-              }
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-          tmem_ld_wait();
-          if (row < M) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const int col = n0 + c0 + j;
-              float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
-              if (bias) {
-                if (col < N) v0 += bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col]);
-                if (col + 1 < N)
-                  v1 += bias_is_f32 ? ((const float*)bias)[col + 1] : __bfloat162float(((const bf16*)bias)[col + 1]);
-              }
-              if (y_is_f32) {
-                float* yp = (float*)y + (size_t)row * N + col;
-                if (col < N) yp[0] = v0;
-                if (col + 1 < N) yp[1] = v1;
-              } else {
-                bf16* yp = (bf16*)y + (size_t)row * N + col;
-                if (col + 1 < N && (N & 1) == 0) {
-                  *reinterpret_cast<__nv_bfloat162*>(yp) = __floats2bfloat162_rn(v0, v1);
-                } else {
-                  if (col < N) yp[0] = __float2bfloat16_rn(v0);
-                  if (col + 1 < N) yp[1] = __float2bfloat16_rn(v1);
-                }
-              }
-            }
-          }
-        }
+    const int ncols = EPI == EPI_SWIGLU ? I : N;
+    const bool vec_ok = y_is_f32 ? ((ncols & 3) == 0) : ((ncols & 7) == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile % m_blocks) * BM;
+      const int n0 = (tile / m_blocks) * OUT_COLS;
+      const int buf = local & 1;
+      const uint32_t aph = (uint32_t)(local >> 1) & 1u;
+      const int row = m0 + q * 32 + lane;
+      bool ok = mbar_wait(&acc_full[buf], aph, vabort);
+      if (!ok && lane == 0) {
+        if (!*vabort) atomicExch(err, 103);
+        *vabort = 1;
       }
+      ok = ok && !*vabort;
+      if (!__all_sync(0xffffffffu, ok)) break;
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+      const size_t row_off = (size_t)row * ncols;
+#pragma unroll 1
+      for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+        float v[32];
+        if (EPI == EPI_SWIGLU) {
+          uint32_t g[32], u[32];
+          tmem_ld32(tmem_acc + (uint32_t)c0, g);
+          tmem_ld32(tmem_acc + (uint32_t)(BN / 2 + c0), u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            // the two-kernel path rounds gate and up to bf16 before the activation; keep that rounding
+            const float gg = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j])));
+            const float uu = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j])));
+            v[j] = (gg / (1.0f + __expf(-gg))) * uu;
+          }
+        } else {
+          uint32_t r[32];
+          tmem_ld32(tmem_acc + (uint32_t)c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = n0 + c0 + j;
+              if (col < N) v[j] += bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col]);
+            }
+          }
+        }
+        if (row < M && n0 + c0 < ncols) store_row32(y, y_is_f32, row_off, n0 + c0, ncols, v, vec_ok);
+      }
+      // this warp has read its part of the accumulator: hand the buffer back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
   }
 }
 
@@ -322,6 +367,16 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
   return r == CUDA_SUCCESS ? OSB_OK : OSB_ERR_BAD_SHAPE;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* y, int yf, const void* bias, int bf, int M, int N, int K,
            int I, int* err, cudaStream_t stream) {
@@ -330,10 +385,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* y, int yf, const 
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int out_cols = EPI == EPI_SWIGLU ? I : N;
-  const int cols_per_cta = EPI == EPI_SWIGLU ? BN / 2 : BN;
-  const dim3 grid((out_cols + cols_per_cta - 1) / cols_per_cta, (M + BM - 1) / BM);
-  k<<<grid, NUM_THREADS, smem, stream>>>(ma, mb, y, yf, bias, bf, M, N, K, I, err);
+  const int cols_per_tile = EPI == EPI_SWIGLU ? BN / 2 : BN;
+  const int m_blocks = (M + BM - 1) / BM;
+  const int num_tiles = m_blocks * ((out_cols + cols_per_tile - 1) / cols_per_tile);
+  const int ctas = num_tiles < sm_count() ? num_tiles : sm_count();
+  k<<<ctas, NUM_THREADS, smem, stream>>>(ma, mb, y, yf, bias, bf, M, N, K, I, m_blocks, num_tiles, err);
   return osb_last_error();
+}
+
+// Time of a shape in units of "one 128-column tile on one SM": full waves over the SMs.
+static inline long long wave_cost(int M, int out_cols, int cols_per_tile, int width) {
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((out_cols + cols_per_tile - 1) / cols_per_tile);
+  const long long waves = (tiles + sm_count() - 1) / sm_count();
+  return waves * width;
 }
 }  // namespace
 
@@ -350,12 +414,31 @@ OSB_API int osb_gemm_tcgen05_bf16(void* y, int y_dtype, const void* x, const voi
   if (rc) return rc;
   if (mode == 1) {
     if ((N & 1) || bias || yf) return OSB_ERR_BAD_SHAPE;
+    const int I = N / 2;
+    // 256-wide B tiles (128 features) unless 128-wide ones fill the SMs better
+    if (wave_cost(M, I, 128, 2) <= wave_cost(M, I, 64, 1)) {  // cost in units of 128 B-tile rows
+      rc = make_map(&mb, w, N, K, 128);
+      if (rc) return rc;
+      return launch<256, 4, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, I, err, stream);
+    }
     rc = make_map(&mb, w, N, K, 64);
     if (rc) return rc;
-    return launch<128, 4, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, N / 2, err, stream);
+    return launch<128, 6, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, I, err, stream);
   }
   if (mode != 0) return OSB_ERR_BAD_SHAPE;
+  // tile width: the one whose full waves over the SMs cost least; wider wins ties (less operand traffic)
+  const long long c256 = wave_cost(M, N, 256, 256), c192 = wave_cost(M, N, 192, 192), c128 = wave_cost(M, N, 128, 128);
+  if (c256 <= c192 && c256 <= c128) {
+    rc = make_map(&mb, w, N, K, 256);
+    if (rc) return rc;
+    return launch<256, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
+  }
+  if (c192 <= c128) {
+    rc = make_map(&mb, w, N, K, 192);
+    if (rc) return rc;
+    return launch<192, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
+  }
   rc = make_map(&mb, w, N, K, 128);
   if (rc) return rc;
-  return launch<128, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
+  return launch<128, 6, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
 }

@@ -42,6 +42,7 @@ _DEVICE_ERR = {
     101: "tcgen05 GEMM: the TMA producer waited too long for a free stage",
     102: "tcgen05 GEMM: the MMA issuer waited too long for operands",
     103: "tcgen05 GEMM: the epilogue waited too long for the accumulator",
+    104: "tcgen05 GEMM: the MMA issuer waited too long for a drained accumulator",
 }
 
 
