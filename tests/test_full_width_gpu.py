@@ -1,0 +1,109 @@
+"""The engine at the layer sizes of Qwen2-VL-2B (hidden 1536, 12 heads in 2 groups, head size 128,
+intermediate 8960, vocabulary 151936, tied head) with two layers and random weights: logits of
+whole prompts, of portions and of mixed batches against the plain implementation, in 32-bit (where
+they must also be bitwise independent of the cut) and in bfloat16 (tensor-core kernels at their
+real shapes: tcgen05 GEMM, paged prefill attention, split-key decode attention, skinny GEMM)."""
+
+import pytest
+import torch
+
+import replay_cases as rc
+from plain import model as pm
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["Qwen2VLForConditionalGeneration"], "hidden_size": 1536, "num_hidden_layers": 2,
+    "num_attention_heads": 12, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 8960,
+    "vocab_size": 151936, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "rope_scaling": {"type": "mrope", "mrope_section": [16, 24, 24]}, "tie_word_embeddings": True,
+}
+
+
+def build(dtype, max_tokens):
+    from omniserver_b200 import EngineConfig, build_runner
+    ec = EngineConfig(dtype=dtype, max_cache_tokens=max_tokens, max_requests=8)
+    r = build_runner(config=CONFIG, seed=2, engine_config=ec, init_std=0.03, norm_noise=0.1)
+    r.cache.poison_freed = True
+    return r
+
+
+def plain_weights(model):
+    f = lambda t: t.detach().float().cpu()
+    w = {"embed_tokens.weight": f(model.embed.weight), "norm.weight": f(model.final_norm.weight)}
+    nq, nkv = 12 * 128, 2 * 128
+    for i, blk in enumerate(model.blocks):
+        p = f"layers.{i}."
+        qkv_w, qkv_b = f(blk.mixer.qkv.weight), f(blk.mixer.qkv.bias)
+        w[p + "self_attn.q_proj.weight"], w[p + "self_attn.k_proj.weight"], w[p + "self_attn.v_proj.weight"] = \
+            qkv_w[:nq], qkv_w[nq:nq + nkv], qkv_w[nq + nkv:]
+        w[p + "self_attn.q_proj.bias"], w[p + "self_attn.k_proj.bias"], w[p + "self_attn.v_proj.bias"] = \
+            qkv_b[:nq], qkv_b[nq:nq + nkv], qkv_b[nq + nkv:]
+        w[p + "self_attn.o_proj.weight"] = f(blk.mixer.out.weight)
+        gu = f(blk.ffn.gate_up.weight)
+        w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"] = gu[:8960], gu[8960:]
+        w[p + "mlp.down_proj.weight"] = f(blk.ffn.down.weight)
+        w[p + "input_layernorm.weight"] = f(blk.mixer_norm.weight)
+        w[p + "post_attention_layernorm.weight"] = f(blk.ffn_norm.weight)
+    return w
+
+
+def replay(runner, steps):
+    from omniserver_b200.replay import TraceReplayer
+    rp, outs = TraceReplayer(runner), {}
+    with torch.inference_mode():
+        for st in steps:
+            lg = rp.run_step(st)
+            if lg is not None:
+                outs[st["step"]] = lg.float().cpu()
+    return outs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_width_logits_match_plain_for_every_cut(dtype):
+    g = torch.Generator().manual_seed(4)
+    reqs = {f"r{i}": torch.randint(0, CONFIG["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate((150, 40, 97))}
+    # logits only at a few places per request: [wanted, 151936] rows are large
+    def thin(steps):
+        for st in steps:
+            for e in st["entries"]:
+                e["want"] = [w for w in e["want"] if w == len(e["tokens"]) - 1]
+        return steps
+    runner = build(dtype, 512)
+    cfg = pm.PlainConfig(CONFIG)
+    w = plain_weights(runner.model)
+    want = {r: pm.forward(cfg, w, torch.tensor(t)) for r, t in reqs.items()}
+    base = None
+    for family in (rc.whole, rc.portions, rc.mixed, rc.tail_decode):
+        steps = thin(family(reqs))
+        outs = replay(runner, steps)
+        got = {}
+        for st in steps:
+            o = 0
+            pos = got.setdefault("_pos", {})
+            for e in st["entries"]:
+                pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
+                if e["want"]:
+                    got.setdefault(e["id"], {})[pos[e["id"]] - 1] = outs[st["step"]][o]
+                    o += 1
+            for rid in st["end"]:
+                pos.pop(rid, None)
+        got.pop("_pos")
+        for rid, rows in got.items():
+            for p, lg in rows.items():
+                ref = want[rid][p]
+                err = (lg - ref).abs().max().item()
+                scale = ref.abs().max().item()
+                if dtype == "float32":
+                    assert err < 2e-4 * max(1.0, scale), f"{family.__name__}/{rid}@{p}: {err}"
+                else:
+                    assert err < 5e-2 * max(1.0, scale), f"{family.__name__}/{rid}@{p}: {err}"
+                    assert ((lg - ref).norm() / ref.norm()).item() < 3e-2
+        if dtype == "float32":
+            if base is None:
+                base = got
+            else:
+                for rid, rows in got.items():
+                    for p, lg in rows.items():
+                        if p in base.get(rid, {}):
+                            assert torch.equal(lg, base[rid][p]), f"{family.__name__}/{rid}@{p} differs bitwise from whole"
