@@ -255,6 +255,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   bf16* kvs = qs + 16 * stride;                  // STAGES x (K, V) x [TILE_N][stride]; later the warps' outputs
   const int tile_elems = TILE_N * stride;
 
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, s = blockIdx.z;
   const int g = nh / nkv;
@@ -398,6 +399,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   }
   cp_async_wait<0>();
   __syncthreads();
+  pdl_trigger();
 
   // merge the four warps (each saw different keys) in warp order
   float* wml = reinterpret_cast<float*>(qs);   // [4][16][2]
@@ -533,10 +535,10 @@ int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q
   if (e != cudaSuccess) return (int)e;
   const int g = nh / nkv;
   const dim3 grid(nsplits, nkv * ((g + 15) / 16), S);
-  k<<<grid, NTHREADS, smem, stream>>>(out, part_o, part_ml, q, q_row_stride, kc, vc, bt, bt_stride, cu_q, seq_lens,
-                                      decode_index, counters, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                      nsplits);
-  return osb_last_error();
+  const int rc = osb_launch(k, grid, dim3(NTHREADS), smem, stream, out, part_o, part_ml, q, q_row_stride, kc, vc, bt,
+                            bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, hd, log2ps, num_pages, scale_log2,
+                            window, chunk, nsplits);
+  return rc ? rc : osb_last_error();
 }
 }  // namespace
 

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #define OSB_API extern "C" __attribute__((visibility("default")))
 
 // dtype codes used across the C interface
@@ -67,6 +69,34 @@ __device__ __forceinline__ float block_max(float v, float* smem32) {
 }
 
 static inline int osb_last_error() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch: a kernel launched through osb_launch may start while the kernel
+// before it in the stream is finishing; it must call pdl_wait() before it reads or writes anything
+// the earlier kernel touches (until then only its own set-up runs), and calls pdl_trigger() when the
+// kernel after it may begin to launch. Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& osb_pdl_enabled() {
+  static int v = 1;
+  return v;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int osb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = osb_pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // Dispatch over the two storage types: f(Tag<T>{}) is called with T = float or bf16.
 template <typename T> struct Tag { typedef T type; };

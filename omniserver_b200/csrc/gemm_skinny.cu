@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
   constexpr bool PFX = NT <= 2;  // activations of the next group fit in registers too
   uint4 cur_lo[PF][2], cur_hi[PF][2], nxt_lo[PF][2], nxt_hi[PF][2];
   uint4 cur_x[PFX ? PF : 1][2][PFX ? NT : 1], nxt_x[PFX ? PF : 1][2][PFX ? NT : 1];
-  auto load_group = [&](int b0, uint4 (&lo)[PF][2], uint4 (&hi)[PF][2], uint4 (&xs)[PFX ? PF : 1][2][PFX ? NT : 1]) {
+  auto load_w = [&](int b0, uint4 (&lo)[PF][2], uint4 (&hi)[PF][2]) {
 #pragma unroll
     for (int u = 0; u < PF; ++u) {
 #pragma unroll
@@ -71,18 +71,35 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
         const bool ok = (b0 + u) < b_end && k < K;
         lo[u][hf] = (ok && row_a >= 0) ? ld_stream16(wa + k) : zero4;
         hi[u][hf] = (ok && row_b >= 0) ? ld_stream16(wb + k) : zero4;
-        if (PFX) {
+      }
+    }
+  };
+  auto load_x = [&](int b0, uint4 (&xs)[PFX ? PF : 1][2][PFX ? NT : 1]) {
+    if (!PFX) return;
 #pragma unroll
-          for (int j = 0; j < NT; ++j) {
-            const int tok = j * 8 + g;
-            xs[PFX ? u : 0][hf][PFX ? j : 0] =
-                (ok && tok < M) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k) : zero4;
-          }
+    for (int u = 0; u < PF; ++u) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int k = (b0 + u) * 64 + c * 8 + hf * 32;
+        const bool ok = (b0 + u) < b_end && k < K;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const int tok = j * 8 + g;
+          xs[PFX ? u : 0][hf][PFX ? j : 0] =
+              (ok && tok < M) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k) : zero4;
         }
       }
     }
   };
-  load_group(b_begin, cur_lo, cur_hi, cur_x);
+  auto load_group = [&](int b0, uint4 (&lo)[PF][2], uint4 (&hi)[PF][2], uint4 (&xs)[PFX ? PF : 1][2][PFX ? NT : 1]) {
+    load_w(b0, lo, hi);
+    load_x(b0, xs);
+  };
+  // The weights do not depend on the kernel before this one: their first loads are already in
+  // flight while that kernel finishes; the activations are read only after it has completed.
+  load_w(b_begin, cur_lo, cur_hi);
+  pdl_wait();
+  load_x(b_begin, cur_x);
   for (int b = b_begin; b < b_end; b += PF) {
     load_group(b + PF, nxt_lo, nxt_hi, nxt_x);
 #pragma unroll
@@ -123,6 +140,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
     }
   }
 
+  pdl_trigger();
   // partial tiles -> shared memory: red[warp][token][row]
   float* mine = red + (size_t)warp * (NT * 8 * 16);
 #pragma unroll
@@ -177,8 +195,9 @@ int launch(void* y, int y_is_f32, const bf16* x, const bf16* w, const void* bias
     if (e != cudaSuccess) return (int)e;
   }
   const int ctas = mode == 1 ? (I + 7) / 8 : (N + 15) / 16;
-  k<<<ctas, WARPS * 32, smem, stream>>>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I);
-  return osb_last_error();
+  const int rc = osb_launch(k, dim3(ctas), dim3(WARPS * 32), smem, stream, y, y_is_f32, x, w, bias, bias_is_f32, M, N, K,
+                            mode, I);
+  return rc ? rc : osb_last_error();
 }
 
 template <int WARPS>

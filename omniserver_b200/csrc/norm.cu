@@ -69,6 +69,7 @@ __global__ void add_rmsnorm_vec_kernel(OT* __restrict__ y, float* res_out, const
                                        const XT* __restrict__ x, const WT* __restrict__ w, float eps, int H,
                                        const int* __restrict__ rows) {
   __shared__ float red[32];
+  pdl_wait();
   const int orow = blockIdx.x;
   const int irow = rows ? rows[orow] : orow;
   const XT* xr = x + (size_t)irow * H;
@@ -91,6 +92,7 @@ __global__ void add_rmsnorm_vec_kernel(OT* __restrict__ y, float* res_out, const
     }
   }
   ss = block_sum(ss, red);
+  pdl_trigger();
   const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
   float* ro = res_out ? res_out + (size_t)irow * H : nullptr;
   OT* yr = y + (size_t)orow * H;
@@ -130,11 +132,12 @@ OSB_API int osb_add_rmsnorm(void* y, int y_dtype, float* res_out, const float* r
           OT* yy = (OT*)y;
           const XT* xx = (const XT*)x;
           const WT* ww = (const WT*)w;
-          if (ch == 1) add_rmsnorm_vec_kernel<XT, WT, OT, 1><<<R, vthreads, 0, stream>>>(yy, res_out, res_in, xx, ww, eps, H, rows);
-          else if (ch == 2) add_rmsnorm_vec_kernel<XT, WT, OT, 2><<<R, vthreads, 0, stream>>>(yy, res_out, res_in, xx, ww, eps, H, rows);
-          else if (ch == 4) add_rmsnorm_vec_kernel<XT, WT, OT, 4><<<R, vthreads, 0, stream>>>(yy, res_out, res_in, xx, ww, eps, H, rows);
-          else add_rmsnorm_vec_kernel<XT, WT, OT, 8><<<R, vthreads, 0, stream>>>(yy, res_out, res_in, xx, ww, eps, H, rows);
-          return osb_last_error();
+          int rc = 0;
+          if (ch == 1) rc = osb_launch(add_rmsnorm_vec_kernel<XT, WT, OT, 1>, dim3(R), dim3(vthreads), 0, stream, yy, res_out, (const float*)res_in, xx, ww, eps, H, rows);
+          else if (ch == 2) rc = osb_launch(add_rmsnorm_vec_kernel<XT, WT, OT, 2>, dim3(R), dim3(vthreads), 0, stream, yy, res_out, (const float*)res_in, xx, ww, eps, H, rows);
+          else if (ch == 4) rc = osb_launch(add_rmsnorm_vec_kernel<XT, WT, OT, 4>, dim3(R), dim3(vthreads), 0, stream, yy, res_out, (const float*)res_in, xx, ww, eps, H, rows);
+          else rc = osb_launch(add_rmsnorm_vec_kernel<XT, WT, OT, 8>, dim3(R), dim3(vthreads), 0, stream, yy, res_out, (const float*)res_in, xx, ww, eps, H, rows);
+          return rc ? rc : osb_last_error();
         });
       });
     });

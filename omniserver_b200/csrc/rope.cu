@@ -67,6 +67,8 @@ __global__ void rope_kv_write_kernel(XT* __restrict__ qkv, const float* __restri
                                      const float* __restrict__ sin_t, CT* __restrict__ k_cache,
                                      CT* __restrict__ v_cache, const int* __restrict__ slot_map, int nh, int nkv,
                                      int hd, int rot, int page_size, int num_slots, int* __restrict__ err) {
+  pdl_wait();
+  pdl_trigger();  // a tiny kernel: the next one may begin to launch at once
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // [0,nh) q, [nh,nh+nkv) k, [nh+nkv, nh+2nkv) v
   const int row_stride = (nh + 2 * nkv) * hd;
@@ -122,10 +124,9 @@ OSB_API int osb_rope_kv_write(void* qkv, int x_dtype, const float* cos_t, const 
     typedef OSB_T(xt) XT;
     return osb_dispatch(cache_dtype, [&](auto ct) {
       typedef OSB_T(ct) CT;
-      rope_kv_write_kernel<XT, CT><<<grid, threads, 0, stream>>>((XT*)qkv, cos_t, sin_t, (CT*)k_cache, (CT*)v_cache,
-                                                               slot_map, nh, nkv, hd, rot, page_size, num_slots,
-                                                               err);
-      return osb_last_error();
+      const int rc = osb_launch(rope_kv_write_kernel<XT, CT>, grid, dim3(threads), 0, stream, (XT*)qkv, cos_t, sin_t,
+                                (CT*)k_cache, (CT*)v_cache, slot_map, nh, nkv, hd, rot, page_size, num_slots, err);
+      return rc ? rc : osb_last_error();
     });
   });
 }
