@@ -239,6 +239,17 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_kernel(
   }
 }
 
+// Optional fusion of the rotary encoding and the cache write into the decode kernel: the query
+// rows are rotated in shared memory, and the CTA whose split holds the new token's position rotates
+// that token's key and stores key and value into their page before it loads its tiles. Only for
+// groups of at most 16 query heads (one CTA per request and kv head reads the new key).
+struct FusedRope {
+  const float* cos_t;   // [T, rot/2]; null: no fusion (q already rotated, cache already written)
+  const float* sin_t;
+  const int* slot_map;  // [T] flat cache slot of every token
+  int rot;
+};
+
 // ------------------------------------------------------------------------------------------------
 // Decode: one token per request. grid = (splits, kv heads x head tiles, requests).
 template <int HD_MAX, int STAGES>
@@ -247,7 +258,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
     const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int hd, int log2ps,
-    int num_pages, float scale_log2, int window, int chunk, int nsplits) {
+    int num_pages, float scale_log2, int window, int chunk, int nsplits, FusedRope fr) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_last;
   const int stride = hd + 8;
@@ -274,6 +285,31 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   const int k_end = min((split + 1) * chunk, kv_len);
   const int ntiles = (k_end - k_begin + TILE_N - 1) / TILE_N;
   const int* bt = block_table + (size_t)s * bt_stride;
+
+  if (fr.cos_t != nullptr && split == last_split && ht == 0) {
+    // the new token's key (rotated) and value go into their page before this CTA reads its tiles
+    const int slot = fr.slot_map[q0];
+    const int page = slot >> log2ps, off = slot & ((1 << log2ps) - 1);
+    if (page >= 0 && page < num_pages) {
+      const size_t dst = ((((size_t)page * nkv + kvh) << log2ps) + off) * hd;
+      bf16* kd = const_cast<bf16*>(kc) + dst;
+      bf16* vd = const_cast<bf16*>(vc) + dst;
+      const bf16* ksrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + kvh) * hd;
+      const bf16* vsrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + nkv + kvh) * hd;
+      const int half = fr.rot >> 1;
+      const float* cs = fr.cos_t + (size_t)q0 * half;
+      const float* sn = fr.sin_t + (size_t)q0 * half;
+      for (int d = tid; d < half; d += NTHREADS) {
+        const float x1 = __bfloat162float(ksrc[d]), x2 = __bfloat162float(ksrc[d + half]);
+        kd[d] = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]);
+        kd[d + half] = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
+      }
+      for (int d = fr.rot + tid; d < hd; d += NTHREADS) kd[d] = ksrc[d];
+      for (int d = tid; d < hd; d += NTHREADS) vd[d] = vsrc[d];
+    }
+    __threadfence();
+    __syncthreads();
+  }
 
   {  // the group's query rows
     const int cpr = hd >> 3;
@@ -318,6 +354,19 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     const bf16* ks = kvs + st * 2 * tile_elems;
     const bf16* vs = ks + tile_elems;
     if (t == 0) {
+      if (fr.cos_t != nullptr) {  // rotate the query rows in place in shared memory
+        const int half = fr.rot >> 1;
+        const float* cs = fr.cos_t + (size_t)q0 * half;
+        const float* sn = fr.sin_t + (size_t)q0 * half;
+        for (int i = tid; i < rows * half; i += NTHREADS) {
+          const int r = i / half, d = i - r * half;
+          bf16* row = qs + r * stride;
+          const float x1 = __bfloat162float(row[d]), x2 = __bfloat162float(row[d + half]);
+          row[d] = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]);
+          row[d + half] = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
+        }
+        __syncthreads();
+      }
 #pragma unroll
       for (int k = 0; k < KS; ++k)
         if (k < ks_n)
@@ -528,7 +577,8 @@ template <int HD_MAX, int STAGES>
 int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_stride, const bf16* kc,
                   const bf16* vc, const int* bt, int bt_stride, const int* cu_q, const int* seq_lens,
                   const int* decode_index, int* counters, int S, int nh, int nkv, int hd, int log2ps, int num_pages,
-                  float scale_log2, int window, int chunk, int nsplits, cudaStream_t stream) {
+                  float scale_log2, int window, int chunk, int nsplits, cudaStream_t stream,
+                  FusedRope fr = FusedRope{nullptr, nullptr, nullptr, 0}) {
   const size_t smem = (size_t)(16 + STAGES * 2 * TILE_N) * (hd + 8) * sizeof(bf16);
   auto k = attn_decode_kernel<HD_MAX, STAGES>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -537,7 +587,7 @@ int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q
   const dim3 grid(nsplits, nkv * ((g + 15) / 16), S);
   const int rc = osb_launch(k, grid, dim3(NTHREADS), smem, stream, out, part_o, part_ml, q, q_row_stride, kc, vc, bt,
                             bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, hd, log2ps, num_pages, scale_log2,
-                            window, chunk, nsplits);
+                            window, chunk, nsplits, fr);
   return rc ? rc : osb_last_error();
 }
 }  // namespace
@@ -565,7 +615,9 @@ static int g_decode_stages = 3;  // the merging CTA keeps (max, sum) of 16 rows 
 // n_decode > 0 (decode_index[s] = index among them; part_o/part_ml/counters sized by
 // osb_attn_decode_scratch, counters all zero before the first use (the kernel leaves them zero);
 // chunk a multiple of 64, nsplits = ceil(max_kv_len / chunk) <= 128); all others (and all, when
-// n_decode == 0) through the prefill kernel.
+// n_decode == 0) through the prefill kernel. rope_cos/rope_sin [T, rope_rot/2] and rope_slot_map [T],
+// when given, make the decode kernel rotate q and k itself and store the new key and value (the
+// caller then skips the separate rotary/cache-write kernel); allowed only when n_multi == 0.
 // Pipeline depth of the decode kernel for head sizes up to 128 (2 or 3 tiles in flight per CTA).
 OSB_API void osb_attn_set_decode_stages(int stages) { g_decode_stages = stages == 2 ? 2 : 3; }
 
@@ -573,7 +625,8 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
                                 const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
                                 const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
                                 float scale, int window, int max_q_len, int n_decode, int n_multi, float* part_o,
-                                float* part_ml, int* counters, int chunk, int nsplits, cudaStream_t stream) {
+                                float* part_ml, int* counters, int chunk, int nsplits, const float* rope_cos,
+                                const float* rope_sin, const int* rope_slot_map, int rope_rot, cudaStream_t stream) {
   if (S <= 0) return OSB_OK;
   if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
   const int log2ps = page_log2(page_size);
@@ -582,6 +635,13 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
     return OSB_ERR_BAD_SHAPE;
   if (n_decode > 0 && nsplits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr))
     return OSB_ERR_BAD_SHAPE;
+  FusedRope fr{rope_cos, rope_sin, rope_slot_map, rope_rot};
+  if (rope_cos != nullptr) {
+    // the fused form covers steps of single-token requests only, with groups of at most 16 heads
+    if (n_multi > 0 || nh / nkv > 16 || rope_sin == nullptr || rope_slot_map == nullptr || rope_rot <= 0 ||
+        rope_rot > hd || (rope_rot & 1))
+      return OSB_ERR_UNSUPPORTED;
+  }
   const float scale_log2 = scale * LOG2E;
   bf16* o = (bf16*)out;
   const bf16 *qq = (const bf16*)q, *kc = (const bf16*)k_cache, *vc = (const bf16*)v_cache;
@@ -603,19 +663,19 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
     if (hd <= 64)
       rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                nsplits, stream);
+                                nsplits, stream, fr);
     else if (hd <= 128 && g_decode_stages == 2)
       rc = launch_decode<128, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                 nsplits, stream);
+                                 nsplits, stream, fr);
     else if (hd <= 128)
       rc = launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                 nsplits, stream);
+                                 nsplits, stream, fr);
     else
       rc = launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                 nsplits, stream);
+                                 nsplits, stream, fr);
   }
   return rc;
 }

@@ -325,13 +325,18 @@ class CudaKernels:
                         nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
                         max_q_len: int, max_kv_len: int, out_dtype: torch.dtype,
                         decode_index: Optional[torch.Tensor] = None, n_decode: int = 0, n_multi: int = 0,
-                        exact: bool = False, scratch: Optional[dict] = None) -> torch.Tensor:
+                        exact: bool = False, scratch: Optional[dict] = None,
+                        rope: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None) -> torch.Tensor:
         """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache.
 
         bfloat16 operands run on the tensor cores (one kernel for requests bringing several tokens,
         a split-key kernel for requests bringing one: ``decode_index`` [S] numbers those, -1 for the
         others). float32 operands, ``exact=True`` and head sizes that are no multiple of 16 run
         through the kernel whose sums have a fixed order.
+
+        ``rope`` = (cos, sin, slot_map, rot_dim): only for steps of single-token requests for which
+        ``can_fuse_rope_decode`` holds; the decode kernel then rotates q and k itself and stores the new
+        key and value, and the caller must not have called ``rope_kv_write``.
         """
         _cuda_contig("qkv", qkv)
         _cuda_contig("k_cache", k_cache)
@@ -347,6 +352,8 @@ class CudaKernels:
         _check(nh % nkv == 0, "paged_attention: heads must be a multiple of kv heads")
         out = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
         win = int(window) if window else 0
+        _check(rope is None or self.can_fuse_rope_decode(qkv, k_cache, nh, nkv, hd, n_decode, n_multi, exact),
+               "paged_attention: this step cannot fuse the rotary encoding into the decode kernel")
         fast = (not exact and qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
                 and out_dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and decode_index is not None
                 and k_cache.shape[2] >= 2 and (k_cache.shape[2] & (k_cache.shape[2] - 1)) == 0)
@@ -366,7 +373,8 @@ class CudaKernels:
                 _p(out), _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
                 _p(cu_q), _p(seq_lens), _p(decode_index), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
                 ctypes.c_float(scale), win, max_q_len, n_decode, n_multi, _p(part_o), _p(part_ml), _p(counters), chunk,
-                nsplits, self._stream())
+                nsplits, _p(rope[0] if rope else None), _p(rope[1] if rope else None),
+                _p(rope[2] if rope else None), int(rope[3]) if rope else 0, self._stream())
             self._ok(rc, "paged_attn_bf16")
             self.launches += (1 if n_multi > 0 or n_decode == 0 else 0) + (1 if n_decode > 0 else 0) - 1
             return out
@@ -377,6 +385,16 @@ class CudaKernels:
             self._stream())
         self._ok(rc, "paged_attn_generic")
         return out
+
+    @staticmethod
+    def can_fuse_rope_decode(qkv: torch.Tensor, k_cache: torch.Tensor, nh: int, nkv: int, hd: int, n_decode: int,
+                             n_multi: int, exact: bool = False) -> bool:
+        """Whether a step's attention may take the rotary encoding and the cache write into the
+        decode kernel: every request brings one token, bf16 tensor-core path, groups of at most 16 heads."""
+        ps = k_cache.shape[2]
+        return (not exact and n_multi == 0 and n_decode > 0 and qkv.dtype == torch.bfloat16
+                and k_cache.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and nh // nkv <= 16
+                and ps >= 2 and (ps & (ps - 1)) == 0)
 
     @staticmethod
     def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 296):

@@ -48,13 +48,20 @@ class GQAAttention(Mixer):
         qkv = self.qkv(x, ctx.act_dtype)
         tables = ctx.position_tables(self.position) if self.position is not None else None
         g = binding.group
-        k.rope_kv_write(qkv, tables.cos if tables else None, tables.sin if tables else None,
-                        binding.k_cache, binding.v_cache, ctx.slot_maps[g] if binding.writes else None,
-                        self.nh, self.nkv, self.hd, tables.rot_dim if tables else 0)
+        rot = tables.rot_dim if tables else 0
+        # A step of single-token requests lets the decode attention kernel rotate q and k and store
+        # the new key and value itself; otherwise a kernel of its own does that for all tokens first.
+        fuse = (rot > 0 and binding.writes and ctx.decode_index is not None
+                and k.can_fuse_rope_decode(qkv, binding.k_cache, self.nh, self.nkv, self.hd, ctx.n_decode, ctx.n_multi))
+        if not fuse:
+            k.rope_kv_write(qkv, tables.cos if tables else None, tables.sin if tables else None,
+                            binding.k_cache, binding.v_cache, ctx.slot_maps[g] if binding.writes else None,
+                            self.nh, self.nkv, self.hd, rot)
         a = k.paged_attention(qkv, binding.k_cache, binding.v_cache, ctx.block_tables[g], ctx.cu_q, ctx.seq_lens,
                               ctx.tok_seq, self.nh, self.nkv, self.hd, self.scale, self.window,
                               ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype, decode_index=ctx.decode_index,
-                              n_decode=ctx.n_decode, n_multi=ctx.n_multi, scratch=ctx.scratch)
+                              n_decode=ctx.n_decode, n_multi=ctx.n_multi, scratch=ctx.scratch,
+                              rope=(tables.cos, tables.sin, ctx.slot_maps[g], rot) if fuse else None)
         return self.out(a, ctx.act_dtype)
 
 

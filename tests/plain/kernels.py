@@ -91,10 +91,14 @@ class PlainKernels:
         k_cache[page, :, off, :] = qk[:, nh:].to(k_cache.dtype)
         v_cache[page, :, off, :] = x[:, nh + nkv:, :].to(v_cache.dtype)
 
+    @staticmethod
+    def can_fuse_rope_decode(*args, **kw):
+        return False
+
     # -- attention
     def paged_attention(self, qkv, k_cache, v_cache, block_table, cu_q, seq_lens, tok_seq, nh, nkv, hd, scale,
                         window, max_q_len, max_kv_len, out_dtype, decode_index=None, n_decode=0, n_multi=0, exact=False,
-                        scratch=None):
+                        scratch=None, rope=None):
         T = qkv.shape[0]
         ps = k_cache.shape[2]
         g = nh // nkv

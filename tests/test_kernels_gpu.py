@@ -308,6 +308,30 @@ def test_decode_attention_long_contexts_split_keys(nh, nkv, hd, ps, window):
     assert torch.allclose(got, want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,rot", [(12, 2, 128, 16, 128), (6, 3, 48, 8, 48), (16, 1, 64, 16, 32)])
+def test_decode_attention_with_fused_rotary_and_cache_write(nh, nkv, hd, ps, rot):
+    """The decode kernel rotating q and k and storing the new key/value itself must give what the
+    rotary kernel followed by the plain decode kernel gives, and leave the same cache behind."""
+    kv_lens = [2048, 1, 777, 64, 65, 129]
+    S = len(kv_lens)
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = [t.to(DEV) for t in _paged_case([1] * S, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=5)]
+    ang = rnd(S, rot // 2, seed=3, scale=3.0)
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    slot_map = torch.stack([bt[s, (kv - 1) // ps] * ps + (kv - 1) % ps for s, kv in enumerate(kv_lens)]).to(torch.int32)
+    didx = torch.arange(S, dtype=torch.int32, device=DEV)
+    args = dict(decode_index=didx, n_decode=S, n_multi=0)
+    q1, k1, v1 = qkv.clone(), kc.clone(), vc.clone()
+    K().rope_kv_write(q1, cos, sin, k1, v1, slot_map, nh, nkv, hd, rot)
+    want = K().paged_attention(q1, k1, v1, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens),
+                               torch.bfloat16, **args)
+    q2, k2, v2 = qkv.clone(), kc.clone(), vc.clone()
+    got = K().paged_attention(q2, k2, v2, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens),
+                              torch.bfloat16, rope=(cos, sin, slot_map, rot), **args)
+    K().check_device_errors()
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    assert torch.equal(got, want)
+
+
 @pytest.mark.parametrize("window", [None, 100])
 def test_decode_attention_finds_one_key_that_matters(window):
     """As below, for the split-key decode kernel: one key dominates, placed at tile, split and window edges."""
