@@ -39,13 +39,58 @@ class PageGroup:
         return self.need.window
 
 
+class PageTable:
+    """A request's page ids in one group (-1 = given back), kept as a growing int32 array so that a
+    step's block table is a row copy instead of a walk over Python lists."""
+
+    __slots__ = ("_a", "_n")
+
+    def __init__(self) -> None:
+        self._a = np.full(16, -1, dtype=np.int32)
+        self._n = 0
+
+    def __len__(self) -> int:
+        return self._n
+
+    def append(self, page: int) -> None:
+        if self._n == self._a.shape[0]:
+            grown = np.full(2 * self._n, -1, dtype=np.int32)
+            grown[:self._n] = self._a
+            self._a = grown
+        self._a[self._n] = page
+        self._n += 1
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return self._a[:self._n][i].tolist()
+        if i < 0:
+            i += self._n
+        if not (0 <= i < self._n):
+            raise IndexError(i)
+        return int(self._a[i])
+
+    def __setitem__(self, i: int, v: int) -> None:
+        if not (0 <= i < self._n):
+            raise IndexError(i)
+        self._a[i] = v
+
+    def __iter__(self):
+        return iter(self._a[:self._n].tolist())
+
+    def __eq__(self, other) -> bool:
+        return list(self) == list(other)
+
+    def array(self) -> np.ndarray:
+        return self._a[:self._n]
+
+
 @dataclass
 class RequestCache:
     request_id: str
     slot: int
     cursor: int = 0                          # tokens of the request in the cache
     reserved: int = 0                        # tokens reserved for the running step
-    tables: List[List[int]] = field(default_factory=list)   # per group: page id per page index, -1 = given back
+    tables: List[PageTable] = field(default_factory=list)   # per group: page id per page index, -1 = given back
     first_live: List[int] = field(default_factory=list)     # per group: first page index still held
 
 
@@ -97,6 +142,7 @@ class CacheManager:
                 g.storage = torch.zeros((len(g.entries), 2, self.num_pages, g.need.num_kv_heads, self.page_size,
                                          g.need.head_dim), dtype=dtype, device=device)
         self.requests: Dict[str, RequestCache] = {}
+        self._no_pages = [0] * len(self.groups)
 
     # ------------------------------------------------------------------ wiring
     def bindings(self) -> List[CacheBinding]:
@@ -124,7 +170,8 @@ class CacheManager:
         if request_id in self.requests:
             raise ValueError(f"request {request_id!r} is already live")
         slot = self.state.alloc()
-        rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups], first_live=[0 for _ in self.groups])
+        rc = RequestCache(request_id, slot, tables=[PageTable() for _ in self.groups],
+                          first_live=[0 for _ in self.groups])
         self.requests[request_id] = rc
         return rc
 
@@ -142,6 +189,8 @@ class CacheManager:
         """New pages per group that ``n_new`` more tokens of this request need."""
         rc = self.requests[request_id]
         end = rc.cursor + rc.reserved + n_new
+        if n_new == 1 and (end - 1) % self.page_size != 0 and all(len(t) * self.page_size >= end for t in rc.tables):
+            return self._no_pages       # a decoded token inside a page the request already holds
         need = []
         for gi, g in enumerate(self.groups):
             have = len(rc.tables[gi])
@@ -215,7 +264,7 @@ class CacheManager:
         for gi, g in enumerate(self.groups):
             for p in rc.tables[gi]:
                 self._release(g, p)
-            rc.tables[gi] = []
+            rc.tables[gi] = PageTable()
             rc.first_live[gi] = 0
         rc.cursor = 0
         rc.reserved = 0
@@ -228,8 +277,8 @@ class CacheManager:
         width = -(-width // round_to) * round_to
         bt = np.full((len(request_ids), width), -1, dtype=np.int32)
         for i, r in enumerate(request_ids):
-            t = self.requests[r].tables[group]
-            bt[i, :len(t)] = t
+            t = self.requests[r].tables[group].array()
+            bt[i, :t.shape[0]] = t
         return bt
 
     def slot_map(self, group: int, request_ids: Sequence[str], q_lens: Sequence[int]) -> np.ndarray:
@@ -239,8 +288,15 @@ class CacheManager:
         ps = self.page_size
         for r, n in zip(request_ids, q_lens):
             rc = self.requests[r]
+            if n == 1:
+                page = rc.tables[group][rc.cursor // ps]
+                if page < 0:
+                    raise RuntimeError(f"request {r!r}: a token of this step maps to a page that was given back")
+                out[o] = page * ps + rc.cursor % ps
+                o += 1
+                continue
             pos = np.arange(rc.cursor, rc.cursor + n)
-            pages = np.asarray(rc.tables[group], dtype=np.int64)[pos // ps]
+            pages = rc.tables[group].array().astype(np.int64)[pos // ps]
             if (pages < 0).any():
                 raise RuntimeError(f"request {r!r}: a token of this step maps to a page that was given back")
             out[o:o + n] = pages * ps + pos % ps

@@ -198,6 +198,54 @@ class ModelRunner:
                     n_logit_rows=len(logit_rows), ov_vals=ov_vals, n_decode=int(single.sum()),
                     explicit_positions=bool((pos_mode == 0).any()))
 
+    def _plan_decode(self, entries: Sequence[StepEntry], bt_round: int) -> Dict[str, Any]:
+        """``_plan`` for a step in which every request brings one token and wants its logits: the same
+        result, built with array operations instead of a loop over entries."""
+        cache = self.cache
+        ps = cache.page_size
+        S = len(entries)
+        rids = [e.request_id for e in entries]
+        if len(set(rids)) != S:
+            raise ValueError("a request may appear once in a step")
+        try:
+            rcs = [cache.requests[r] for r in rids]
+        except KeyError as k:
+            raise KeyError(f"request {k.args[0]!r} was not started") from None
+        token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+        if token_ids.min() < 0 or token_ids.max() >= self.vocab_size:
+            raise ValueError(f"token id outside [0, {self.vocab_size})")
+        boundary = [rc for rc in rcs if (rc.cursor + rc.reserved) % ps == 0]
+        if boundary and len(boundary) > min(cache.free_pages(), default=len(boundary)):
+            from ..cache.page_pool import OutOfPages
+            raise OutOfPages(f"the step needs more pages than are free ({cache.free_pages()} free)")
+        for rc in rcs:
+            if (rc.cursor + rc.reserved) % ps == 0:
+                cache.reserve(rc.request_id, 1)
+            else:
+                rc.reserved += 1
+        cursors = np.fromiter((rc.cursor for rc in rcs), dtype=np.int32, count=S)
+        ar = np.arange(S + 1, dtype=np.int32)
+        G = len(cache.groups)
+        bts = [cache.block_table(g, rids, bt_round) for g in range(G)]
+        sms = []
+        for g in range(G):
+            pages = np.fromiter((rc.tables[g][rc.cursor // ps] for rc in rcs), dtype=np.int32, count=S)
+            if (pages < 0).any():
+                raise RuntimeError("a token of this step maps to a page that was given back")
+            sms.append(pages * ps + cursors % ps)
+        segs: List[Tuple[str, np.ndarray]] = [
+            ("token_ids", token_ids.astype(np.int32)), ("cu_q", ar), ("seq_lens", cursors + 1), ("tok_seq", ar[:S]),
+            ("state_slot", np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=S)),
+            ("positions", np.zeros(3 * S, dtype=np.int32)), ("pos_mode", np.ones(S, dtype=np.int32)),
+            ("logit_rows", ar[:S]), ("override_rows", np.zeros(0, dtype=np.int32)), ("decode_index", ar[:S]),
+        ]
+        for g in range(G):
+            segs.append((f"bt{g}", bts[g].reshape(-1)))
+            segs.append((f"sm{g}", sms[g].astype(np.int32)))
+        kv_lens = (cursors + 1).tolist()
+        return dict(S=S, T=S, segs=segs, q_lens=[1] * S, kv_lens=kv_lens, bt_widths=[b.shape[1] for b in bts],
+                    n_logit_rows=S, ov_vals=[], n_decode=S, explicit_positions=False)
+
     @staticmethod
     def _layout(segs: List[Tuple[str, np.ndarray]]) -> Tuple[Dict[str, Tuple[int, int]], int]:
         offs, total = {}, 0
@@ -293,7 +341,7 @@ class ModelRunner:
         """
         k = ops.kernels()
         round_to = self.graph_bt_round
-        plan = self._plan(entries, bt_round=round_to)
+        plan = self._plan_decode(entries, bt_round=round_to)
         key = (plan["S"], tuple(plan["bt_widths"]))
         slot = self._graphs.get(key)
         if slot is None:

@@ -84,6 +84,11 @@ class CudaKernels:
         #: bf16 products with more rows than SKINNY_MAX_ROWS: the tcgen05/TMEM/TMA kernel (True) or the
         #: vendor library's GEMM (False)
         self.use_tcgen05 = True
+        #: Row counts from which the tcgen05 kernel is used (measured on B200 at this model's shapes:
+        #: with fewer rows there are too few 128-row tiles to fill 148 SMs and the library's split
+        #: kernels win; the fused SiLU*up epilogue pays off earlier because it saves a whole pass)
+        self.tcgen05_min_rows = 1024
+        self.tcgen05_min_rows_swiglu = 256
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> ctypes.c_void_p:
@@ -212,7 +217,8 @@ class CudaKernels:
             if rc != 10003:
                 self._ok(rc, "gemm_skinny_bf16")
                 return y
-        if self.use_tcgen05 and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+        if (self.use_tcgen05 and M >= self.tcgen05_min_rows and K % 8 == 0 and x.data_ptr() % 16 == 0
+                and w.data_ptr() % 16 == 0):
             return self.gemm_tcgen05(x, w, bias, out_dtype)
         if K % 8 == 0 and N % 8 == 0:
             # Library GEMM on the tensor cores (fp32 accumulation inside).
@@ -263,7 +269,8 @@ class CudaKernels:
                                                self._stream())
             self._ok(rc, "gemm_skinny_bf16(swiglu)")
             return y
-        if (self.use_tcgen05 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+        if (self.use_tcgen05 and M >= self.tcgen05_min_rows_swiglu and x.dtype == torch.bfloat16
+                and w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
                 and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
             return self.gemm_tcgen05(x, w, None, out_dtype, swiglu=True)
         return self.silu_mul(self.linear(x, w, None, x.dtype if x.dtype == w.dtype else torch.float32), out_dtype)

@@ -57,3 +57,41 @@ def test_replay_families_match_plain(name, family, tmp_path, cpu_kernels):
         want = pm.forward(cfg, w, torch.tensor(toks))
         err = (got[rid] - want).abs().max().item()
         assert err < 5e-5, f"{family}/{rid}: max abs logit difference {err}"
+
+
+def test_decode_plan_equals_general_plan(tmp_path, cpu_kernels):
+    """The vectorised plan of a pure decode step lays out the same metadata as the general one,
+    also right at a page boundary (where a request needs a new page)."""
+    import numpy as np
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_c")
+    runner = _runner(d, 512)
+    lens = {"a": 15, "b": 16, "c": 40, "d": 1}
+    for rid, n in lens.items():
+        runner.start_request(rid)
+        runner.step([StepEntry(rid, list(range(1, n + 1)), [])])
+    entries = [StepEntry(r, [7 + i], [0]) for i, r in enumerate(lens)]
+
+    def undo(snapshot):
+        for r, (tables, first_live) in snapshot.items():
+            rc = runner.cache.requests[r]
+            rc.reserved = 0
+            for g, t in enumerate(tables):
+                while len(rc.tables[g]) > len(t):
+                    page = rc.tables[g][len(rc.tables[g]) - 1]
+                    rc.tables[g]._n -= 1
+                    if page >= 0:
+                        runner.cache.groups[g].pool.free(page)
+            rc.first_live = list(first_live)
+
+    snap = {r: ([list(t) for t in runner.cache.requests[r].tables], list(runner.cache.requests[r].first_live)) for r in lens}
+    p1 = runner._plan(entries, bt_round=4)
+    undo(snap)
+    p2 = runner._plan_decode(entries, bt_round=4)
+    undo(snap)
+    assert [n for n, _ in p1["segs"]] == [n for n, _ in p2["segs"]]
+    for (n1, a1), (n2, a2) in zip(p1["segs"], p2["segs"]):
+        assert np.array_equal(np.asarray(a1), np.asarray(a2)), n1
+    for k in ("S", "T", "q_lens", "kv_lens", "bt_widths", "n_logit_rows", "n_decode"):
+        assert p1[k] == p2[k], k
+    runner.cache.check_invariants()
