@@ -78,6 +78,8 @@ class CudaKernels:
 
     def __init__(self) -> None:
         self.lib = library.load()
+        # the library GEMM (used for medium row counts) must accumulate in fp32, also across its K splits
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self._err: Dict[int, torch.Tensor] = {}
         self.launches = 0  # kernels of this library launched so far
         self.skinny_warps = 0  # 0: the skinny GEMM picks its K split from the shape
@@ -206,17 +208,26 @@ class CudaKernels:
         self._ok(rc, "gemm_simt")
         return y
 
+    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
+                    ) -> torch.Tensor:
+        """The weight-streaming bf16 product for up to 64 rows (K a multiple of 8)."""
+        _cuda_contig("x", x, torch.bfloat16)
+        _cuda_contig("w", w, torch.bfloat16)
+        M, K = x.shape
+        N = w.shape[0]
+        _check(w.shape[1] == K and M <= 64 and K % 8 == 0, "gemm_skinny: x [M<=64, K], w [N, K], K % 8 == 0")
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
+                                           M, N, K, 0, self.skinny_warps, self._stream())
+        self._ok(rc, "gemm_skinny_bf16")
+        return y
+
     def _linear_bf16(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
                      ) -> torch.Tensor:
         M, K = x.shape
         N = w.shape[0]
-        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and hasattr(self.lib, "osb_gemm_skinny_bf16"):
-            y = torch.empty((M, N), dtype=out_dtype, device=x.device)
-            rc = self.lib.osb_gemm_skinny_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias),
-                                               _dt(bias) if bias is not None else 0, M, N, K, 0, self.skinny_warps, self._stream())
-            if rc != 10003:
-                self._ok(rc, "gemm_skinny_bf16")
-                return y
+        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0:
+            return self.gemm_skinny(x, w, bias, out_dtype)
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows and K % 8 == 0 and x.data_ptr() % 16 == 0
                 and w.data_ptr() % 16 == 0):
             return self.gemm_tcgen05(x, w, bias, out_dtype)

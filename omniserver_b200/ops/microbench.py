@@ -67,7 +67,7 @@ def bench_gemm(args, K, dev, peak) -> None:
                 if mode:
                     us = graph_time_us(lambda i: K.gate_up_silu(x, ws[i], out_dt), n_rot)
                 else:
-                    us = graph_time_us(lambda i: K.linear(x, ws[i], None, out_dt), n_rot)
+                    us = graph_time_us(lambda i: K.gemm_skinny(x, ws[i], None, out_dt), n_rot)
                 gbs = N * Kd * 2 / us / 1e3
                 cols.append(f"warps={warps}: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
             K.skinny_warps = 0

@@ -271,8 +271,10 @@ def forward(cfg: PlainConfig, w: Dict[str, torch.Tensor], ids: torch.Tensor,
             pos: Optional[torch.Tensor] = None,
             override_rows: Optional[torch.Tensor] = None,
             override_vals: Optional[torch.Tensor] = None,
-            return_hidden: bool = False):
-    """Logits [T, V] of one whole sequence.  Layer order: omniserve/model/qwen2_llm.py:145-157,179-190."""
+            return_hidden: bool = False, rows: Optional[Sequence[int]] = None):
+    """Logits [T, V] of one whole sequence (of the given rows only when ``rows`` is set, as the
+    reference's logits_indices, omniserve/model/qwen2_llm.py:187-189).
+    Layer order: omniserve/model/qwen2_llm.py:145-157,179-190."""
     T = ids.shape[0]
     dtype = w["embed_tokens.weight"].dtype
     if pos is None:
@@ -298,7 +300,8 @@ def forward(cfg: PlainConfig, w: Dict[str, torch.Tensor], ids: torch.Tensor,
     res = add_residual(res, x)
     h = rms_norm(res, w["norm.weight"], cfg.eps)
     head = w["embed_tokens.weight"] if cfg.tied else w["lm_head.weight"]
-    logits = lm_head(h, head)
+    hs = h if rows is None else h[torch.as_tensor(list(rows), dtype=torch.long)]
+    logits = lm_head(hs, head)
     return (logits, h) if return_hidden else logits
 
 
