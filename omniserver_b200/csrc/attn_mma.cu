@@ -15,7 +15,11 @@
 // request, query head h reads kv head h / (nh/nkv).
 // Cache layout: [pages, kv_heads, page_size, head_dim]; a page id < 0 marks a page given back (its
 // keys are outside every window and are read as zeros, then masked).
+#include <cooperative_groups.h>
+
 #include "mma_utils.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 constexpr int TILE_N = 64;
@@ -252,7 +256,7 @@ struct FusedRope {
 
 // ------------------------------------------------------------------------------------------------
 // Decode: one token per request. grid = (splits, kv heads x head tiles, requests).
-template <int HD_MAX, int STAGES>
+template <int HD_MAX, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
@@ -280,10 +284,12 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   const int p = kv_len - 1;
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int first_split = lo / chunk, last_split = p / chunk;
-  if (split < first_split || split > last_split) return;
+  // a split without keys has nothing to do; inside a cluster it still takes part in the merge
+  const bool active = split >= first_split && split <= last_split;
+  if (!CLUSTER && !active) return;
   const int k_begin = max(split * chunk, (lo / TILE_N) * TILE_N);
   const int k_end = min((split + 1) * chunk, kv_len);
-  const int ntiles = (k_end - k_begin + TILE_N - 1) / TILE_N;
+  const int ntiles = active ? (k_end - k_begin + TILE_N - 1) / TILE_N : 0;
   const int* bt = block_table + (size_t)s * bt_stride;
 
   if (fr.cos_t != nullptr && split == last_split && ht == 0) {
@@ -450,50 +456,70 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   __syncthreads();
   pdl_trigger();
 
-  // merge the four warps (each saw different keys) in warp order
-  float* wml = reinterpret_cast<float*>(qs);   // [4][16][2]
-  float* wo = reinterpret_cast<float*>(kvs);   // [4][16][hd]
+  // merge the four warps (each saw different keys) in warp order: per-warp results of the valid rows
+  // go to shared memory (row stride hd + 8 floats: the 64-bit stores of a half-warp hit distinct banks)
+  const int ostride = hd + 8;
+  float* wml = reinterpret_cast<float*>(qs);   // [4][16][2], then the CTA's own [16][2]
+  float* wo = reinterpret_cast<float*>(kvs);   // [4][16][ostride], then the CTA's own [16][ostride]
+  float* cml = wml + 4 * 16 * 2;
+  float* co = wo + 4 * 16 * ostride;
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     float l = l_run[hh];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     const int r = g0 + hh * 8;
-    if ((lane & 3) == 0) {
-      wml[(warp * 16 + r) * 2] = m_run[hh];
-      wml[(warp * 16 + r) * 2 + 1] = l;
-    }
+    if (r < rows) {
+      if ((lane & 3) == 0) {
+        wml[(warp * 16 + r) * 2] = m_run[hh];
+        wml[(warp * 16 + r) * 2 + 1] = l;
+      }
 #pragma unroll
-    for (int i = 0; i < KS * 2; ++i) {
-      const int d = i * 8 + c2;
-      if (d < hd) {
-        wo[(warp * 16 + r) * hd + d] = o[i][hh * 2];
-        wo[(warp * 16 + r) * hd + d + 1] = o[i][hh * 2 + 1];
+      for (int i = 0; i < KS * 2; ++i) {
+        const int d = i * 8 + c2;
+        if (d < hd)
+          *reinterpret_cast<float2*>(wo + (warp * 16 + r) * ostride + d) = make_float2(o[i][hh * 2], o[i][hh * 2 + 1]);
       }
     }
   }
   __syncthreads();
-  const bool direct = first_split == last_split;
+  const bool direct = !CLUSTER && first_split == last_split;
   const int drow = decode_index[s];
-  for (int idx = tid; idx < rows * hd; idx += NTHREADS) {
-    const int r = idx / hd, d = idx - r * hd;
+  const int hq = hd >> 2;
+  for (int idx = tid; idx < rows * hq; idx += NTHREADS) {
+    const int r = idx / hq, d = (idx - r * hq) * 4;
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, wml[(w * 16 + r) * 2]);
-    float L = 0.0f, acc = 0.0f;
+    float L = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = wml[(w * 16 + r) * 2];
-      const float f = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - M);
+      if (mw == -INFINITY) continue;
+      const float f = fast_exp2(mw - M);
+      const float4 v = *reinterpret_cast<const float4*>(wo + (w * 16 + r) * ostride + d);
       L += wml[(w * 16 + r) * 2 + 1] * f;
-      acc += wo[(w * 16 + r) * hd + d] * f;
+      acc.x += v.x * f;
+      acc.y += v.y * f;
+      acc.z += v.z * f;
+      acc.w += v.w * f;
     }
     const int head = head0 + r;
     if (direct) {
-      out[((size_t)q0 * nh + head) * hd + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+      const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+      bf16* op = out + ((size_t)q0 * nh + head) * hd + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    } else if (CLUSTER) {
+      *reinterpret_cast<float4*>(co + r * ostride + d) = acc;
+      if (d == 0) {
+        cml[r * 2] = M;
+        cml[r * 2 + 1] = L;
+      }
     } else {
       const size_t prow = ((size_t)drow * nh + head) * nsplits + split;
-      part_o[prow * hd + d] = acc;
+      *reinterpret_cast<float4*>(part_o + prow * hd + d) = acc;
       if (d == 0) {
         part_ml[prow * 2] = M;
         part_ml[prow * 2 + 1] = L;
@@ -502,8 +528,52 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   }
   if (direct) return;
 
-  // The CTA that finishes last among this (request, kv head) group's splits merges them, in split
-  // order, so the result does not depend on which CTA that is. The counter returns to zero.
+  if (CLUSTER) {
+    // The splits of one (request, kv head) are the CTAs of one cluster: every CTA merges a share of the
+    // output columns over all of them through distributed shared memory, in split order.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    for (int idx = tid * csize + crank; idx < rows * hq; idx += NTHREADS * csize) {
+      const int r = idx / hq, d = (idx - r * hq) * 4;
+      float ms[8], ls[8];
+      float4 vs4[8];
+      float M = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < csize) {
+          const float* rml = cluster.map_shared_rank(cml, c);
+          const float* rco = cluster.map_shared_rank(co, c);
+          ms[c] = rml[r * 2];
+          ls[c] = rml[r * 2 + 1];
+          vs4[c] = *reinterpret_cast<const float4*>(rco + r * ostride + d);
+          M = fmaxf(M, ms[c]);
+        }
+      }
+      float L = 0.0f;
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < csize && ms[c] != -INFINITY) {
+          const float f = fast_exp2(ms[c] - M);
+          L += ls[c] * f;
+          acc.x += vs4[c].x * f;
+          acc.y += vs4[c].y * f;
+          acc.z += vs4[c].z * f;
+          acc.w += vs4[c].w * f;
+        }
+      }
+      const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+      bf16* op = out + ((size_t)q0 * nh + head0 + r) * hd + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    }
+    cluster.sync();  // nobody's shared memory goes away while another CTA still reads it
+    return;
+  }
+
+  // Without a cluster: the CTA that finishes last among this (request, kv head) group's splits merges
+  // them, in split order, so the result does not depend on which CTA that is. The counter returns to zero.
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -525,7 +595,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   }
   __syncthreads();
   // four output columns per thread; the loads of up to 8 splits are in flight together
-  const int hq = hd >> 2;
   for (int idx = tid; idx < rows * hq; idx += NTHREADS) {
     const int r = idx / hq, d = (idx - r * hq) * 4;
     const float* ml = sml + (size_t)r * nv * 2;
@@ -578,16 +647,29 @@ int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, int q
                   const bf16* vc, const int* bt, int bt_stride, const int* cu_q, const int* seq_lens,
                   const int* decode_index, int* counters, int S, int nh, int nkv, int hd, int log2ps, int num_pages,
                   float scale_log2, int window, int chunk, int nsplits, cudaStream_t stream,
-                  FusedRope fr = FusedRope{nullptr, nullptr, nullptr, 0}) {
-  const size_t smem = (size_t)(16 + STAGES * 2 * TILE_N) * (hd + 8) * sizeof(bf16);
-  auto k = attn_decode_kernel<HD_MAX, STAGES>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
+                  FusedRope fr = FusedRope{nullptr, nullptr, nullptr, 0}, bool use_cluster = false) {
+  // stage buffers; after the main loop they hold the warps' and the CTA's fp32 results
+  size_t smem = (size_t)(16 + STAGES * 2 * TILE_N) * (hd + 8) * sizeof(bf16);
+  const size_t merge = (size_t)16 * (hd + 8) * sizeof(bf16) + (size_t)5 * 16 * (hd + 8) * sizeof(float);
+  if (merge > smem) smem = merge;
   const int g = nh / nkv;
   const dim3 grid(nsplits, nkv * ((g + 15) / 16), S);
-  const int rc = osb_launch(k, grid, dim3(NTHREADS), smem, stream, out, part_o, part_ml, q, q_row_stride, kc, vc, bt,
-                            bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, hd, log2ps, num_pages, scale_log2,
-                            window, chunk, nsplits, fr);
+  int rc;
+  if (use_cluster && nsplits > 1 && nsplits <= 8) {
+    auto k = attn_decode_kernel<HD_MAX, STAGES, true>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    rc = osb_launch_cluster(k, grid, dim3(NTHREADS), smem, stream, nsplits, out, part_o, part_ml, q, q_row_stride, kc,
+                            vc, bt, bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, hd, log2ps, num_pages,
+                            scale_log2, window, chunk, nsplits, fr);
+  } else {
+    auto k = attn_decode_kernel<HD_MAX, STAGES, false>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    rc = osb_launch(k, grid, dim3(NTHREADS), smem, stream, out, part_o, part_ml, q, q_row_stride, kc, vc, bt,
+                    bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, hd, log2ps, num_pages, scale_log2,
+                    window, chunk, nsplits, fr);
+  }
   return rc ? rc : osb_last_error();
 }
 }  // namespace
@@ -618,6 +700,8 @@ static int g_decode_stages = 3;  // the merging CTA keeps (max, sum) of 16 rows 
 // n_decode == 0) through the prefill kernel. rope_cos/rope_sin [T, rope_rot/2] and rope_slot_map [T],
 // when given, make the decode kernel rotate q and k itself and store the new key and value (the
 // caller then skips the separate rotary/cache-write kernel); allowed only when n_multi == 0.
+// use_cluster: with 2..8 splits, launch the splits of a request as one thread-block cluster and merge
+// them through distributed shared memory (no scratch, no second phase through global memory).
 // Pipeline depth of the decode kernel for head sizes up to 128 (2 or 3 tiles in flight per CTA).
 OSB_API void osb_attn_set_decode_stages(int stages) { g_decode_stages = stages == 2 ? 2 : 3; }
 
@@ -626,14 +710,16 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
                                 const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
                                 float scale, int window, int max_q_len, int n_decode, int n_multi, float* part_o,
                                 float* part_ml, int* counters, int chunk, int nsplits, const float* rope_cos,
-                                const float* rope_sin, const int* rope_slot_map, int rope_rot, cudaStream_t stream) {
+                                const float* rope_sin, const int* rope_slot_map, int rope_rot, int use_cluster,
+                                cudaStream_t stream) {
   if (S <= 0) return OSB_OK;
   if (hd <= 0 || hd % 16 != 0 || hd > 256 || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
   const int log2ps = page_log2(page_size);
   if (log2ps < 0) return OSB_ERR_UNSUPPORTED;
   if (n_decode > 0 && (chunk <= 0 || chunk % TILE_N != 0 || nsplits <= 0 || nsplits > MAX_SPLITS))
     return OSB_ERR_BAD_SHAPE;
-  if (n_decode > 0 && nsplits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr))
+  if (use_cluster && (nsplits < 2 || nsplits > 8)) use_cluster = 0;
+  if (n_decode > 0 && nsplits > 1 && !use_cluster && (part_o == nullptr || part_ml == nullptr || counters == nullptr))
     return OSB_ERR_BAD_SHAPE;
   FusedRope fr{rope_cos, rope_sin, rope_slot_map, rope_rot};
   if (rope_cos != nullptr) {
@@ -663,19 +749,19 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
     if (hd <= 64)
       rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                nsplits, stream, fr);
+                                nsplits, stream, fr, use_cluster != 0);
     else if (hd <= 128 && g_decode_stages == 2)
       rc = launch_decode<128, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                 nsplits, stream, fr);
+                                 nsplits, stream, fr, use_cluster != 0);
     else if (hd <= 128)
       rc = launch_decode<128, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                 nsplits, stream, fr);
+                                 nsplits, stream, fr, use_cluster != 0);
     else
       rc = launch_decode<256, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
-                                 nsplits, stream, fr);
+                                 nsplits, stream, fr, use_cluster != 0);
   }
   return rc;
 }

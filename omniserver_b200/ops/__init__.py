@@ -75,6 +75,8 @@ class CudaKernels:
     #: rows up to which the bf16 weight-streaming GEMM is used instead of the tiled tensor-core GEMM
     #: (measured on B200: it wins up to 16 rows, the library GEMM from 32 rows on)
     SKINNY_MAX_ROWS = 16
+    #: splits of a request's keys that one thread-block cluster of the decode attention merges
+    CLUSTER_MAX_SPLITS = 8
 
     def __init__(self) -> None:
         self.lib = library.load()
@@ -86,6 +88,7 @@ class CudaKernels:
         #: bf16 products with more rows than SKINNY_MAX_ROWS: the tcgen05/TMEM/TMA kernel (True) or the
         #: vendor library's GEMM (False)
         self.use_tcgen05 = True
+        self.decode_clusters = True   # decode attention: merge a request's splits inside a cluster
         #: Row counts from which the tcgen05 kernel is used (measured on B200 at this model's shapes:
         #: with fewer rows there are too few 128-row tiles to fill 148 SMs and the library's split
         #: kernels win; the fused SiLU*up epilogue pays off earlier because it saves a whole pass)
@@ -379,9 +382,15 @@ class CudaKernels:
             _cuda_contig("decode_index", decode_index, torch.int32)
             part_o = part_ml = counters = None
             chunk, nsplits = 64, 1
+            use_cluster = 0
             if n_decode > 0:
                 chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len)
-                if nsplits > 1:
+                if self.decode_clusters and 1 < nsplits <= 2 * self.CLUSTER_MAX_SPLITS:
+                    # few enough splits: one cluster per (request, kv head), merged in shared memory
+                    chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len,
+                                                        max_splits=self.CLUSTER_MAX_SPLITS)
+                    use_cluster = 1
+                if nsplits > 1 and not use_cluster:
                     n_o, n_ml = n_decode * nh * nsplits * hd, n_decode * nh * nsplits * 2
                     part_o = self._scratch(scratch, "attn_part_o", n_o, qkv.device)
                     part_ml = self._scratch(scratch, "attn_part_ml", n_ml, qkv.device)
@@ -392,7 +401,7 @@ class CudaKernels:
                 _p(cu_q), _p(seq_lens), _p(decode_index), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
                 ctypes.c_float(scale), win, max_q_len, n_decode, n_multi, _p(part_o), _p(part_ml), _p(counters), chunk,
                 nsplits, _p(rope[0] if rope else None), _p(rope[1] if rope else None),
-                _p(rope[2] if rope else None), int(rope[3]) if rope else 0, self._stream())
+                _p(rope[2] if rope else None), int(rope[3]) if rope else 0, use_cluster, self._stream())
             self._ok(rc, "paged_attn_bf16")
             self.launches += (1 if n_multi > 0 or n_decode == 0 else 0) + (1 if n_decode > 0 else 0) - 1
             return out
@@ -415,7 +424,8 @@ class CudaKernels:
                 and ps >= 2 and (ps & (ps - 1)) == 0)
 
     @staticmethod
-    def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 296):
+    def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 296,
+                      max_splits: int = 128):
         """(chunk, nsplits) of the split-key decode kernel. ``target_ctas`` is the number of CTAs the
         GPU holds at once (148 SMs x 2); the keys are cut so that the grid fills them but does not
         spill into a second wave. Splits end at multiples of ``chunk`` keys (a multiple of 64)."""
@@ -423,8 +433,8 @@ class CudaKernels:
         want = max(1, target_ctas // per_split)
         chunk = -(-max(1, max_kv_len) // want)
         chunk = max(128, -(-chunk // 64) * 64)
-        while -(-max_kv_len // chunk) > 128:      # the kernel merges at most 128 splits
-            chunk *= 2
+        while -(-max_kv_len // chunk) > max_splits:   # the kernel merges at most 128 splits (8 in a cluster)
+            chunk += 64
         return chunk, max(1, -(-max_kv_len // chunk))
 
     @staticmethod

@@ -114,7 +114,7 @@ def bench_attn_decode(args, K, dev, peak) -> None:
         for target in args.target_ctas:
             orig = ops.CudaKernels.decode_splits
             ops.CudaKernels.decode_splits = staticmethod(
-                lambda n, k, g, m, target_ctas=target, _o=orig: _o(n, k, g, m, target_ctas))
+                lambda n, k, g, m, target_ctas=target, _o=orig, **kw: _o(n, k, g, m, target_ctas, **kw))
             try:
                 us = graph_time_us(lambda i: K.paged_attention(
                     qkv, kc[i], vc[i], bt, cu_q, sl, ts, nh, nkv, hd, hd ** -0.5, None, 1, ctx, torch.bfloat16,
@@ -123,7 +123,12 @@ def bench_attn_decode(args, K, dev, peak) -> None:
                 ops.CudaKernels.decode_splits = orig
             gbs = B * ctx * nkv * hd * 2 * 2 / us / 1e3
             chunk, nsp = orig(B, nkv, nh // nkv, ctx, target)
-            print(f"B={B:3d} chunk={chunk:5d} splits={nsp:3d} | {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}", flush=True)
+            how = "global merge"
+            if K.decode_clusters and 1 < nsp <= 2 * K.CLUSTER_MAX_SPLITS:
+                chunk, nsp = orig(B, nkv, nh // nkv, ctx, target, max_splits=K.CLUSTER_MAX_SPLITS)
+                how = "cluster merge"
+            print(f"B={B:3d} chunk={chunk:5d} splits={nsp:3d} {how:13s} | {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}",
+                  flush=True)
 
 
 def bench_attn_prefill(args, K, dev, peak) -> None:
@@ -168,6 +173,7 @@ def main() -> None:
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--warps", default="0", help="K splits of the skinny GEMM to try (0 = its own choice)")
+    ap.add_argument("--no-clusters", action="store_true", help="decode attention: merge splits through global memory")
     ap.add_argument("--stages", type=int, default=3, help="pipeline depth of the decode attention kernel (2 or 3)")
     ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
     args = ap.parse_args()
@@ -178,6 +184,7 @@ def main() -> None:
     dev = torch.device("cuda:0")
     K = ops.kernels()
     K.lib.osb_attn_set_decode_stages(args.stages)
+    K.decode_clusters = not args.no_clusters
     peak = peak_gbs()
     with torch.inference_mode():
         if args.what in ("all", "gemm"):
