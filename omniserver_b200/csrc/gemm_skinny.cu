@@ -23,8 +23,11 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return v;
 }
 
-template <int WARPS, int NT>
-__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restrict__ y, int y_is_f32,
+// DEEP: two groups of blocks in flight per warp (more registers, fewer CTAs per SM): for grids of many
+// waves. Otherwise one group and at least 8 CTAs of 4 warps per SM: a grid of about a thousand CTAs
+// then runs as one wave instead of one and a half.
+template <int WARPS, int NT, bool DEEP>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? (DEEP ? 5 : 8) : 1) gemm_skinny_kernel(void* __restrict__ y, int y_is_f32,
                                                                  const bf16* __restrict__ x,
                                                                  const bf16* __restrict__ w,
                                                                  const void* __restrict__ bias, int bias_is_f32,
@@ -58,7 +61,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
 
   // Blocks are processed in groups of PF with the next group's weights (and, for few tokens, the
   // next group's activations) already in flight.
-  constexpr int PF = 2;
+  constexpr int PF = DEEP ? 2 : 1;
   constexpr bool PFX = NT <= 2;  // activations of the next group fit in registers too
   uint4 cur_lo[PF][2], cur_hi[PF][2], nxt_lo[PF][2], nxt_hi[PF][2];
   uint4 cur_x[PFX ? PF : 1][2][PFX ? NT : 1], nxt_x[PFX ? PF : 1][2][PFX ? NT : 1];
@@ -185,11 +188,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(void* __restric
   }
 }
 
-template <int WARPS, int NT>
+template <int WARPS, int NT, bool DEEP>
 int launch(void* y, int y_is_f32, const bf16* x, const bf16* w, const void* bias, int bias_is_f32, int M, int N,
            int K, int mode, int I, cudaStream_t stream) {
   const size_t smem = (size_t)WARPS * NT * 8 * 16 * sizeof(float);
-  auto k = gemm_skinny_kernel<WARPS, NT>;
+  auto k = gemm_skinny_kernel<WARPS, NT, DEEP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -200,15 +203,15 @@ int launch(void* y, int y_is_f32, const bf16* x, const bf16* w, const void* bias
   return rc ? rc : osb_last_error();
 }
 
-template <int WARPS>
+template <int WARPS, bool DEEP>
 int launch_nt(int nt, void* y, int y_is_f32, const bf16* x, const bf16* w, const void* bias, int bias_is_f32, int M,
               int N, int K, int mode, int I, cudaStream_t stream) {
   switch (nt) {
-    case 1: return launch<WARPS, 1>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
-    case 2: return launch<WARPS, 2>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
+    case 1: return launch<WARPS, 1, DEEP>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
+    case 2: return launch<WARPS, 2, DEEP>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
     case 3:
-    case 4: return launch<WARPS, 4>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
-    default: return launch<WARPS, 8>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
+    case 4: return launch<WARPS, 4, DEEP>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
+    default: return launch<WARPS, 8, DEEP>(y, y_is_f32, x, w, bias, bias_is_f32, M, N, K, mode, I, stream);
   }
 }
 }  // namespace
@@ -235,7 +238,11 @@ OSB_API int osb_gemm_skinny_bf16(void* y, int y_dtype, const void* x, const void
   const int nt = (M + 7) / 8;
   const int yf = y_dtype == OSB_F32, bf = bias_dtype == OSB_F32;
   const bf16 *xx = (const bf16*)x, *ww = (const bf16*)w;
-  if (warps == 4) return launch_nt<4>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
-  if (warps == 8) return launch_nt<8>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
-  return launch_nt<16>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
+  if (warps == 4) {
+    // up to one wave of 8 CTAs per SM: the shallow variant; beyond that the deep one
+    if (ctas <= 148 * 8 && nt <= 2) return launch_nt<4, false>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
+    return launch_nt<4, true>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
+  }
+  if (warps == 8) return launch_nt<8, true>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
+  return launch_nt<16, true>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
 }

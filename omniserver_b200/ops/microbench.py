@@ -56,6 +56,8 @@ def bench_gemm(args, K, dev, peak) -> None:
               ("head", V, H, 0)]
     print("== projections: y[M,N] = x[M,K] W[N,K]^T  (us | GB/s of W | fraction of %.0f GB/s)" % peak)
     for name, N, Kd, mode in shapes:
+        if args.only and name not in args.only:
+            continue
         n_rot = max(3, int(300e6 // (N * Kd * 2)) + 1)
         ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(n_rot)]
         for M in args.batch:
@@ -162,6 +164,7 @@ def bench_norm(args, K, dev, peak) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--what", default="all", choices=["all", "gemm", "gemm_prefill", "attn_decode", "attn_prefill", "norm"])
+    ap.add_argument("--only", default="", help="comma-separated projection names to restrict --what gemm to")
     ap.add_argument("--rows", default="2048", help="row counts for --what gemm_prefill")
     ap.add_argument("--batch", default="1,8,64")
     ap.add_argument("--ctx", type=int, default=2048)
@@ -179,6 +182,7 @@ def main() -> None:
     args = ap.parse_args()
     args.batch = [int(b) for b in args.batch.split(",")]
     args.rows = [int(b) for b in args.rows.split(",")]
+    args.only = [x for x in args.only.split(",") if x]
     args.warps = [int(b) for b in args.warps.split(",")]
     args.target_ctas = [int(b) for b in args.target_ctas.split(",")]
     dev = torch.device("cuda:0")
