@@ -1,0 +1,421 @@
+// Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores.
+//
+// One CTA = 128 query rows of one (request, query head). Keys and values stream through shared
+// memory in tiles of 128 keys, fetched page by page with TMA (128-byte swizzle) straight from the
+// cache pages. S = Q K^T and O += P V are tcgen05.mma instructions issued by one thread; S (two
+// buffers) and O live in tensor memory. Four softmax warps (one thread per query row) read S with
+// tcgen05.ld, keep the running maximum and sum in fp32, write P as bf16 into shared memory in the
+// layout the second MMA reads, and rescale O in tensor memory only when a row's maximum has grown
+// by more than 2^8 since the last rescale (the exponent offset in use stays consistent, so the
+// result is exact up to rounding). Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax
+// and epilogue. All mbarrier waits are bounded; on a time-out the CTA records a code in *err, waits
+// for its copies in flight, frees its tensor memory and returns.
+//
+// Semantics as attn_generic.cu / attn_mma.cu (omniserve/model/qwen2_llm.py:96-112,
+// omniserve/cache/kv_prealloc.py:138-142): scale on the scores, query at absolute position p sees keys
+// max(0, p-window+1)..p of its own request, query head h reads kv head h / (nh/nkv).
+#include "tc_utils.cuh"
+
+namespace {
+using namespace tc;
+
+constexpr int BLOCK_M = 128, TILE_N = 128;
+constexpr int NUM_THREADS = 192;
+constexpr int ATOM_BYTES = 128 * 128;  // 128 rows of 128 bytes
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
+
+
+// The maximum of one row of a 128-key S tile (raw scores, before the scale). MASK: only keys lo_row..p_row count.
+template <bool MASK>
+__device__ __forceinline__ float tile_row_max(uint32_t s_addr, int key0, int p_row, int lo_row) {
+  float mx = -INFINITY;
+#pragma unroll 1
+  for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld32(s_addr + (uint32_t)c0, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int key = key0 + c0 + j;
+      if (!MASK || (key <= p_row && key >= lo_row)) mx = fmaxf(mx, __uint_as_float(v[j]));
+    }
+  }
+  return mx;
+}
+
+// P = exp2(S * scale - offset) of one row as bf16 into the K-major, 128-byte-swizzled operand tile of the
+// second MMA ([key atom][row][64 keys]); returns the row's sum of P.
+template <bool MASK>
+__device__ __forceinline__ float tile_write_p(uint32_t s_addr, unsigned char* p_smem, int r, float scale_log2,
+                                              float offset, int key0, int p_row, int lo_row) {
+  float sum = 0.0f;
+#pragma unroll 1
+  for (int c0 = 0; c0 < TILE_N; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld32(s_addr + (uint32_t)c0, v);
+    tmem_ld_wait();
+    unsigned char* prow = p_smem + (c0 >> 6) * ATOM_BYTES + r * 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float pv[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int j = i * 8 + e * 2 + u;
+          const int key = key0 + c0 + j;
+          const bool vis = !MASK || (key <= p_row && key >= lo_row);
+          pv[u] = vis ? exp2f(fmaf(__uint_as_float(v[j]), scale_log2, -offset)) : 0.0f;
+          sum += pv[u];
+        }
+        __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
+        w[e] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      const int chunk = ((c0 & 63) >> 3) + i;  // 16-byte chunk of the 128-byte row
+      *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  return sum;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens, int nh, int nkv, int log2ps,
+    float scale_log2, int window, int skip_single, int* __restrict__ err) {
+  constexpr int NA = HD / 64;                 // 64-element atoms along the head dimension
+  constexpr int Q_BYTES = NA * ATOM_BYTES;    // [atom][128 rows][128 B]
+  constexpr int KV_BYTES = NA * ATOM_BYTES;   // one K or V tile: [atom][128 keys][128 B]
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t S_COL0 = 0, O_COL = 256;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_smem = base;
+  unsigned char* k_smem = q_smem + Q_BYTES;            // 2 stages
+  unsigned char* v_smem = k_smem + 2 * KV_BYTES;       // 2 stages
+  unsigned char* p_smem = v_smem + 2 * KV_BYTES;
+  __shared__ uint64_t q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = gridDim.x - 1 - blockIdx.x;  // long tiles first
+  const int h = blockIdx.y, s = blockIdx.z;
+  const int q0 = cu_q[s], q_len = cu_q[s + 1] - q0;
+  if (q_len <= 0 || (skip_single && q_len == 1)) return;
+  const int m0 = m_tile * BLOCK_M;
+  if (m0 >= q_len) return;
+  const int g = nh / nkv, kvh = h / g;
+  const int kv_len = seq_lens[s];
+  const int rows_here = min(BLOCK_M, q_len - m0);
+  const int p_first = kv_len - q_len + m0;
+  const int p_last = p_first + rows_here - 1;
+  const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int tile_begin = lo / TILE_N, n_tiles = p_last / TILE_N - tile_begin + 1;
+  const int lo_last = (window > 0 && p_last - window + 1 > 0) ? p_last - window + 1 : 0;
+  const int* bt = block_table + (size_t)s * bt_stride;
+  const int ps = 1 << log2ps;
+  const int box_rows = ps < TILE_N ? ps : TILE_N;  // keys per TMA box: a page, or a tile's worth of a larger page
+  const int n_boxes = TILE_N / box_rows;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(&p_full, 4);
+    mbar_init(&pv_done, 1);
+    mbar_init_fence();
+  }
+  // stale shared memory may hold anything; rows of a partial last page are never written by TMA
+  for (int i = threadIdx.x * 16; i < 4 * KV_BYTES; i += NUM_THREADS * 16)
+    *reinterpret_cast<uint4*>(k_smem + i) = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* vabort = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, Q_BYTES);
+      for (int a = 0; a < NA; ++a) tma_load_2d(q_smem + a * ATOM_BYTES, &map_q, &q_full, h * HD + a * 64, q0 + m0);
+    }
+    int issued = 0;
+    bool ok = true;
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int st = t & 1;
+      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      if (lane == 0 && !mbar_wait(&kv_empty[st], ph ^ 1u, vabort)) {
+        if (!*vabort) atomicExch(err, 111);
+        *vabort = 1;
+      }
+      __syncwarp();
+      if (*vabort) {
+        ok = false;
+        break;
+      }
+      const int key0 = (tile_begin + t) * TILE_N;
+      // whole boxes (pages) up to the last key this CTA may look at; a box that starts beyond it is skipped
+      const int boxes = min(n_boxes, (p_last - key0) / box_rows + 1);
+      if (lane == 0) {
+        mbar_expect_tx(&k_full[st], (uint32_t)(boxes * NA * box_rows * 128));
+        mbar_expect_tx(&v_full[st], (uint32_t)(boxes * NA * box_rows * 128));
+      }
+      __syncwarp();
+      for (int i = lane; i < boxes * NA; i += 32) {
+        const int b = i / NA, a = i - b * NA;
+        const int key = key0 + b * box_rows;
+        const int page = bt[key >> log2ps];
+        const int in_page = key & (ps - 1);
+        unsigned char* kd = k_smem + st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128;
+        unsigned char* vd = v_smem + st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128;
+        tma_load_4d(kd, &map_k, &k_full[st], a * 64, in_page, kvh, page);
+        tma_load_4d(vd, &map_v, &v_full[st], a * 64, in_page, kvh, page);
+      }
+      issued = t + 1;
+    }
+    if (*vabort && lane == 0) {
+      for (int t = max(0, issued - 2); t < issued; ++t) {
+        const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&k_full[t & 1], ph); ++w) {
+        }
+        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&v_full[t & 1], ph); ++w) {
+        }
+      }
+      for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&q_full, 0); ++w) {
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(BLOCK_M, TILE_N, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc(BLOCK_M, HD, 0, 1);  // B = V: N (head dim) contiguous
+      bool ok = mbar_wait(&q_full, 0, vabort);
+      auto issue_s = [&](int t) -> bool {
+        const int st = t & 1;
+        if (!mbar_wait(&k_full[st], (uint32_t)(t >> 1) & 1u, vabort)) return false;
+        if (!mbar_wait(&s_empty[st], ((uint32_t)(t >> 1) & 1u) ^ 1u, vabort)) return false;
+        fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t ad = desc_kmajor(q_smem + (ks >> 2) * ATOM_BYTES) + (uint64_t)((ks & 3) * 2);
+          const uint64_t bd = desc_kmajor(k_smem + st * KV_BYTES + (ks >> 2) * ATOM_BYTES) + (uint64_t)((ks & 3) * 2);
+          umma_bf16(tmem + S_COL0 + (uint32_t)(st * TILE_N), ad, bd, idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int st = t & 1;
+        if (t + 1 < n_tiles) ok = issue_s(t + 1);
+        if (!ok) break;
+        if (!mbar_wait(&p_full, (uint32_t)t & 1u, vabort) || !mbar_wait(&v_full[st], (uint32_t)(t >> 1) & 1u, vabort)) {
+          ok = false;
+          break;
+        }
+        fence_after();
+#pragma unroll
+        for (int ks = 0; ks < TILE_N / 16; ++ks) {
+          const uint64_t ad = desc_kmajor(p_smem + (ks >> 2) * ATOM_BYTES) + (uint64_t)((ks & 3) * 2);
+          const uint64_t bd = desc_mnmajor(v_smem + st * KV_BYTES, ATOM_BYTES) + (uint64_t)(ks * (16 * 128 / 16));
+          umma_bf16(tmem + O_COL, ad, bd, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);
+        umma_commit(&pv_done);
+      }
+      if (!ok) {
+        if (!*vabort) atomicExch(err, 112);
+        *vabort = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax and epilogue: warps 2..5
+    const int qd = warp & 3;             // TMEM lane quarter of this warp
+    const int r = qd * 32 + lane;        // query row of this thread
+    const int p_row = r < rows_here ? p_first + r : -1;
+    const int lo_row = (window > 0 && p_row - window + 1 > 0) ? p_row - window + 1 : 0;
+    const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
+    float m_used = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t & 1;
+      if (!mbar_wait(&s_full[st], (uint32_t)(t >> 1) & 1u, vabort)) ok = false;
+      if (!__all_sync(0xffffffffu, ok)) {
+        ok = false;
+        break;
+      }
+      fence_after();
+      const int key0 = (tile_begin + t) * TILE_N;
+      const uint32_t s_addr = tmem + lane_addr + S_COL0 + (uint32_t)(st * TILE_N);
+      // a tile wholly below the diagonal and inside every row's window needs no mask
+      const bool unmasked = key0 + TILE_N - 1 <= p_first && key0 >= lo_last;
+      float mx = unmasked ? tile_row_max<false>(s_addr, key0, p_row, lo_row) : tile_row_max<true>(s_addr, key0, p_row, lo_row);
+      mx *= scale_log2;  // the scale is positive
+      // the exponent offset in use moves only when the maximum has grown enough (or at the first keys)
+      const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx > -INFINITY);
+      const float m_new = grow ? mx : m_used;
+      const float alpha = (grow && m_used != -INFINITY) ? exp2f(m_used - m_new) : 1.0f;
+      // P and O belong to the MMA of the tile before until it has completed
+      if (t > 0) {
+        if (!mbar_wait(&pv_done, (uint32_t)(t - 1) & 1u, vabort)) ok = false;
+        if (!__all_sync(0xffffffffu, ok)) {
+          ok = false;
+          break;
+        }
+        fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+            tmem_st32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
+          }
+          tmem_st_wait();
+        }
+      }
+      l_run *= alpha;
+      m_used = m_new;
+      // pass 2: P; rows that have seen no key yet (offset -inf) are all masked in this tile too
+      const float offset = m_used == -INFINITY ? 0.0f : m_used;
+      l_run += unmasked ? tile_write_p<false>(s_addr, p_smem, r, scale_log2, offset, key0, p_row, lo_row)
+                        : tile_write_p<true>(s_addr, p_smem, r, scale_log2, offset, key0, p_row, lo_row);
+      // keys at and beyond the request's length lie in the loaded pages but hold whatever was there before:
+      // their P is 0, and 0 x (Inf or NaN) must not reach O, so their V rows are cleared
+      {
+        const int loaded = min(n_boxes, (p_last - key0) / box_rows + 1) * box_rows;
+        const int stale = kv_len - key0;
+        if (stale < loaded) {
+          if (!mbar_wait(&v_full[st], (uint32_t)(t >> 1) & 1u, vabort)) ok = false;
+          if (!__all_sync(0xffffffffu, ok)) {
+            ok = false;
+            break;
+          }
+          if (r >= stale && r < loaded)
+            for (int a = 0; a < NA; ++a)
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(v_smem + st * KV_BYTES + a * ATOM_BYTES + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      // S of this buffer has been read; P is written
+      fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[st]);
+        mbar_arrive(&p_full);
+      }
+    }
+    // epilogue: O / l
+    if (ok) {
+      if (!mbar_wait(&pv_done, (uint32_t)(n_tiles - 1) & 1u, vabort)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      fence_after();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (r < rows_here) {
+          bf16* op = out + ((size_t)(q0 + m0 + r) * nh + h) * HD + c0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 u;
+            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              hh[e] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]) * inv, __uint_as_float(v[j + 2 * e + 1]) * inv);
+            *reinterpret_cast<uint4*>(op + j) = u;
+          }
+        }
+      }
+    } else if (lane == 0) {
+      if (!*vabort) atomicExch(err, 113);
+      *vabort = 1;
+    }
+  }
+  fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, bf16* out, const int* bt, int bt_stride,
+           const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int log2ps, float scale_log2, int window,
+           int max_q_len, int skip_single, int* err, cudaStream_t stream) {
+  // at least 120 KB so that one CTA is resident per SM: each takes all 512 tensor-memory columns
+  constexpr size_t need = (size_t)(HD / 64) * ATOM_BYTES * 5 + 2 * ATOM_BYTES + 1024;
+  constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
+  auto k = attn_prefill_tc_kernel<HD>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const dim3 grid((max_q_len + BLOCK_M - 1) / BLOCK_M, nh, S);
+  k<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, out, bt, bt_stride, cu_q, seq_lens, nh, nkv, log2ps, scale_log2,
+                                         window, skip_single, err);
+  return osb_last_error();
+}
+}  // namespace
+
+// out [T, nh*hd] bf16; q = the first nh*hd columns of rows of q_row_stride elements; caches
+// [pages, nkv, page_size, hd] bf16. Head sizes 64 and 128, page sizes that are powers of two from 8
+// up; anything else is refused with OSB_ERR_UNSUPPORTED (the caller then uses the mma.sync kernel).
+// Requests bringing one token are skipped when skip_single is set.
+OSB_API int osb_attn_prefill_tc(void* out, const void* q, int q_row_stride, int T, const void* k_cache,
+                                const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
+                                const int* seq_lens, int S, int nh, int nkv, int hd, int page_size, int num_pages,
+                                float scale, int window, int max_q_len, int skip_single, int* err,
+                                cudaStream_t stream) {
+  if (S <= 0 || T <= 0) return OSB_OK;
+  if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || !(scale > 0.0f)) return OSB_ERR_UNSUPPORTED;
+  if (page_size < 8 || (page_size & (page_size - 1))) return OSB_ERR_UNSUPPORTED;
+  if ((q_row_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+    return OSB_ERR_UNSUPPORTED;
+  int log2ps = 0;
+  while ((1 << log2ps) < page_size) ++log2ps;
+  CUtensorMap mq, mk, mv;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)q_row_stride, (cuuint64_t)T};
+    const cuuint64_t strides[1] = {(cuuint64_t)q_row_stride * 2};
+    const cuuint32_t box[2] = {64, 128};
+    int rc = tc::make_map_bf16(&mq, q, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)page_size, (cuuint64_t)nkv, (cuuint64_t)num_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)page_size * hd * 2,
+                                   (cuuint64_t)nkv * page_size * hd * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)(page_size < 128 ? page_size : 128), 1, 1};
+    int rc = tc::make_map_bf16(&mk, k_cache, 4, dims, strides, box);
+    if (rc) return rc;
+    rc = tc::make_map_bf16(&mv, v_cache, 4, dims, strides, box);
+    if (rc) return rc;
+  }
+  const float scale_log2 = scale * LOG2E;
+  if (hd == 64)
+    return launch<64>(mq, mk, mv, (bf16*)out, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, log2ps, scale_log2,
+                      window, max_q_len, skip_single, err, stream);
+  return launch<128>(mq, mk, mv, (bf16*)out, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, log2ps, scale_log2,
+                     window, max_q_len, skip_single, err, stream);
+}

@@ -43,6 +43,9 @@ _DEVICE_ERR = {
     102: "tcgen05 GEMM: the MMA issuer waited too long for operands",
     103: "tcgen05 GEMM: the epilogue waited too long for the accumulator",
     104: "tcgen05 GEMM: the MMA issuer waited too long for a drained accumulator",
+    111: "tcgen05 attention: the TMA producer waited too long for a free key/value stage",
+    112: "tcgen05 attention: the MMA issuer waited too long for operands",
+    113: "tcgen05 attention: the softmax warps waited too long for scores or the output",
 }
 
 
@@ -89,6 +92,7 @@ class CudaKernels:
         #: vendor library's GEMM (False)
         self.use_tcgen05 = True
         self.decode_clusters = True   # decode attention: merge a request's splits inside a cluster
+        self.tc_prefill = True        # prompt attention on tcgen05 where the head size allows (64, 128)
         #: Row counts from which the tcgen05 kernel is used (measured on B200 at this model's shapes:
         #: with fewer rows there are too few 128-row tiles to fill 148 SMs and the library's split
         #: kernels win; the fused SiLU*up epilogue pays off earlier because it saves a whole pass)
@@ -380,6 +384,18 @@ class CudaKernels:
                 and k_cache.shape[2] >= 2 and (k_cache.shape[2] & (k_cache.shape[2] - 1)) == 0)
         if fast:
             _cuda_contig("decode_index", decode_index, torch.int32)
+            if (self.tc_prefill and (n_multi > 0 or n_decode == 0) and hd in (64, 128) and k_cache.shape[2] >= 8
+                    and qkv.shape[1] % 8 == 0 and scale > 0):
+                # requests bringing several tokens: tcgen05 kernel; the others follow in the decode kernel
+                rc = self.lib.osb_attn_prefill_tc(
+                    _p(out), _p(qkv), qkv.shape[1], T, _p(k_cache), _p(v_cache), _p(block_table),
+                    block_table.shape[1], _p(cu_q), _p(seq_lens), S, nh, nkv, hd, k_cache.shape[2],
+                    k_cache.shape[0], ctypes.c_float(scale), win, max_q_len, 1 if n_decode > 0 else 0,
+                    _p(self.err_flag(qkv.device)), self._stream())
+                self._ok(rc, "attn_prefill_tc")
+                if n_decode == 0:
+                    return out
+                n_multi = 0
             part_o = part_ml = counters = None
             chunk, nsplits = 64, 1
             use_cluster = 0

@@ -399,6 +399,108 @@ def test_paged_attention_finds_one_key_that_matters(dtype, window):
                 assert got[t].abs().mean() < 2.0, f"key {j} must be invisible to the query at {p}"
 
 
+def _attn_bf16_bound(case, nh, nkv, hd, window, want):
+    """What bf16 tensor-core attention may differ by: the probabilities are rounded to bf16 (2^-9
+    relative each) before they meet the values, so the numerator is off by at most 2^-9 sum_j p_j |v_j|,
+    and the output is rounded once more; a factor of two covers the fp32 sums' order."""
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = case
+    mq, mk = int((cu_q[1:] - cu_q[:-1]).max()), int(seq_lens.max())
+    mag = REF.paged_attention(qkv, kc, vc.abs(), bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, window, mq, mk,
+                              torch.float32)
+    return 2.0 ** -8 * (mag + want.abs()) + 1e-6
+
+
+def _assert_attn_close(got, want, case, nh, nkv, hd, window, what=""):
+    bound = _attn_bf16_bound(case, nh, nkv, hd, window, want)
+    over = (got - want).abs() - bound
+    assert not (over > 0).any(), f"{what}: {int((over > 0).sum())} values beyond the bf16 bound, worst by {float(over.max()):.3g}"
+
+
+def _poison_unused(case, ps):
+    """NaN wherever no live key lies: pages of nobody, and the rest of each request's last page."""
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = case
+    live = torch.zeros(kc.shape[0], ps, dtype=torch.bool)
+    for s, kv in enumerate(seq_lens.tolist()):
+        for j in range(kv):
+            live[int(bt[s, j // ps]), j % ps] = True
+    dead = ~live
+    for c in (kc, vc):
+        c.permute(0, 2, 1, 3)[dead] = float("nan")
+    return case
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(12, 2, 128, 16), (4, 4, 64, 8), (6, 2, 64, 32), (2, 1, 128, 128), (3, 1, 128, 256),
+                                          (2, 2, 64, 64)])
+@pytest.mark.parametrize("window", [None, 100, 200])
+def test_prefill_attention_tcgen05(nh, nkv, hd, ps, window):
+    """Prompt portions on the tcgen05 kernel: several 128-key tiles, portions that start and end inside
+    tiles and pages, a request shorter than a tile, single tokens beside them; what lies in the pages
+    beyond a request's length is NaN and must not reach the output."""
+    assert K().tc_prefill
+    q_lens, kv_lens = [300, 1, 130, 128, 2, 257], [300, 500, 700, 128, 259, 1000]
+    case = _poison_unused(_paged_case(q_lens, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=11), ps)
+    before = K().launches
+    got, want = _run_attn(case, nh, nkv, hd, window, torch.bfloat16)
+    assert K().launches - before == 2  # the tcgen05 kernel and the decode kernel
+    assert torch.isfinite(got).all()
+    _assert_attn_close(got, want, case, nh, nkv, hd, window, "tcgen05")
+    # the mma.sync kernel stays within the same bound
+    K().tc_prefill = False
+    try:
+        other, _ = _run_attn(case, nh, nkv, hd, window, torch.bfloat16)
+    finally:
+        K().tc_prefill = True
+    _assert_attn_close(other, want, case, nh, nkv, hd, window, "mma.sync")
+
+
+@pytest.mark.parametrize("window", [None, 130])
+def test_prefill_attention_tcgen05_finds_one_key_that_matters(window):
+    """One dominating key at the edges of the 128-key tiles, of pages, of the window and at the query
+    itself, for queries in the first and in a later 128-row tile of the portion."""
+    nh, nkv, hd, ps = 4, 2, 64, 16
+    kv_len, q_len = 700, 300
+    dtype = torch.bfloat16
+    for qi in (0, 127, 128, 299):
+        p = kv_len - q_len + qi
+        spots = [0, 127, 128, 255, 256, 511, 512, p - 1, p, min(p + 1, kv_len - 1)]
+        if window:
+            spots += [p - window + 1, p - window, p - window + 2]
+        for j in spots:
+            case = list(_paged_case([q_len], [kv_len], nh, nkv, hd, ps, dtype, seed=j + 7))
+            qkv, kc, vc, bt = case[0], case[1], case[2], case[3]
+            for kvh in range(nkv):
+                qh = qkv[qi, (kvh * (nh // nkv)) * hd:(kvh * (nh // nkv) + 1) * hd].float()
+                for h in range(kvh * (nh // nkv), (kvh + 1) * (nh // nkv)):
+                    qkv[qi, h * hd:(h + 1) * hd] = qh.to(dtype)
+                kvec = qh / qh.norm() ** 2 * 25.0 * math.sqrt(hd)
+                page = int(bt[0, j // ps])
+                kc[page, kvh, j % ps] = kvec.to(dtype)
+                vc[page, kvh, j % ps] = 7.0
+            got, want = _run_attn(tuple(case), nh, nkv, hd, window, dtype)
+            visible = j <= p and (not window or j > p - window)
+            _assert_attn_close(got, want, tuple(case), nh, nkv, hd, window, f"key {j}, query at {p}")
+            if visible:
+                assert got[qi].mean() > 6.5, f"key {j} should dominate the query at {p}"
+            else:
+                assert got[qi].abs().mean() < 2.0, f"key {j} must be invisible to the query at {p}"
+
+
+def test_prefill_attention_tcgen05_rescales_when_the_maximum_grows():
+    """Scores that grow along the keys: the running offset has to move several times and the
+    accumulated output has to be rescaled in tensor memory each time."""
+    nh, nkv, hd, ps = 2, 1, 128, 16
+    kv_len = q_len = 640
+    case = list(_paged_case([q_len], [kv_len], nh, nkv, hd, ps, torch.bfloat16, seed=5))
+    qkv, kc, bt = case[0], case[1], case[3]
+    qkv[:, :nh * hd] = 0
+    qkv[:, 0] = 4.0
+    qkv[:, hd] = 4.0
+    for j in range(kv_len):
+        kc[int(bt[0, j // ps]), 0, j % ps, 0] = 0.25 * j   # score of key j: j / sqrt(hd) * ... grows by tiles
+    got, want = _run_attn(tuple(case), nh, nkv, hd, None, torch.bfloat16)
+    _assert_attn_close(got, want, tuple(case), nh, nkv, hd, None)
+
+
 def test_paged_attention_fp32_is_independent_of_the_batch():
     """In 32-bit the kernel's sums run in an order fixed by absolute key positions: a request's
     output is bitwise the same alone, cut into portions, or beside other requests."""
