@@ -3,13 +3,16 @@
 // One CTA = 128 query rows of one (request, query head). Keys and values stream through shared
 // memory in tiles of 128 keys, fetched page by page with TMA (128-byte swizzle) straight from the
 // cache pages. S = Q K^T and O += P V are tcgen05.mma instructions issued by one thread; S (two
-// buffers) and O live in tensor memory. Four softmax warps (one thread per query row) read S with
-// tcgen05.ld, keep the running maximum and sum in fp32, write P as bf16 into shared memory in the
-// layout the second MMA reads, and rescale O in tensor memory only when a row's maximum has grown
-// by more than 2^8 since the last rescale (the exponent offset in use stays consistent, so the
-// result is exact up to rounding). Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax
-// and epilogue. All mbarrier waits are bounded; on a time-out the CTA records a code in *err, waits
-// for its copies in flight, frees its tensor memory and returns.
+// buffers) and O live in tensor memory. Four softmax warps (one thread per query row) read a row
+// of S with tcgen05.ld into registers, keep the running maximum and sum in fp32 and write P as
+// bf16 back into tensor memory over the S it came from (two values per 32-bit column), from where
+// the second MMA takes it as its A operand: P never touches shared memory, and the softmax of
+// tile t+1 runs while the tensor cores work on P V of tile t and Q K^T of tile t+2. O is rescaled
+// in tensor memory only when a row's maximum has grown by more than 2^8 since the offset in use
+// was set (the offset stays consistent, so the result is exact up to rounding).
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax and epilogue. All mbarrier
+// waits are bounded; on a time-out the CTA records a code in *err, waits for its copies in flight,
+// frees its tensor memory and returns.
 //
 // Semantics as attn_generic.cu / attn_mma.cu (omniserve/model/qwen2_llm.py:96-112,
 // omniserve/cache/kv_prealloc.py:138-142): scale on the scores, query at absolute position p sees keys
@@ -25,85 +28,32 @@ constexpr int ATOM_BYTES = 128 * 128;  // 128 rows of 128 bytes
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
-
-// The maximum of one row of a 128-key S tile (raw scores, before the scale). MASK: only keys lo_row..p_row count.
-template <bool MASK>
-__device__ __forceinline__ float tile_row_max(uint32_t s_addr, int key0, int p_row, int lo_row) {
-  float mx = -INFINITY;
-#pragma unroll 1
-  for (int c0 = 0; c0 < TILE_N; c0 += 32) {
-    uint32_t v[32];
-    tmem_ld32(s_addr + (uint32_t)c0, v);
-    tmem_ld_wait();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int key = key0 + c0 + j;
-      if (!MASK || (key <= p_row && key >= lo_row)) mx = fmaxf(mx, __uint_as_float(v[j]));
-    }
-  }
-  return mx;
-}
-
-// P = exp2(S * scale - offset) of one row as bf16 into the K-major, 128-byte-swizzled operand tile of the
-// second MMA ([key atom][row][64 keys]); returns the row's sum of P.
-template <bool MASK>
-__device__ __forceinline__ float tile_write_p(uint32_t s_addr, unsigned char* p_smem, int r, float scale_log2,
-                                              float offset, int key0, int p_row, int lo_row) {
-  float sum = 0.0f;
-#pragma unroll 1
-  for (int c0 = 0; c0 < TILE_N; c0 += 32) {
-    uint32_t v[32];
-    tmem_ld32(s_addr + (uint32_t)c0, v);
-    tmem_ld_wait();
-    unsigned char* prow = p_smem + (c0 >> 6) * ATOM_BYTES + r * 128;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float pv[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int j = i * 8 + e * 2 + u;
-          const int key = key0 + c0 + j;
-          const bool vis = !MASK || (key <= p_row && key >= lo_row);
-          pv[u] = vis ? exp2f(fmaf(__uint_as_float(v[j]), scale_log2, -offset)) : 0.0f;
-          sum += pv[u];
-        }
-        __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
-        w[e] = *reinterpret_cast<uint32_t*>(&b);
-      }
-      const int chunk = ((c0 & 63) >> 3) + i;  // 16-byte chunk of the 128-byte row
-      *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-  }
-  return sum;
-}
-
 template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens, int nh, int nkv, int log2ps,
-    float scale_log2, int window, int skip_single, int* __restrict__ err) {
+    float scale_log2, int window, int skip_single, int m_tiles, int* __restrict__ err) {
   constexpr int NA = HD / 64;                 // 64-element atoms along the head dimension
   constexpr int Q_BYTES = NA * ATOM_BYTES;    // [atom][128 rows][128 B]
   constexpr int KV_BYTES = NA * ATOM_BYTES;   // one K or V tile: [atom][128 keys][128 B]
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t S_COL0 = 0, O_COL = 256;
+  constexpr uint32_t S_COL0 = 0, O_COL = 256;  // S buffers at columns 0 and 128, P over the first 64 columns of its S
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_smem = base;
   unsigned char* k_smem = q_smem + Q_BYTES;            // 2 stages
   unsigned char* v_smem = k_smem + 2 * KV_BYTES;       // 2 stages
-  unsigned char* p_smem = v_smem + 2 * KV_BYTES;
-  __shared__ uint64_t q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], pv_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tile = gridDim.x - 1 - blockIdx.x;  // long tiles first
-  const int h = blockIdx.y, s = blockIdx.z;
+  // blocks are numbered so that the tiles with the most keys (the last rows of the longest portions) start first
+  const int per_tile = gridDim.x / m_tiles;
+  const int m_tile = m_tiles - 1 - (int)blockIdx.x / per_tile;
+  const int hs = (int)blockIdx.x % per_tile;
+  const int h = hs % nh, s = hs / nh;
   const int q0 = cu_q[s], q_len = cu_q[s + 1] - q0;
   if (q_len <= 0 || (skip_single && q_len == 1)) return;
   const int m0 = m_tile * BLOCK_M;
@@ -114,8 +64,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
   const int p_first = kv_len - q_len + m0;
   const int p_last = p_first + rows_here - 1;
   const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-  const int tile_begin = lo / TILE_N, n_tiles = p_last / TILE_N - tile_begin + 1;
   const int lo_last = (window > 0 && p_last - window + 1 > 0) ? p_last - window + 1 : 0;
+  const int tile_begin = lo / TILE_N, n_tiles = p_last / TILE_N - tile_begin + 1;
   const int* bt = block_table + (size_t)s * bt_stride;
   const int ps = 1 << log2ps;
   const int box_rows = ps < TILE_N ? ps : TILE_N;  // keys per TMA box: a page, or a tile's worth of a larger page
@@ -127,15 +77,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 4);
     }
-    mbar_init(&p_full, 4);
     mbar_init(&pv_done, 1);
     mbar_init_fence();
   }
-  // stale shared memory may hold anything; rows of a partial last page are never written by TMA
+  // stale shared memory may hold anything; rows of a partial last tile are never written by TMA
   for (int i = threadIdx.x * 16; i < 4 * KV_BYTES; i += NUM_THREADS * 16)
     *reinterpret_cast<uint4*>(k_smem + i) = make_uint4(0, 0, 0, 0);
   fence_async_smem();
@@ -153,37 +103,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       for (int a = 0; a < NA; ++a) tma_load_2d(q_smem + a * ATOM_BYTES, &map_q, &q_full, h * HD + a * 64, q0 + m0);
     }
     int issued = 0;
-    bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
+    for (int t = 0; t < n_tiles; ++t) {
       const int st = t & 1;
       const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-      if (lane == 0 && !mbar_wait(&kv_empty[st], ph ^ 1u, vabort)) {
-        if (!*vabort) atomicExch(err, 111);
-        *vabort = 1;
-      }
-      __syncwarp();
-      if (*vabort) {
-        ok = false;
-        break;
-      }
       const int key0 = (tile_begin + t) * TILE_N;
       // whole boxes (pages) up to the last key this CTA may look at; a box that starts beyond it is skipped
       const int boxes = min(n_boxes, (p_last - key0) / box_rows + 1);
-      if (lane == 0) {
-        mbar_expect_tx(&k_full[st], (uint32_t)(boxes * NA * box_rows * 128));
-        mbar_expect_tx(&v_full[st], (uint32_t)(boxes * NA * box_rows * 128));
-      }
-      __syncwarp();
-      for (int i = lane; i < boxes * NA; i += 32) {
-        const int b = i / NA, a = i - b * NA;
+      int page = 0, in_page = 0, off = 0, a = 0;
+      const bool mine = lane < boxes * NA;  // boxes * NA <= 32: a box is at least 8 keys
+      if (mine) {
+        const int b = lane / NA;
+        a = lane - b * NA;
         const int key = key0 + b * box_rows;
-        const int page = bt[key >> log2ps];
-        const int in_page = key & (ps - 1);
-        unsigned char* kd = k_smem + st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128;
-        unsigned char* vd = v_smem + st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128;
-        tma_load_4d(kd, &map_k, &k_full[st], a * 64, in_page, kvh, page);
-        tma_load_4d(vd, &map_v, &v_full[st], a * 64, in_page, kvh, page);
+        page = bt[key >> log2ps];
+        in_page = key & (ps - 1);
+        off = st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128;
       }
+      for (int which = 0; which < 2; ++which) {  // keys first: Q K^T is waiting for them
+        uint64_t* empty = which ? &v_empty[st] : &k_empty[st];
+        uint64_t* full = which ? &v_full[st] : &k_full[st];
+        if (lane == 0) {
+          if (!mbar_wait(empty, ph ^ 1u, vabort)) {
+            if (!*vabort) atomicExch(err, 111);
+            *vabort = 1;
+          } else {
+            mbar_expect_tx(full, (uint32_t)(boxes * NA * box_rows * 128));
+          }
+        }
+        __syncwarp();
+        if (*vabort) break;
+        if (mine) tma_load_4d((which ? v_smem : k_smem) + off, which ? &map_v : &map_k, full, a * 64, in_page, kvh, page);
+      }
+      if (*vabort) break;
       issued = t + 1;
     }
     if (*vabort && lane == 0) {
@@ -206,7 +157,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       auto issue_s = [&](int t) -> bool {
         const int st = t & 1;
         if (!mbar_wait(&k_full[st], (uint32_t)(t >> 1) & 1u, vabort)) return false;
-        if (!mbar_wait(&s_empty[st], ((uint32_t)(t >> 1) & 1u) ^ 1u, vabort)) return false;
         fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -215,26 +165,34 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           umma_bf16(tmem + S_COL0 + (uint32_t)(st * TILE_N), ad, bd, idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
         return true;
       };
-      if (ok) ok = issue_s(0);
+      for (int t = 0; t < 2 && t < n_tiles && ok; ++t) ok = issue_s(t);
       for (int t = 0; t < n_tiles && ok; ++t) {
         const int st = t & 1;
-        if (t + 1 < n_tiles) ok = issue_s(t + 1);
-        if (!ok) break;
-        if (!mbar_wait(&p_full, (uint32_t)t & 1u, vabort) || !mbar_wait(&v_full[st], (uint32_t)(t >> 1) & 1u, vabort)) {
+        if (!mbar_wait(&p_full[st], (uint32_t)(t >> 1) & 1u, vabort) ||
+            !mbar_wait(&v_full[st], (uint32_t)(t >> 1) & 1u, vabort)) {
           ok = false;
           break;
         }
         fence_after();
+        const uint32_t p_tmem = tmem + S_COL0 + (uint32_t)(st * TILE_N);
 #pragma unroll
         for (int ks = 0; ks < TILE_N / 16; ++ks) {
-          const uint64_t ad = desc_kmajor(p_smem + (ks >> 2) * ATOM_BYTES) + (uint64_t)((ks & 3) * 2);
           const uint64_t bd = desc_mnmajor(v_smem + st * KV_BYTES, ATOM_BYTES) + (uint64_t)(ks * (16 * 128 / 16));
-          umma_bf16(tmem + O_COL, ad, bd, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem + O_COL, p_tmem + (uint32_t)(ks * 8), bd, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[st]);
         umma_commit(&pv_done);
+        if (t + 2 < n_tiles) {
+          // the S buffer of tile t+2 still holds P of tile t until that product has completed
+          if (!mbar_wait(&pv_done, (uint32_t)t & 1u, vabort)) {
+            ok = false;
+            break;
+          }
+          ok = issue_s(t + 2);
+        }
       }
       if (!ok) {
         if (!*vabort) atomicExch(err, 112);
@@ -260,41 +218,73 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       fence_after();
       const int key0 = (tile_begin + t) * TILE_N;
       const uint32_t s_addr = tmem + lane_addr + S_COL0 + (uint32_t)(st * TILE_N);
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + (uint32_t)(c * 32), v[c]);
+      tmem_ld_wait();
       // a tile wholly below the diagonal and inside every row's window needs no mask
       const bool unmasked = key0 + TILE_N - 1 <= p_first && key0 >= lo_last;
-      float mx = unmasked ? tile_row_max<false>(s_addr, key0, p_row, lo_row) : tile_row_max<true>(s_addr, key0, p_row, lo_row);
-      mx *= scale_log2;  // the scale is positive
+      if (!unmasked) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c * 32 + j;
+            if (key > p_row || key < lo_row) v[c][j] = 0xff800000u;  // -inf
+          }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        mx0 = fmaxf(mx0, __uint_as_float(v[0][j]));
+        mx1 = fmaxf(mx1, __uint_as_float(v[1][j]));
+        mx2 = fmaxf(mx2, __uint_as_float(v[2][j]));
+        mx3 = fmaxf(mx3, __uint_as_float(v[3][j]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;  // the scale is positive
       // the exponent offset in use moves only when the maximum has grown enough (or at the first keys)
       const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx > -INFINITY);
       const float m_new = grow ? mx : m_used;
-      const float alpha = (grow && m_used != -INFINITY) ? exp2f(m_used - m_new) : 1.0f;
-      // P and O belong to the MMA of the tile before until it has completed
-      if (t > 0) {
+      const float alpha = (grow && m_used != -INFINITY) ? ex2_approx(m_used - m_new) : 1.0f;
+      if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        // O belongs to the tensor cores until the product of the tile before has completed
         if (!mbar_wait(&pv_done, (uint32_t)(t - 1) & 1u, vabort)) ok = false;
         if (!__all_sync(0xffffffffu, ok)) {
           ok = false;
           break;
         }
         fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
-            tmem_ld_wait();
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld32(tmem + lane_addr + O_COL + (uint32_t)c0, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-            tmem_st32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
-          }
-          tmem_st_wait();
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st32(tmem + lane_addr + O_COL + (uint32_t)c0, o);
         }
       }
       l_run *= alpha;
       m_used = m_new;
-      // pass 2: P; rows that have seen no key yet (offset -inf) are all masked in this tile too
+      // P = exp2(S * scale - offset), two bf16 per column, over the first half of this S buffer;
+      // rows that have seen no key yet (offset -inf) are all masked here: exp2(-inf) = 0 with any finite offset
       const float offset = m_used == -INFINITY ? 0.0f : m_used;
-      l_run += unmasked ? tile_write_p<false>(s_addr, p_smem, r, scale_log2, offset, key0, p_row, lo_row)
-                        : tile_write_p<true>(s_addr, p_smem, r, scale_log2, offset, key0, p_row, lo_row);
+      float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(v[c][j]), scale_log2, -offset));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(v[c][j + 1]), scale_log2, -offset));
+          sum0 += p0;
+          sum1 += p1;
+          __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+          v[c >> 1][(c & 1) * 16 + (j >> 1)] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        if (c == 1) tmem_st32(s_addr, v[0]);
+      }
+      tmem_st32(s_addr + 32u, v[1]);
+      l_run += sum0 + sum1;
       // keys at and beyond the request's length lie in the loaded pages but hold whatever was there before:
       // their P is 0, and 0 x (Inf or NaN) must not reach O, so their V rows are cleared
       {
@@ -311,16 +301,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
 #pragma unroll
               for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(v_smem + st * KV_BYTES + a * ATOM_BYTES + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+          fence_async_smem();
         }
       }
-      // S of this buffer has been read; P is written
+      tmem_st_wait();
       fence_before();
-      fence_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[st]);
-        mbar_arrive(&p_full);
-      }
+      if (lane == 0) mbar_arrive(&p_full[st]);
     }
     // epilogue: O / l
     if (ok) {
@@ -332,8 +319,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem + lane_addr + O_COL + (uint32_t)c0, v);
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_addr + O_COL + (uint32_t)c0, o);
         tmem_ld_wait();
         if (r < rows_here) {
           bf16* op = out + ((size_t)(q0 + m0 + r) * nh + h) * HD + c0;
@@ -343,7 +330,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
             __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              hh[e] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]) * inv, __uint_as_float(v[j + 2 * e + 1]) * inv);
+              hh[e] = __floats2bfloat162_rn(__uint_as_float(o[j + 2 * e]) * inv, __uint_as_float(o[j + 2 * e + 1]) * inv);
             *reinterpret_cast<uint4*>(op + j) = u;
           }
         }
@@ -366,14 +353,15 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int log2ps, float scale_log2, int window,
            int max_q_len, int skip_single, int* err, cudaStream_t stream) {
   // at least 120 KB so that one CTA is resident per SM: each takes all 512 tensor-memory columns
-  constexpr size_t need = (size_t)(HD / 64) * ATOM_BYTES * 5 + 2 * ATOM_BYTES + 1024;
+  constexpr size_t need = (size_t)(HD / 64) * ATOM_BYTES * 5 + 1024;
   constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
   auto k = attn_prefill_tc_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  const dim3 grid((max_q_len + BLOCK_M - 1) / BLOCK_M, nh, S);
+  const int m_tiles = (max_q_len + BLOCK_M - 1) / BLOCK_M;
+  const dim3 grid((unsigned)m_tiles * (unsigned)nh * (unsigned)S);
   k<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, out, bt, bt_stride, cu_q, seq_lens, nh, nkv, log2ps, scale_log2,
-                                         window, skip_single, err);
+                                         window, skip_single, m_tiles, err);
   return osb_last_error();
 }
 }  // namespace
