@@ -2,15 +2,16 @@
 //
 // One CTA = 128 query rows of one (request, query head). Keys and values stream through shared
 // memory in tiles of 128 keys, fetched page by page with TMA (128-byte swizzle) straight from the
-// cache pages. S = Q K^T and O += P V are tcgen05.mma instructions issued by one thread; S (two
-// buffers) and O live in tensor memory. Four softmax warps (one thread per query row) read a row
+// cache pages. S = Q K^T and O += P V are tcgen05.mma instructions, each kind issued by one thread of a
+// warp of its own; S (three buffers) and O live in tensor memory. Four softmax warps (one thread per query row) read a row
 // of S with tcgen05.ld into registers, keep the running maximum and sum in fp32 and write P as
 // bf16 back into tensor memory over the S it came from (two values per 32-bit column), from where
 // the second MMA takes it as its A operand: P never touches shared memory, and the softmax of
-// tile t+1 runs while the tensor cores work on P V of tile t and Q K^T of tile t+2. O is rescaled
+// tile t+1 runs while the tensor cores work on P V of tile t and Q K^T of the tiles after. O is rescaled
 // in tensor memory only when a row's maximum has grown by more than 2^8 since the offset in use
 // was set (the offset stays consistent, so the result is exact up to rounding).
-// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax and epilogue. All mbarrier
+// Roles: warp 0 TMA producer of Q and keys, warp 6 of values, warp 1 issues Q K^T (up to three tiles ahead),
+// warp 7 issues P V, warps 2-5 softmax and epilogue. All mbarrier
 // waits are bounded; on a time-out the CTA records a code in *err, waits for its copies in flight,
 // frees its tensor memory and returns.
 //
@@ -23,10 +24,19 @@ namespace {
 using namespace tc;
 
 constexpr int BLOCK_M = 128, TILE_N = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 256;
+constexpr int STAGES = 3;  // K tiles, V tiles and S buffers in flight: tile t uses number t % STAGES of each
 constexpr int ATOM_BYTES = 128 * 128;  // 128 rows of 128 bytes
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
+
+#ifdef OSB_ATTN_TIMELINE
+// Development aid (not compiled into the library): clock stamps of block 0, 16 slots per key tile.
+__device__ long long g_timeline[64 * 16];
+#define TL(t, i) do { if (blockIdx.x == 0 && (t) < 64) g_timeline[(t) * 16 + (i)] = clock64(); } while (0)
+#else
+#define TL(t, i) do { } while (0)
+#endif
 
 template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
@@ -38,13 +48,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
   constexpr int Q_BYTES = NA * ATOM_BYTES;    // [atom][128 rows][128 B]
   constexpr int KV_BYTES = NA * ATOM_BYTES;   // one K or V tile: [atom][128 keys][128 B]
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t S_COL0 = 0, O_COL = 256;  // S buffers at columns 0 and 128, P over the first 64 columns of its S
+  constexpr uint32_t S_COL0 = 0, O_COL = STAGES * TILE_N;  // S buffers of 128 columns, P over the first 64 of its S; then O
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* q_smem = base;
-  unsigned char* k_smem = q_smem + Q_BYTES;            // 2 stages
-  unsigned char* v_smem = k_smem + 2 * KV_BYTES;       // 2 stages
-  __shared__ uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], pv_done;
+  unsigned char* k_smem = q_smem + Q_BYTES;                  // STAGES tiles
+  unsigned char* v_smem = k_smem + STAGES * KV_BYTES;     // STAGES tiles
+  // s_full[i]: Q K^T of a tile complete (S may be read, the K tile may be overwritten);
+  // pv_done[i]: P V of a tile complete (the V tile and the S buffer that held P may be overwritten, O may be read)
+  __shared__ uint64_t q_full, k_full[STAGES], v_full[STAGES], s_full[STAGES], p_full[STAGES], pv_done[STAGES];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -74,21 +86,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
   if (threadIdx.x == 0) {
     abort_flag = 0;
     mbar_init(&q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < STAGES; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(&pv_done, 1);
     mbar_init_fence();
   }
-  // stale shared memory may hold anything; rows of a partial last tile are never written by TMA
-  for (int i = threadIdx.x * 16; i < 4 * KV_BYTES; i += NUM_THREADS * 16)
-    *reinterpret_cast<uint4*>(k_smem + i) = make_uint4(0, 0, 0, 0);
-  fence_async_smem();
   if (warp == 1) tmem_alloc(&tmem_slot, TMEM_COLS);
   fence_before();
   __syncthreads();
@@ -96,67 +102,74 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
   const uint32_t tmem = tmem_slot;
   volatile int* vabort = &abort_flag;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------------ TMA producers: warp 0 keys (and Q), warp 6 values
+    const int which = warp == 0 ? 0 : 1;
+    if (which == 0 && lane == 0) {
       mbar_expect_tx(&q_full, Q_BYTES);
       for (int a = 0; a < NA; ++a) tma_load_2d(q_smem + a * ATOM_BYTES, &map_q, &q_full, h * HD + a * 64, q0 + m0);
     }
+    unsigned char* tiles = which ? v_smem : k_smem;
+    const CUtensorMap* map = which ? &map_v : &map_k;
+    // lane = (box b, atom a) of a tile: boxes * NA <= 32, a box being at least 8 keys
+    const int b = lane / NA, a = lane - b * NA;
+    auto page_of = [&](int t) -> int {
+      const int key = (tile_begin + t) * TILE_N + b * box_rows;
+      return (t < n_tiles && b < n_boxes && key <= p_last) ? bt[key >> log2ps] : -1;
+    };
     int issued = 0;
+    int page = page_of(0);
     for (int t = 0; t < n_tiles; ++t) {
-      const int st = t & 1;
-      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      const int st = t % STAGES;
+      const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
       const int key0 = (tile_begin + t) * TILE_N;
+      const int next_page = page_of(t + 1);  // in flight while this tile's copies are issued
       // whole boxes (pages) up to the last key this CTA may look at; a box that starts beyond it is skipped
       const int boxes = min(n_boxes, (p_last - key0) / box_rows + 1);
-      int page = 0, in_page = 0, off = 0, a = 0;
-      const bool mine = lane < boxes * NA;  // boxes * NA <= 32: a box is at least 8 keys
-      if (mine) {
-        const int b = lane / NA;
-        a = lane - b * NA;
-        const int key = key0 + b * box_rows;
-        page = bt[key >> log2ps];
-        in_page = key & (ps - 1);
-        off = st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128;
-      }
-      for (int which = 0; which < 2; ++which) {  // keys first: Q K^T is waiting for them
-        uint64_t* empty = which ? &v_empty[st] : &k_empty[st];
-        uint64_t* full = which ? &v_full[st] : &k_full[st];
-        if (lane == 0) {
-          if (!mbar_wait(empty, ph ^ 1u, vabort)) {
-            if (!*vabort) atomicExch(err, 111);
-            *vabort = 1;
-          } else {
-            mbar_expect_tx(full, (uint32_t)(boxes * NA * box_rows * 128));
-          }
+      uint64_t* empty = which ? &pv_done[st] : &s_full[st];
+      uint64_t* full = which ? &v_full[st] : &k_full[st];
+      if (lane == 0) {
+        if (!mbar_wait(empty, ph ^ 1u, vabort)) {
+          if (!*vabort) atomicExch(err, 111);
+          *vabort = 1;
+        } else {
+          mbar_expect_tx(full, (uint32_t)(boxes * NA * box_rows * 128));
+          TL(t, which);  // 0: keys may be loaded, 1: values may be loaded
         }
-        __syncwarp();
-        if (*vabort) break;
-        if (mine) tma_load_4d((which ? v_smem : k_smem) + off, which ? &map_v : &map_k, full, a * 64, in_page, kvh, page);
       }
+      __syncwarp();
       if (*vabort) break;
+      if (lane < boxes * NA)
+        tma_load_4d(tiles + st * KV_BYTES + a * ATOM_BYTES + b * box_rows * 128, map, full, a * 64,
+                    (key0 + b * box_rows) & (ps - 1), kvh, page);
+      page = next_page;
       issued = t + 1;
     }
     if (*vabort && lane == 0) {
-      for (int t = max(0, issued - 2); t < issued; ++t) {
-        const uint32_t ph = (uint32_t)(t >> 1) & 1u;
-        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&k_full[t & 1], ph); ++w) {
-        }
-        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&v_full[t & 1], ph); ++w) {
+      for (int t = max(0, issued - STAGES); t < issued; ++t) {
+        const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
+        uint64_t* full = which ? &v_full[t % STAGES] : &k_full[t % STAGES];
+        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(full, ph); ++w) {
         }
       }
-      for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&q_full, 0); ++w) {
-      }
+      if (which == 0)
+        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&q_full, 0); ++w) {
+        }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ issuer of S = Q K^T, up to STAGES tiles ahead
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(BLOCK_M, TILE_N, 0, 0);
-      constexpr uint32_t idesc_o = make_idesc(BLOCK_M, HD, 0, 1);  // B = V: N (head dim) contiguous
       bool ok = mbar_wait(&q_full, 0, vabort);
-      auto issue_s = [&](int t) -> bool {
-        const int st = t & 1;
-        if (!mbar_wait(&k_full[st], (uint32_t)(t >> 1) & 1u, vabort)) return false;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        const int st = t % STAGES;
+        const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
+        // the keys have landed, and the product that read P out of this S buffer (tile t - STAGES) has completed
+        if (!mbar_wait(&k_full[st], ph, vabort) || !mbar_wait(&pv_done[st], ph ^ 1u, vabort)) {
+          ok = false;
+          break;
+        }
+        TL(t, 2);
         fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -165,17 +178,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           umma_bf16(tmem + S_COL0 + (uint32_t)(st * TILE_N), ad, bd, idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
-        umma_commit(&k_empty[st]);
-        return true;
-      };
-      for (int t = 0; t < 2 && t < n_tiles && ok; ++t) ok = issue_s(t);
+        TL(t, 11);
+      }
+      if (!ok) {
+        if (!*vabort) atomicExch(err, 112);
+        *vabort = 1;
+      }
+    }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------ issuer of O += P V
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = make_idesc(BLOCK_M, HD, 0, 1);  // B = V: N (head dim) contiguous
+      bool ok = true;
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(&p_full[st], (uint32_t)(t >> 1) & 1u, vabort) ||
-            !mbar_wait(&v_full[st], (uint32_t)(t >> 1) & 1u, vabort)) {
+        const int st = t % STAGES;
+        const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
+        TL(t, 4);
+        if (!mbar_wait(&p_full[st], ph, vabort) || !mbar_wait(&v_full[st], ph, vabort)) {
           ok = false;
           break;
         }
+        TL(t, 3);
         fence_after();
         const uint32_t p_tmem = tmem + S_COL0 + (uint32_t)(st * TILE_N);
 #pragma unroll
@@ -183,23 +206,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           const uint64_t bd = desc_mnmajor(v_smem + st * KV_BYTES, ATOM_BYTES) + (uint64_t)(ks * (16 * 128 / 16));
           umma_bf16_ts(tmem + O_COL, p_tmem + (uint32_t)(ks * 8), bd, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&v_empty[st]);
-        umma_commit(&pv_done);
-        if (t + 2 < n_tiles) {
-          // the S buffer of tile t+2 still holds P of tile t until that product has completed
-          if (!mbar_wait(&pv_done, (uint32_t)t & 1u, vabort)) {
-            ok = false;
-            break;
-          }
-          ok = issue_s(t + 2);
-        }
+        umma_commit(&pv_done[st]);
+        TL(t, 9);
       }
       if (!ok) {
         if (!*vabort) atomicExch(err, 112);
         *vabort = 1;
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------------ softmax and epilogue: warps 2..5
     const int qd = warp & 3;             // TMEM lane quarter of this warp
     const int r = qd * 32 + lane;        // query row of this thread
@@ -209,19 +224,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
     float m_used = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
-      const int st = t & 1;
-      if (!mbar_wait(&s_full[st], (uint32_t)(t >> 1) & 1u, vabort)) ok = false;
+      const int st = t % STAGES;
+      if (!mbar_wait(&s_full[st], (uint32_t)(t / STAGES) & 1u, vabort)) ok = false;
       if (!__all_sync(0xffffffffu, ok)) {
         ok = false;
         break;
       }
       fence_after();
+      if (threadIdx.x == 64) TL(t, 5);  // S there
       const int key0 = (tile_begin + t) * TILE_N;
       const uint32_t s_addr = tmem + lane_addr + S_COL0 + (uint32_t)(st * TILE_N);
       uint32_t v[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + (uint32_t)(c * 32), v[c]);
       tmem_ld_wait();
+      if (threadIdx.x == 64) TL(t, 6);  // S in registers
       // a tile wholly below the diagonal and inside every row's window needs no mask
       const bool unmasked = key0 + TILE_N - 1 <= p_first && key0 >= lo_last;
       if (!unmasked) {
@@ -248,7 +265,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       const float alpha = (grow && m_used != -INFINITY) ? ex2_approx(m_used - m_new) : 1.0f;
       if (t > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
         // O belongs to the tensor cores until the product of the tile before has completed
-        if (!mbar_wait(&pv_done, (uint32_t)(t - 1) & 1u, vabort)) ok = false;
+        if (!mbar_wait(&pv_done[(t - 1) % STAGES], (uint32_t)((t - 1) / STAGES) & 1u, vabort)) ok = false;
         if (!__all_sync(0xffffffffu, ok)) {
           ok = false;
           break;
@@ -285,18 +302,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       }
       tmem_st32(s_addr + 32u, v[1]);
       l_run += sum0 + sum1;
-      // keys at and beyond the request's length lie in the loaded pages but hold whatever was there before:
-      // their P is 0, and 0 x (Inf or NaN) must not reach O, so their V rows are cleared
-      {
+      // The last tile may end before its 128 keys do: rows of the V tile from the first key that was
+      // not loaded (shared memory never written, or an older tile) or that lies at or beyond the request's
+      // length (whatever the page held before) have P = 0, and 0 x (Inf or NaN) must not reach O: clear them.
+      if (t == n_tiles - 1) {
         const int loaded = min(n_boxes, (p_last - key0) / box_rows + 1) * box_rows;
-        const int stale = kv_len - key0;
-        if (stale < loaded) {
-          if (!mbar_wait(&v_full[st], (uint32_t)(t >> 1) & 1u, vabort)) ok = false;
+        const int first_bad = min(kv_len - key0, loaded);
+        if (first_bad < TILE_N) {
+          if (!mbar_wait(&v_full[st], (uint32_t)(t / STAGES) & 1u, vabort)) ok = false;
           if (!__all_sync(0xffffffffu, ok)) {
             ok = false;
             break;
           }
-          if (r >= stale && r < loaded)
+          if (r >= first_bad)
             for (int a = 0; a < NA; ++a)
 #pragma unroll
               for (int c = 0; c < 8; ++c)
@@ -304,14 +322,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           fence_async_smem();
         }
       }
+      if (threadIdx.x == 64) TL(t, 7);  // P computed
       tmem_st_wait();
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[st]);
+      if (threadIdx.x == 64) TL(t, 8);  // P handed over
     }
     // epilogue: O / l
     if (ok) {
-      if (!mbar_wait(&pv_done, (uint32_t)(n_tiles - 1) & 1u, vabort)) ok = false;
+      if (!mbar_wait(&pv_done[(n_tiles - 1) % STAGES], (uint32_t)((n_tiles - 1) / STAGES) & 1u, vabort)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -353,7 +373,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int log2ps, float scale_log2, int window,
            int max_q_len, int skip_single, int* err, cudaStream_t stream) {
   // at least 120 KB so that one CTA is resident per SM: each takes all 512 tensor-memory columns
-  constexpr size_t need = (size_t)(HD / 64) * ATOM_BYTES * 5 + 1024;
+  constexpr size_t need = (size_t)(HD / 64) * ATOM_BYTES * (1 + 2 * STAGES) + 1024;
   constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
   auto k = attn_prefill_tc_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -365,6 +385,12 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   return osb_last_error();
 }
 }  // namespace
+
+#ifdef OSB_ATTN_TIMELINE
+OSB_API int osb_attn_timeline(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_timeline, sizeof(long long) * (size_t)n);
+}
+#endif
 
 // out [T, nh*hd] bf16; q = the first nh*hd columns of rows of q_row_stride elements; caches
 // [pages, nkv, page_size, hd] bf16. Head sizes 64 and 128, page sizes that are powers of two from 8
