@@ -191,16 +191,34 @@ def run_ours(args):
 
     # ------------------------------------------------------------------ decode through the step function
     def decode_run(B, steps, warmup, sample_clocks=False):
+        """Decode steps through the step function, the way the engine drives it: the sampled tokens stay on
+        the device for the next step's embedding lookup and are read on the host one step later, so the
+        host's planning of step t+1 overlaps the device's work on step t. Every step copies its metadata
+        from pinned host memory and brings its tokens back to the host."""
         rids = [f"d{B}_{i}" for i in range(B)]
+        sampler = Sampler(SEED)
         with torch.inference_mode():
-            last = []
             for r in rids:
                 runner.start_request(r)
-                lg = runner.step([StepEntry(r, new_prompt(CONTEXT), want=[CONTEXT - 1])])
-                last.append(int(K.sample(lg, None, None).item()))
-            for _ in range(warmup):
-                lg = runner.step([StepEntry(r, [t], want=[0]) for r, t in zip(rids, last)])
-                last = K.sample(lg, None, None).tolist()
+                lg = runner.step([StepEntry(r, new_prompt(CONTEXT), want=[CONTEXT - 1])], copy_logits=False)
+                sampler.sample_async(lg, None, runner.last_token, runner.logit_slots).result()
+            entries = [StepEntry(r, [0], want=[0], from_device=True) for r in rids]
+
+            def launch():
+                lg = runner.step(entries, copy_logits=False)
+                return sampler.sample_async(lg, None, runner.last_token, runner.logit_slots)
+
+            def run(n):
+                prev, got = None, 0
+                for _ in range(n):
+                    h = launch()
+                    if prev is not None:
+                        got += len(prev.result())
+                    prev = h
+                got += len(prev.result())
+                return got
+
+            run(warmup)
             torch.cuda.synchronize()
             clocks = ClockSampler() if sample_clocks else None
             if clocks:
@@ -211,12 +229,11 @@ def run_ours(args):
             torch.cuda.synchronize()
             torch.cuda.nvtx.range_push("timed_decode")
             e0.record()
-            for _ in range(steps):
-                lg = runner.step([StepEntry(r, [t], want=[0]) for r, t in zip(rids, last)])
-                last = K.sample(lg, None, None).tolist()
+            got = run(steps)
             e1.record()
             torch.cuda.synchronize()
             torch.cuda.nvtx.range_pop()
+            assert got == steps * B
             ms = e0.elapsed_time(e1) / steps
             launches = K.launches - l0
             ck = clocks.stop() if clocks else None
@@ -248,22 +265,18 @@ def run_ours(args):
         for i in range(args.batch if args.only == "all" else 0):
             eng.add_request(Request(prompt=new_prompt(CONTEXT),
                                     sampling=SamplingParams(max_new_tokens=n_new, ignore_eos=True)))
-        while any(s.num_output_tokens < 1 + args.warmup for s in eng.sequences()):
+        while any(s.num_streamed < 1 + args.warmup for s in eng.sequences()):
             eng.step()
         torch.cuda.synchronize()
         t1 = time.perf_counter()
-        n_steps = 0
+        n_steps = e2e_tokens = 0
         while eng.has_unfinished():
-            eng.step()
+            e2e_tokens += sum(len(d.new_token_ids) for d in eng.step())     # tokens that reached the host
             n_steps += 1
         torch.cuda.synchronize()
         e2e_s = max(time.perf_counter() - t1, 1e-9)
-    e2e_tokens = n_steps * args.batch
-    # per step: token ids, cu_q, seq_lens, tok_seq, slots, positions(3), pos_mode, logit rows, block table, slot map
-    bt_w = -(-(CONTEXT + NEW_TOKENS) // 16)
-    h2d = 4 * (args.batch * (1 + 1 + 1 + 1 + 3 + 1 + 1 + bt_w + 1) + 1)
-    e2e = {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": 4 * args.batch, "steps": n_steps}
+    e2e = {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": runner.last_h2d_bytes,
+           "d2h_bytes_per_step": 4 * args.batch, "steps": n_steps, "tokens": e2e_tokens}
 
     line = {
         "metric": "decode tokens/s (Qwen2-VL-2B text decoder, batch %d, 2048-token contexts)" % args.batch,

@@ -4,9 +4,12 @@
 
 template <typename TT, typename OT>
 __global__ void embed_lookup_kernel(OT* __restrict__ out, const TT* __restrict__ table,
-                                    const int* __restrict__ ids, int H, int V, int* __restrict__ err) {
+                                    const int* __restrict__ ids, const int* __restrict__ src_slots,
+                                    const int* __restrict__ last_token, int H, int V, int* __restrict__ err) {
   const int t = blockIdx.x;
-  const int id = ids[t];
+  // a token that was sampled on the device and has not been to the host yet is taken from its request's slot
+  const int slot = src_slots ? src_slots[t] : -1;
+  const int id = slot >= 0 ? last_token[slot] : ids[t];
   const bool ok = (id >= 0 && id < V);
   if (!ok && threadIdx.x == 0) atomicExch(err, 1);
   const TT* src = table + (size_t)(ok ? id : 0) * H;
@@ -27,16 +30,20 @@ __global__ void scatter_rows_kernel(OT* __restrict__ out, const int* __restrict_
     out[(size_t)row * H + i] = from_f32<OT>(to_f32(vals[(size_t)r * H + i]));
 }
 
-// out[T,H] = table[ids]; an id outside [0,V) sets *err = 1 and writes zeros.
+// out[T,H] = table[ids]; an id outside [0,V) sets *err = 1 and writes zeros. With src_slots [T] and
+// last_token given, token t is last_token[src_slots[t]] where src_slots[t] >= 0 (the caller keeps the
+// slots inside last_token).
 OSB_API int osb_embed_lookup(void* out, int out_dtype, const void* table, int table_dtype, const int* ids,
-                             int T, int H, int V, int* err, cudaStream_t stream) {
+                             const int* src_slots, const int* last_token, int T, int H, int V, int* err,
+                             cudaStream_t stream) {
   if (T <= 0) return OSB_OK;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   return osb_dispatch(table_dtype, [&](auto tt) {
     typedef OSB_T(tt) TT;
     return osb_dispatch(out_dtype, [&](auto ot) {
       typedef OSB_T(ot) OT;
-      embed_lookup_kernel<TT, OT><<<T, threads, 0, stream>>>((OT*)out, (const TT*)table, ids, H, V, err);
+      embed_lookup_kernel<TT, OT><<<T, threads, 0, stream>>>((OT*)out, (const TT*)table, ids, src_slots, last_token, H, V,
+                                                             err);
       return osb_last_error();
     });
   });

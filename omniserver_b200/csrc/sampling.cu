@@ -51,7 +51,8 @@ __device__ int block_argmax(const float* row, int V, float* sv, int* si) {
 // One block per row. temperature[r] <= 0 means greedy for that row.
 __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
                                                          const float* __restrict__ temperature,
-                                                         const float* __restrict__ uniform, int V) {
+                                                         const float* __restrict__ uniform, int V,
+                                                         int* __restrict__ keep, const int* __restrict__ keep_at) {
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ float part[THREADS];
@@ -61,7 +62,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
   const float temp = temperature ? temperature[r] : 0.0f;
   const int amax = block_argmax(row, V, sv, si);
   if (!(temp > 0.0f)) {
-    if (threadIdx.x == 0) out[r] = amax;
+    if (threadIdx.x == 0) {
+      out[r] = amax;
+      if (keep) keep[keep_at[r]] = amax;
+    }
     return;
   }
   const float mx = row[amax];
@@ -102,7 +106,11 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ out, 
     atomicMax(&chosen, pick);
   }
   __syncthreads();
-  if (threadIdx.x == 0) out[r] = chosen >= 0 ? chosen : amax;
+  if (threadIdx.x == 0) {
+    const int tok = chosen >= 0 ? chosen : amax;
+    out[r] = tok;
+    if (keep) keep[keep_at[r]] = tok;
+  }
 }
 
 // Greedy over many CTAs: each block takes a slice of the row, the last step combines the slices.
@@ -162,7 +170,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(float* __restrict__
   }
 }
 
-__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const int* __restrict__ pi) {
+__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const int* __restrict__ pi,
+                                    int* __restrict__ keep, const int* __restrict__ keep_at) {
   const int r = blockIdx.x, lane = threadIdx.x;
   float bv = pv[r * ARGMAX_SLICES + lane];
   int bi = pi[r * ARGMAX_SLICES + lane];
@@ -172,28 +181,34 @@ __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restri
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
     argmax_combine(bv, bi, ov, oi);
   }
-  if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
+  if (lane == 0) {
+    const int tok = bi == 0x7fffffff ? 0 : bi;
+    out[r] = tok;
+    if (keep) keep[keep_at[r]] = tok;
+  }
 }
 }  // namespace
 
 // Greedy for all rows with the row spread over 32 CTAs. scratch: R*32 floats and R*32 ints.
-OSB_API int osb_argmax(int* out, const float* logits, float* scratch_v, int* scratch_i, int R, int V,
-                       cudaStream_t stream) {
+// keep/keep_at (may be null): the token of row r is also stored at keep[keep_at[r]], from where the next
+// step's embedding lookup can take it without a trip to the host.
+OSB_API int osb_argmax(int* out, const float* logits, float* scratch_v, int* scratch_i, int R, int V, int* keep,
+                       const int* keep_at, cudaStream_t stream) {
   if (R <= 0) return OSB_OK;
   if (V <= 0) return OSB_ERR_BAD_SHAPE;
   static_assert(ARGMAX_SLICES == 32, "the final step is one warp");
   argmax_partial_kernel<<<dim3(ARGMAX_SLICES, R), 256, 0, stream>>>(scratch_v, scratch_i, logits, V);
   int rc = osb_last_error();
   if (rc) return rc;
-  argmax_final_kernel<<<R, 32, 0, stream>>>(out, scratch_v, scratch_i);
+  argmax_final_kernel<<<R, 32, 0, stream>>>(out, scratch_v, scratch_i, keep, keep_at);
   return osb_last_error();
 }
 
 // out[R] int32; logits [R,V] fp32; temperature/uniform [R] fp32 (temperature may be null: all greedy).
 OSB_API int osb_sample(int* out, const float* logits, const float* temperature, const float* uniform, int R, int V,
-                       cudaStream_t stream) {
+                       int* keep, const int* keep_at, cudaStream_t stream) {
   if (R <= 0) return OSB_OK;
   if (V <= 0) return OSB_ERR_BAD_SHAPE;
-  sample_kernel<<<R, THREADS, 0, stream>>>(out, logits, temperature, uniform, V);
+  sample_kernel<<<R, THREADS, 0, stream>>>(out, logits, temperature, uniform, V, keep, keep_at);
   return osb_last_error();
 }

@@ -16,10 +16,24 @@ import torch
 
 from ..config import EngineConfig, resolve, resolve_dir
 from ..config.model_config import read_config_dict
-from ..sampling import Sampler
+from ..sampling import SampleHandle, Sampler
 from .request import Request, SamplingParams, Sequence, Status
 from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput
 from .step import ModelRunner, StepEntry
+
+
+#: stands in ``Sequence.output_token_ids`` for a token that has been sampled on the device but not read yet
+PENDING_TOKEN = -1
+
+
+@dataclass
+class _InFlight:
+    """A launched step whose tokens have not been read yet."""
+
+    handle: SampleHandle
+    wanting: List[Sequence]      # row i of the sampled tokens belongs to wanting[i] ...
+    fill_at: List[int]           # ... and goes to this place of its output_token_ids
+    seqs: List[Sequence]         # every sequence that took part
 
 
 @dataclass
@@ -67,7 +81,7 @@ def build_runner(model_dir: Optional[str] = None, engine_config: Optional[Engine
 
 class LLMEngine:
     def __init__(self, runner: ModelRunner, sched_config: Optional[SchedulerConfig] = None, seed: int = 0,
-                 eos_token_id: Optional[int] = None, detokenize=None):
+                 eos_token_id: Optional[int] = None, detokenize=None, overlap: Optional[bool] = None):
         self.runner = runner
         self.scheduler = Scheduler(sched_config or SchedulerConfig(), runner.cache,
                                    on_admit=lambda s: runner.start_request(s.request_id, s.rope_delta),
@@ -78,7 +92,10 @@ class LLMEngine:
         self._detokenize = detokenize
         self._seqs: Dict[str, Sequence] = {}
         self._history: Dict[str, Sequence] = {}
-        self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        #: launch step t+1 before reading the tokens of step t (see ``step``); on by default on a GPU
+        self.overlap = (runner.device.type == "cuda") if overlap is None else bool(overlap)
+        self._pending: Optional[_InFlight] = None
+        self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "overlapped_steps": 0}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -111,53 +128,117 @@ class LLMEngine:
         self.scheduler.abort(request_id)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._pending is not None
 
     # ------------------------------------------------------------------ the step (omniserve/engine.py:53-84)
     def step(self) -> List[StepDelta]:
-        out = self.scheduler.schedule()
+        """Schedules and launches one step and returns what has become known since the last call.
+
+        With ``overlap`` the host does not wait for the step it has just launched: sampled tokens stay
+        on the device for the next step's embedding lookup (``StepEntry.from_device``) and are read one
+        call later, so that scheduling and launching step t+1 overlaps the device's work on step t.
+        That is done only while every running request decodes, nothing waits for admission and no
+        preemption can happen; otherwise the step in flight is read before the next is scheduled.
+        A request that ends on a stop token is found out one step late; the token computed for it
+        meanwhile is dropped."""
         deltas: List[StepDelta] = []
+        pend = self._pending
+        if pend is not None and not (self.overlap and self._steady_decode()):
+            deltas += self._finalize(pend)
+            pend = self._pending = None
+        out = self.scheduler.schedule()
         self.counters["preemptions"] += len(out.preempted)
         for seq in out.aborted:
             self._seqs.pop(seq.request_id, None)
             deltas.append(StepDelta(seq.request_id, [], True))
-        if out.entries:
-            entries = []
-            wanting: List[Sequence] = []
-            for e in out.entries:
-                seq = e.seq
-                stop = e.start + e.count
-                rows = vals = None
-                req = seq.request
-                if req.embed_rows is not None and e.start < seq.num_prompt_tokens:
-                    pick = [i for i, r in enumerate(req.embed_rows) if e.start <= r < stop]
-                    if pick:
-                        rows = [req.embed_rows[i] - e.start for i in pick]
-                        vals = req.embed_values[pick]
-                entries.append(StepEntry(seq.request_id, seq.tokens(e.start, stop),
-                                         want=[e.count - 1] if e.wants_logits else [],
-                                         positions=seq.positions_for(e.start, stop), embed_rows=rows, embed_values=vals))
-                if e.wants_logits:
-                    wanting.append(seq)
-                self.counters["decode_tokens" if e.is_decode else "prefill_tokens"] += e.count
-            logits = self.runner.step(entries)
-            new_tokens = self.sampler.sample(logits, wanting)
-            for e in out.entries:
-                e.seq.num_computed += e.count
-                e.seq.scheduled = 0
-            for seq, tok in zip(wanting, new_tokens):
-                seq.append_token(tok)
-                seq.maybe_finish()
-            for e in out.entries:
-                seq = e.seq
-                new_ids = seq.output_token_ids[seq.num_streamed:]
-                if new_ids:
-                    seq.num_streamed = seq.num_output_tokens
-                    text = self._detokenize(new_ids) if self._detokenize else ""
-                    deltas.append(StepDelta(seq.request_id, list(new_ids), seq.status != Status.RUNNING, text))
+        new = self._launch(out) if out.entries else None
+        if pend is not None:
+            self.counters["overlapped_steps"] += 1 if new is not None else 0
+            deltas += self._finalize(pend)
+        self._pending = new
+        if new is not None and not self.overlap:
+            deltas += self._finalize(new)
+            self._pending = None
         self.counters["steps"] += 1
         for seq in self.scheduler.free_finished():
             self._seqs.pop(seq.request_id, None)
+        return deltas
+
+    def _steady_decode(self) -> bool:
+        """Whether the next step can be scheduled before the tokens of the step in flight are known."""
+        sch = self.scheduler
+        if sch.waiting:
+            return False
+        live = [s for s in sch.running if s.status == Status.RUNNING]
+        if not all(s.is_decoding for s in live):
+            return False
+        free = self.runner.cache.free_pages()
+        return not free or min(free) >= len(live)     # nobody can run out of pages: no preemption
+
+    def _launch(self, out: SchedulerOutput) -> "_InFlight":
+        entries = []
+        wanting: List[Sequence] = []
+        for e in out.entries:
+            seq = e.seq
+            stop = e.start + e.count
+            rows = vals = None
+            req = seq.request
+            if req.embed_rows is not None and e.start < seq.num_prompt_tokens:
+                pick = [i for i, r in enumerate(req.embed_rows) if e.start <= r < stop]
+                if pick:
+                    rows = [req.embed_rows[i] - e.start for i in pick]
+                    vals = req.embed_values[pick]
+            toks = seq.tokens(e.start, stop)
+            from_device = e.count == 1 and toks[0] == PENDING_TOKEN
+            if from_device:
+                toks = [0]
+            elif PENDING_TOKEN in toks:
+                raise RuntimeError(f"request {seq.request_id!r}: a token still on the device is needed on the host")
+            entries.append(StepEntry(seq.request_id, toks, want=[e.count - 1] if e.wants_logits else [],
+                                     positions=seq.positions_for(e.start, stop), embed_rows=rows, embed_values=vals,
+                                     from_device=from_device))
+            if e.wants_logits:
+                wanting.append(seq)
+            self.counters["decode_tokens" if e.is_decode else "prefill_tokens"] += e.count
+        logits = self.runner.step(entries, copy_logits=False)
+        handle = self.sampler.sample_async(logits, wanting, self.runner.last_token,
+                                           self.runner.logit_slots if self.runner.last_token is not None else None)
+        for e in out.entries:
+            e.seq.num_computed += e.count
+            e.seq.scheduled = 0
+        fill_at = []
+        for seq in wanting:
+            fill_at.append(seq.num_output_tokens)
+            seq.append_token(PENDING_TOKEN)
+            seq.maybe_finish()          # by count; a stop token shows when the value is read
+        return _InFlight(handle, wanting, fill_at, [e.seq for e in out.entries])
+
+    def _finalize(self, fl: "_InFlight") -> List[StepDelta]:
+        """Reads the tokens of a launched step (waits for the device) and retires what ended."""
+        for seq, idx, tok in zip(fl.wanting, fl.fill_at, fl.handle.result()):
+            if idx >= seq.num_output_tokens:
+                continue                # the request ended on an earlier token; this one is dropped
+            seq.output_token_ids[idx] = int(tok)
+            if int(tok) in seq.request.sampling.stop_token_ids:
+                del seq.output_token_ids[idx + 1:]
+                if seq.status == Status.RUNNING:
+                    seq.maybe_finish()
+        deltas: List[StepDelta] = []
+        seen = set()
+        for seq in fl.seqs:
+            if id(seq) in seen:
+                continue
+            seen.add(id(seq))
+            outs = seq.output_token_ids
+            known = seq.num_streamed
+            while known < len(outs) and outs[known] != PENDING_TOKEN:
+                known += 1
+            if known > seq.num_streamed:
+                new_ids = outs[seq.num_streamed:known]
+                seq.num_streamed = known
+                text = self._detokenize(new_ids) if self._detokenize else ""
+                done = seq.status != Status.RUNNING and known == len(outs)
+                deltas.append(StepDelta(seq.request_id, list(new_ids), done, text))
         return deltas
 
     def run_until_complete(self) -> Dict[str, List[int]]:

@@ -32,6 +32,9 @@ class StepEntry:
     request: cursor + rope_delta + offset on all axes.
     ``embed_rows``/``embed_values``: places among ``tokens`` whose looked-up embedding is replaced
     by the given rows [len(embed_rows), hidden] (the hook the vision tower's output uses).
+    ``from_device``: the entry brings one token, the one the sampler last kept for this request on
+    the device (``ModelRunner.last_token``); ``tokens[0]`` is only a placeholder. This lets the next
+    step be launched before the host has read the token.
     """
 
     request_id: str
@@ -40,6 +43,7 @@ class StepEntry:
     positions: Optional[np.ndarray] = None
     embed_rows: Optional[Sequence[int]] = None
     embed_values: Optional[torch.Tensor] = None
+    from_device: bool = False
 
 
 class StepContext:
@@ -50,6 +54,8 @@ class StepContext:
         self.act_dtype: torch.dtype = None
         self.T = self.S = self.num_logit_rows = 0
         self.token_ids = self.cu_q = self.seq_lens = self.tok_seq = self.state_slot = None
+        self.token_src: Optional[torch.Tensor] = None      # [T]: slot of last_token to take the id from, or -1
+        self.last_token: Optional[torch.Tensor] = None     # [slots]: the token last sampled for each request
         self.positions = self.pos_mode = self.logit_rows = None
         self.block_tables: List[torch.Tensor] = []
         self.slot_maps: List[torch.Tensor] = []
@@ -59,6 +65,7 @@ class StepContext:
         self.q_lens: List[int] = []
         self.kv_lens: List[int] = []
         self.page_size = 0
+        self.logit_slots: Optional[torch.Tensor] = None    # [wanted rows]: the request slot of each logits row
         self.decode_index: Optional[torch.Tensor] = None   # [S]: index among requests bringing one token, else -1
         self.n_decode = self.n_multi = 0
         self.scratch: Dict[str, torch.Tensor] = {}         # per-step scratch buffers shared by the layers
@@ -103,6 +110,14 @@ class ModelRunner:
         self._graphs: Dict[Any, Dict[str, Any]] = {}
         model.attach_cache(cache.bindings(), cache.shared_state())
         self._has_rope_state = ROPE_STATE in cache.state.fields
+        #: per request slot, the token the sampler last kept on the device (see StepEntry.from_device)
+        self.last_token: Optional[torch.Tensor] = None
+        #: after a step: the request slot of each returned logits row, on the device (for Sampler.sample_async)
+        self.logit_slots: Optional[torch.Tensor] = None
+        self.last_h2d_bytes = 0           # size of the last step's metadata copy
+        if cache.state.tensors or self.device.type == "cuda":
+            with torch.inference_mode(False):
+                self.last_token = torch.zeros(max(cache.state.num_slots, 1), dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ request life
     def start_request(self, request_id: str, rope_delta: int = 0) -> None:
@@ -146,16 +161,23 @@ class ModelRunner:
         cursors = [cache.requests[r].cursor for r in rids]
         kv_lens = [c + n for c, n in zip(cursors, q_lens)]
         token_ids = np.empty(T, dtype=np.int32)
+        tok_src = np.full(T, -1, dtype=np.int32)
         tok_seq = np.empty(T, dtype=np.int32)
         positions = np.zeros((3, T), dtype=np.int32)
         pos_mode = np.ones(S, dtype=np.int32)
         logit_rows: List[int] = []
+        logit_slots: List[int] = []
         ov_rows: List[int] = []
         ov_vals: List[torch.Tensor] = []
         V = self.vocab_size
         for i, e in enumerate(entries):
             a, b = int(cu_q[i]), int(cu_q[i + 1])
             toks = np.asarray(e.tokens, dtype=np.int64)
+            if e.from_device:
+                if b - a != 1:
+                    raise ValueError(f"request {e.request_id!r}: a token taken from the device comes alone")
+                toks = np.zeros(1, dtype=np.int64)
+                tok_src[a] = cache.requests[e.request_id].slot
             if toks.min() < 0 or toks.max() >= V:
                 raise ValueError(f"request {e.request_id!r}: token id outside [0, {V})")
             token_ids[a:b] = toks
@@ -170,6 +192,7 @@ class ModelRunner:
                 if not (0 <= w < b - a):
                     raise ValueError(f"request {e.request_id!r}: wanted place {w} outside its {b - a} tokens")
                 logit_rows.append(a + int(w))
+                logit_slots.append(cache.requests[e.request_id].slot)
             if e.embed_rows is not None and len(e.embed_rows):
                 rows = [int(r) for r in e.embed_rows]
                 if min(rows) < 0 or max(rows) >= b - a:
@@ -190,6 +213,7 @@ class ModelRunner:
             ("tok_seq", tok_seq), ("state_slot", slots), ("positions", positions.reshape(-1)),
             ("pos_mode", pos_mode), ("logit_rows", np.asarray(logit_rows, dtype=np.int32)),
             ("override_rows", np.asarray(ov_rows, dtype=np.int32)), ("decode_index", decode_index),
+            ("token_src", tok_src), ("logit_slots", np.asarray(logit_slots, dtype=np.int32)),
         ]
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
@@ -211,7 +235,9 @@ class ModelRunner:
             rcs = [cache.requests[r] for r in rids]
         except KeyError as k:
             raise KeyError(f"request {k.args[0]!r} was not started") from None
+        from_dev = np.fromiter((e.from_device for e in entries), dtype=bool, count=S)
         token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+        token_ids[from_dev] = 0
         if token_ids.min() < 0 or token_ids.max() >= self.vocab_size:
             raise ValueError(f"token id outside [0, {self.vocab_size})")
         boundary = [rc for rc in rcs if (rc.cursor + rc.reserved) % ps == 0]
@@ -233,11 +259,13 @@ class ModelRunner:
             if (pages < 0).any():
                 raise RuntimeError("a token of this step maps to a page that was given back")
             sms.append(pages * ps + cursors % ps)
+        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=S)
         segs: List[Tuple[str, np.ndarray]] = [
             ("token_ids", token_ids.astype(np.int32)), ("cu_q", ar), ("seq_lens", cursors + 1), ("tok_seq", ar[:S]),
-            ("state_slot", np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=S)),
+            ("state_slot", slots),
             ("positions", np.zeros(3 * S, dtype=np.int32)), ("pos_mode", np.ones(S, dtype=np.int32)),
             ("logit_rows", ar[:S]), ("override_rows", np.zeros(0, dtype=np.int32)), ("decode_index", ar[:S]),
+            ("token_src", np.where(from_dev, slots, -1).astype(np.int32)), ("logit_slots", slots),
         ]
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
@@ -278,6 +306,9 @@ class ModelRunner:
         ctx.max_q_len, ctx.max_kv_len = max(plan["q_lens"]), max(plan["kv_lens"])
         ctx.page_size = self.cache.page_size
         ctx.decode_index = seg("decode_index")
+        if self.last_token is not None:
+            ctx.token_src, ctx.last_token = seg("token_src"), self.last_token
+        ctx.logit_slots = seg("logit_slots")
         ctx.n_decode = plan["n_decode"]
         ctx.n_multi = S - ctx.n_decode
         ctx.scratch = self._scratch
@@ -294,16 +325,21 @@ class ModelRunner:
             hv[o:o + n] = arr
         dev = host.to(self.device, non_blocking=True)
         ctx = self._context(plan, dev, offs)
-        ctx.h2d_bytes = total * 4
+        ctx.h2d_bytes = self.last_h2d_bytes = total * 4
         return ctx
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], copy_logits: bool = True) -> torch.Tensor:
         """Runs the entries as one batch; returns fp32 logits [wanted, vocab] in the order of the
-        entries and of their ``want``. The requests' tokens are in the cache afterwards."""
+        entries and of their ``want``. The requests' tokens are in the cache afterwards.
+
+        Nothing here waits for the device. ``copy_logits=False`` may return a buffer that the next
+        step overwrites: for callers that consume the logits (sample from them) on the same stream
+        before they step again."""
         if self.use_graphs and self._graphable(entries):
-            return self._graph_step(entries)
+            return self._graph_step(entries, copy_logits)
         ctx = self.build_context(entries)
+        self.logit_slots = ctx.logit_slots
         try:
             logits = self.model.forward(ctx)
         except Exception:
@@ -332,7 +368,7 @@ class ModelRunner:
                 return False
         return True
 
-    def _graph_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _graph_step(self, entries: Sequence[StepEntry], copy_logits: bool = True) -> torch.Tensor:
         """A decode step replayed from a CUDA graph: the launch-bound inner loop of generation.
 
         One graph per (batch size, block-table width bucket). The step's metadata goes into a
@@ -347,19 +383,26 @@ class ModelRunner:
         if slot is None:
             offs, total = self._layout(plan["segs"])
             with torch.inference_mode(False):
-                host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+                # two staging buffers in turn: the host may fill one while the copy out of the other waits
+                # behind the step before on the stream
+                hosts = [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
                 dev = torch.zeros(total, dtype=torch.int32, device=self.device)
-            slot = {"offs": offs, "host": host, "dev": dev, "graph": None, "logits": None, "launches": 0,
-                    "copied": torch.cuda.Event()}
+            slot = {"offs": offs, "hosts": hosts, "dev": dev, "graph": None, "logits": None, "launches": 0,
+                    "copied": [torch.cuda.Event(), torch.cuda.Event()], "turn": 0, "used": [False, False]}
             self._graphs[key] = slot
-        else:
-            slot["copied"].synchronize()      # the previous copy out of the pinned buffer has finished
-        hv = slot["host"].numpy()
+        turn = slot["turn"]
+        slot["turn"] = turn ^ 1
+        if slot["used"][turn]:
+            slot["copied"][turn].synchronize()      # the last copy out of this pinned buffer has finished
+        host = slot["hosts"][turn]
+        hv = host.numpy()
         for name, arr in plan["segs"]:
             o, n = slot["offs"][name]
             hv[o:o + n] = arr
-        slot["dev"].copy_(slot["host"], non_blocking=True)
-        slot["copied"].record()
+        slot["dev"].copy_(host, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
+        slot["copied"][turn].record()
+        slot["used"][turn] = True
         try:
             if slot["graph"] is None:
                 ctx = self._context(plan, slot["dev"], slot["offs"])
@@ -383,4 +426,6 @@ class ModelRunner:
                 self.cache.requests[e.request_id].reserved = 0
             raise
         self._after_step(entries)
-        return slot["logits"].clone()
+        o, n = slot["offs"]["logit_slots"]
+        self.logit_slots = slot["dev"][o:o + n]
+        return slot["logits"].clone() if copy_logits else slot["logits"]

@@ -125,14 +125,23 @@ class CudaKernels:
                 raise KernelError("device-side check failed: " + _DEVICE_ERR.get(v, f"code {v}"))
 
     # ------------------------------------------------------------------ embedding
-    def embed_lookup(self, table: torch.Tensor, ids: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    def embed_lookup(self, table: torch.Tensor, ids: torch.Tensor, out_dtype: torch.dtype,
+                     src_slots: Optional[torch.Tensor] = None, last_token: Optional[torch.Tensor] = None
+                     ) -> torch.Tensor:
+        """table[ids]; where ``src_slots[t] >= 0`` the id is ``last_token[src_slots[t]]`` instead (a token
+        sampled on the device that the host has not seen yet)."""
         _cuda_contig("table", table)
         _cuda_contig("ids", ids, torch.int32)
         _check(table.dim() == 2 and ids.dim() == 1, "embed_lookup: table [V,H], ids [T]")
         V, H = table.shape
         T = ids.shape[0]
+        if src_slots is not None:
+            _cuda_contig("src_slots", src_slots, torch.int32)
+            _cuda_contig("last_token", last_token, torch.int32)
+            _check(src_slots.shape == (T,), "embed_lookup: src_slots [T]")
         out = torch.empty((T, H), dtype=out_dtype, device=table.device)
-        rc = self.lib.osb_embed_lookup(_p(out), _dt(out), _p(table), _dt(table), _p(ids), T, H, V,
+        rc = self.lib.osb_embed_lookup(_p(out), _dt(out), _p(table), _dt(table), _p(ids), _p(src_slots),
+                                       _p(last_token if src_slots is not None else None), T, H, V,
                                        _p(self.err_flag(table.device)), self._stream())
         self._ok(rc, "embed_lookup")
         return out
@@ -483,11 +492,19 @@ class CudaKernels:
         return out
 
     # ------------------------------------------------------------------ sampling
-    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor]
-               ) -> torch.Tensor:
-        """Token ids [R] int32: argmax where temperature <= 0, else inverse-CDF draw with the given uniforms."""
+    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
+               keep: Optional[torch.Tensor] = None, keep_at: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Token ids [R] int32: argmax where temperature <= 0, else inverse-CDF draw with the given uniforms.
+        With ``keep`` (int32 [N]) and ``keep_at`` (int32 [R], values in [0, N)) row r's token is also stored
+        at ``keep[keep_at[r]]``."""
         _cuda_contig("logits", logits, torch.float32)
         R, V = logits.shape
+        if keep is not None:
+            _cuda_contig("keep", keep, torch.int32)
+            _cuda_contig("keep_at", keep_at, torch.int32)
+            _check(keep_at.shape == (R,), "sample: keep_at [R]")
+        else:
+            keep_at = None
         if temperature is not None:
             _cuda_contig("temperature", temperature, torch.float32)
             _cuda_contig("uniform", uniform, torch.float32)
@@ -496,11 +513,12 @@ class CudaKernels:
         if temperature is None and V >= 4096:
             sv = torch.empty((R, 32), dtype=torch.float32, device=logits.device)
             si = torch.empty((R, 32), dtype=torch.int32, device=logits.device)
-            rc = self.lib.osb_argmax(_p(out), _p(logits), _p(sv), _p(si), R, V, self._stream())
+            rc = self.lib.osb_argmax(_p(out), _p(logits), _p(sv), _p(si), R, V, _p(keep), _p(keep_at), self._stream())
             self._ok(rc, "argmax")
             self.launches += 1
             return out
-        rc = self.lib.osb_sample(_p(out), _p(logits), _p(temperature), _p(uniform), R, V, self._stream())
+        rc = self.lib.osb_sample(_p(out), _p(logits), _p(temperature), _p(uniform), R, V, _p(keep), _p(keep_at),
+                                 self._stream())
         self._ok(rc, "sample")
         return out
 

@@ -26,7 +26,8 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx: Any) -> torch.Tensor:
         k = ops.kernels()
-        x = k.embed_lookup(self.weight, ctx.token_ids, ctx.act_dtype)
+        x = k.embed_lookup(self.weight, ctx.token_ids, ctx.act_dtype, getattr(ctx, "token_src", None),
+                           getattr(ctx, "last_token", None))
         if ctx.override_rows is not None:
             k.scatter_rows(x, ctx.override_rows, ctx.override_vals)
         return x

@@ -1,2 +1,2 @@
-from .sampler import Sampler
+from .sampler import SampleHandle, Sampler
 from . import rng

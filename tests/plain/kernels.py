@@ -21,8 +21,12 @@ class PlainKernels:
         pass
 
     # -- embedding
-    def embed_lookup(self, table, ids, out_dtype):
-        return table[ids.long()].to(out_dtype)
+    def embed_lookup(self, table, ids, out_dtype, src_slots=None, last_token=None):
+        ids = ids.long()
+        if src_slots is not None:
+            from_slot = src_slots >= 0
+            ids = torch.where(from_slot, last_token[src_slots.clamp(min=0).long()].long(), ids)
+        return table[ids].to(out_dtype)
 
     def scatter_rows(self, x, rows, vals):
         x[rows.long()] = vals.to(x.dtype)
@@ -137,7 +141,13 @@ class PlainKernels:
         return ((g * torch.sigmoid(g)) * u).to(out_dtype)
 
     # -- sampling
-    def sample(self, logits, temperature, uniform):
+    def sample(self, logits, temperature, uniform, keep=None, keep_at=None):
+        out = self._sample(logits, temperature, uniform)
+        if keep is not None:
+            keep[keep_at.long()] = out
+        return out
+
+    def _sample(self, logits, temperature, uniform):
         R = logits.shape[0]
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
         for r in range(R):

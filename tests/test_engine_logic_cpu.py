@@ -95,3 +95,74 @@ def test_decode_plan_equals_general_plan(tmp_path, cpu_kernels):
     for k in ("S", "T", "q_lens", "kv_lens", "bt_widths", "n_logit_rows", "n_decode"):
         assert p1[k] == p2[k], k
     runner.cache.check_invariants()
+
+
+def _engine(model_dir, overlap, max_tokens=1024, page_size=16, **sched):
+    from omniserver_b200 import LLMEngine, SchedulerConfig
+    return LLMEngine(_runner(model_dir, max_tokens, page_size), SchedulerConfig(**sched), seed=5, overlap=overlap)
+
+
+def _greedy_by_plain(cfg, w, prompt, n, stop=()):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(pm.forward(cfg, w, torch.tensor(toks))[-1].argmax())
+        toks.append(nxt)
+        out.append(nxt)
+        if nxt in stop:
+            break
+    return out
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
+def test_overlapped_steps_give_the_same_tokens(name, tmp_path, cpu_kernels):
+    """Launching step t+1 before the tokens of step t are read (they stay on the device for the
+    embedding lookup) changes nothing: same tokens as step-by-step, as the plain model's greedy
+    decoding, with requests that end at different lengths and others that arrive meanwhile."""
+    from omniserver_b200 import Request, SamplingParams
+    d = make_model_dir(tmp_path, name)
+    cfg, w = plain_model(d)
+    prompts = list(_requests(cfg.V, [9, 21, 4, 30], seed=8).values())
+    lens = [12, 5, 9, 7]
+    outs = {}
+    for overlap in (False, True):
+        eng = _engine(d, overlap, max_running=3, max_prefill_tokens=16)
+        ids = [eng.add_request(Request(prompt=p, sampling=SamplingParams(max_new_tokens=n), request_id=f"q{i}"))
+               for i, (p, n) in enumerate(zip(prompts[:3], lens))]
+        got = {i: [] for i in ids}
+        steps = 0
+        while eng.has_unfinished():
+            for dl in eng.step():
+                got[dl.request_id] += dl.new_token_ids
+            steps += 1
+            if steps == 6:      # a late arrival: the engine leaves the overlapped mode to admit it
+                ids.append(eng.add_request(Request(prompt=prompts[3], sampling=SamplingParams(max_new_tokens=lens[3]),
+                                                   request_id="q3")))
+                got["q3"] = []
+            eng.runner.cache.check_invariants()
+        assert all(p == 0 for p in eng.runner.cache.pages_in_use())
+        assert all(-1 not in s.output_token_ids for s in eng.sequences())
+        assert (eng.counters["overlapped_steps"] > 3) == overlap
+        outs[overlap] = got
+    assert outs[True] == outs[False]
+    for i, (p, n) in enumerate(zip(prompts, lens)):
+        assert outs[True][f"q{i}"] == _greedy_by_plain(cfg, w, p, n), f"request {i}"
+
+
+def test_overlapped_steps_and_stop_tokens(tmp_path, cpu_kernels):
+    """A stop token is seen one step late in the overlapped mode: the token computed meanwhile is
+    dropped, the outputs end with the stop token, and the pages come back."""
+    from omniserver_b200 import Request, SamplingParams
+    d = make_model_dir(tmp_path, "tiny_b")
+    cfg, w = plain_model(d)
+    prompts = list(_requests(cfg.V, [7, 13], seed=2).values())
+    free_run = [_greedy_by_plain(cfg, w, p, 10) for p in prompts]
+    stops = [[free_run[0][3]], [free_run[1][6]]]           # the 4th and the 7th token end their requests
+    want = [_greedy_by_plain(cfg, w, p, 10, stop=s) for p, s in zip(prompts, stops)]
+    for overlap in (False, True):
+        eng = _engine(d, overlap)
+        ids = [eng.add_request(Request(prompt=p, sampling=SamplingParams(max_new_tokens=10, stop_token_ids=list(s))))
+               for p, s in zip(prompts, stops)]
+        outs = eng.run_until_complete()
+        assert [outs[i] for i in ids] == want
+        assert [s.output_token_ids for s in eng.sequences()] == want
+        assert all(p == 0 for p in eng.runner.cache.pages_in_use())

@@ -116,3 +116,36 @@ def test_bfloat16_generation_runs_and_mostly_agrees(tmp_path):
         top2 = lg.topk(2).values
         if (top2[0] - top2[1]) > 0.1:
             assert o[0] == ref[0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_and_step_by_step_engines_agree(dtype, tmp_path):
+    """The engine launches a step before it has read the tokens of the one before (they stay on the
+    device for the embedding lookup, also inside the CUDA graphs of decode steps). Same tokens as
+    with a wait after every step; greedy and seeded temperature rows, a stop token, uneven lengths."""
+    from omniserver_b200 import EngineConfig, LLMEngine, Request, SamplingParams, SchedulerConfig
+    d = make_model_dir(tmp_path, "tiny_c", dtype)
+    cfg, w = plain_model(d)
+    prompts = prompts_for(cfg.V, (6, 19, 40, 11), seed=4)
+    outs = {}
+    for overlap in (False, True):
+        with torch.inference_mode():
+            eng = LLMEngine.from_model_dir(d, EngineConfig(dtype=dtype, max_cache_tokens=2048, max_requests=8),
+                                           SchedulerConfig(max_running=4, max_prefill_per_step=4), seed=3)
+            eng.overlap = overlap
+            sps = [SamplingParams(max_new_tokens=40), SamplingParams(max_new_tokens=23, temperature=0.8, seed=9),
+                   SamplingParams(max_new_tokens=31), SamplingParams(max_new_tokens=12, temperature=1.3)]
+            if outs:
+                sps[2].stop_token_ids = [outs[False][2][17]]      # ends the third request at its 18th token
+            ids = [eng.add_request(Request(prompt=p, sampling=sp, request_id=f"o{i}")) for i, (p, sp) in
+                   enumerate(zip(prompts, sps))]
+            res = eng.run_until_complete()
+            assert (eng.counters["overlapped_steps"] > 10) == overlap
+            assert all(p == 0 for p in eng.runner.cache.pages_in_use())
+        outs[overlap] = [res[i] for i in ids]
+    want = [list(o) for o in outs[False]]
+    first = want[2].index(want[2][17])                           # the stop token may have come earlier too
+    want[2] = want[2][:first + 1]
+    assert outs[True] == want
+    if dtype == "float32":
+        assert outs[False][0] == pm.generate(cfg, w, prompts[0], 40)

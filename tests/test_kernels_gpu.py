@@ -47,6 +47,17 @@ def test_embed_lookup_and_scatter(dtype, V, H, T):
     K().check_device_errors()
 
 
+def test_embed_lookup_takes_ids_kept_on_the_device():
+    table = rnd(50, 24)
+    ids = torch.tensor([3, 7, 0, 49, 5], dtype=torch.int32)
+    src = torch.tensor([-1, 2, -1, 0, 5], dtype=torch.int32)
+    last = torch.tensor([11, 0, 13, 0, 0, 48], dtype=torch.int32)
+    got = K().embed_lookup(table.to(DEV), ids.to(DEV), torch.float32, src.to(DEV), last.to(DEV))
+    assert torch.equal(got.cpu(), table[torch.tensor([3, 13, 0, 11, 48])])
+    assert torch.equal(got.cpu(), REF.embed_lookup(table, ids, torch.float32, src, last))
+    K().check_device_errors()
+
+
 def test_embed_lookup_reports_bad_id():
     from omniserver_b200.ops import KernelError
     table = rnd(10, 8)
@@ -529,7 +540,12 @@ def test_sample_greedy_and_temperature(V):
     logits[1, 7] = logits[1, 900 % V] = logits[1].max() + 1   # a tie: the lowest index wins
     got = K().sample(logits.to(DEV), None, None).cpu()
     assert torch.equal(got, REF.sample(logits, None, None))
+    # the tokens can be kept on the device at given places as well
+    keep, at = torch.full((9,), -7, dtype=torch.int32, device=DEV), torch.tensor([4, 0, 8, 1, 6], dtype=torch.int32)
     temps = torch.tensor([0.8, 0.0, 1.5, 0.3, 1.0])
+    for tp, u in ((None, None), (temps.to(DEV), torch.full((R,), 0.37, device=DEV))):
+        ids = K().sample(logits.to(DEV), tp, u, keep, at.to(DEV)).cpu()
+        assert torch.equal(keep.cpu()[at.long()], ids) and (keep.cpu()[[2, 3, 5, 7]] == -7).all()
     for trial in range(8):
         u = torch.rand(R, generator=torch.Generator().manual_seed(trial))
         got = K().sample(logits.to(DEV), temps.to(DEV), u.to(DEV)).cpu()
