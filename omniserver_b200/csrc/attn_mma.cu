@@ -254,6 +254,15 @@ struct FusedRope {
   int rot;
 };
 
+#ifdef OSB_ATTN_TIMELINE
+// Development aid (not compiled into the library): clock stamps of the CTAs of request 0, kv head 0.
+__device__ long long g_decode_timeline[16 * 16];
+#define DTL(i) do { if (blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && blockIdx.x < 16) \
+    g_decode_timeline[blockIdx.x * 16 + (i)] = clock64(); } while (0)
+#else
+#define DTL(i) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------------------------------------
 // Decode: one token per request. grid = (splits, kv heads x head tiles, requests).
 template <int HD_MAX, int STAGES, bool CLUSTER>
@@ -270,7 +279,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   bf16* kvs = qs + 16 * stride;                  // STAGES x (K, V) x [TILE_N][stride]; later the warps' outputs
   const int tile_elems = TILE_N * stride;
 
+  DTL(0);
   pdl_wait();
+  DTL(1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, s = blockIdx.z;
   const int g = nh / nkv;
@@ -317,6 +328,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     __syncthreads();
   }
 
+  DTL(2);
   {  // the group's query rows
     const int cpr = hd >> 3;
     for (int i = tid; i < 16 * cpr; i += NTHREADS) {
@@ -357,6 +369,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     }
     cp_async_wait<STAGES - 1>();
     __syncthreads();
+    if (t < 8) DTL(4 + t);
     const bf16* ks = kvs + st * 2 * tile_elems;
     const bf16* vs = ks + tile_elems;
     if (t == 0) {
@@ -455,6 +468,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   cp_async_wait<0>();
   __syncthreads();
   pdl_trigger();
+  DTL(12);
 
   // merge the four warps (each saw different keys) in warp order: per-warp results of the valid rows
   // go to shared memory (row stride hd + 8 floats: the 64-bit stores of a half-warp hit distinct banks)
@@ -532,7 +546,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     // The splits of one (request, kv head) are the CTAs of one cluster: every CTA merges a share of the
     // output columns over all of them through distributed shared memory, in split order.
     cg::cluster_group cluster = cg::this_cluster();
+    DTL(13);
     cluster.sync();
+    DTL(14);
     const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
     for (int idx = tid * csize + crank; idx < rows * hq; idx += NTHREADS * csize) {
       const int r = idx / hq, d = (idx - r * hq) * 4;
@@ -569,6 +585,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
       *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     }
     cluster.sync();  // nobody's shared memory goes away while another CTA still reads it
+    DTL(15);
     return;
   }
 
@@ -767,6 +784,12 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
 }
 
 // ------------------------------------------------------------------------------------------------
+#ifdef OSB_ATTN_TIMELINE
+OSB_API int osb_attn_decode_timeline(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_decode_timeline, sizeof(long long) * (size_t)n);
+}
+#endif
+
 // Decode attention for callers that cannot allocate (declared in attn_decode_noalloc.h).
 //
 // The split-key decode kernel above needs scratch memory for the splits' partial results. Some
