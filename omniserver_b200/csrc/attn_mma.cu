@@ -280,8 +280,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   const int tile_elems = TILE_N * stride;
 
   DTL(0);
-  pdl_wait();
-  DTL(1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, s = blockIdx.z;
   const int g = nh / nkv;
@@ -303,6 +301,23 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   const int ntiles = active ? (k_end - k_begin + TILE_N - 1) / TILE_N : 0;
   const int* bt = block_table + (size_t)s * bt_stride;
 
+  // Everything read so far was written by the host before the step. When this kernel stores the new key
+  // and value itself (fused rotary form), the tiles of every split but the last do not depend on the
+  // kernel before this one either: their first copies start before the wait for that kernel.
+  const bool early = fr.cos_t != nullptr && split != last_split;
+  auto first_tiles = [&]() {
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+      if (st < ntiles) {
+        bf16* dst = kvs + st * 2 * tile_elems;
+        load_kv_tiles_async(dst, dst + tile_elems, kc, vc, bt, kvh, nkv, log2ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
+      }
+      cp_async_commit();
+    }
+  };
+  if (early) first_tiles();
+  pdl_wait();
+  DTL(1);
   if (fr.cos_t != nullptr && split == last_split && ht == 0) {
     // the new token's key (rotated) and value go into their page before this CTA reads its tiles
     const int slot = fr.slot_map[q0];
@@ -329,23 +344,16 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   }
 
   DTL(2);
-  {  // the group's query rows
+  {  // the group's query rows (plain loads: they must not become a copy group of their own)
     const int cpr = hd >> 3;
     for (int i = tid; i < 16 * cpr; i += NTHREADS) {
       const int r = i / cpr, c = i - r * cpr;
-      const bool valid = r < rows;
-      const bf16* src = valid ? q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * hd + c * 8 : q;
-      cp_async16(qs + r * stride + c * 8, src, valid);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * hd + c * 8);
+      *reinterpret_cast<uint4*>(qs + r * stride + c * 8) = v;
     }
   }
-#pragma unroll
-  for (int st = 0; st < STAGES - 1; ++st) {
-    if (st < ntiles) {
-      bf16* dst = kvs + st * 2 * tile_elems;
-      load_kv_tiles_async(dst, dst + tile_elems, kc, vc, bt, kvh, nkv, log2ps, hd, k_begin + st * TILE_N, k_end, num_pages, tid);
-    }
-    cp_async_commit();
-  }
+  if (!early) first_tiles();
 
   constexpr int KS = HD_MAX / 16;
   const int ks_n = hd >> 4;
