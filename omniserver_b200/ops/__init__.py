@@ -93,6 +93,9 @@ class CudaKernels:
         self.use_tcgen05 = True
         self.decode_clusters = True   # decode attention: merge a request's splits inside a cluster
         self.tc_prefill = True        # prompt attention on tcgen05 where the head size allows (64, 128)
+        # few rows: the norm before a projection can run inside the projection's kernel. Off: measured in a full
+        # decode step it is slower than the two kernels (every CTA re-reads the rows of the residual stream)
+        self.fuse_prenorm = False
         #: Row counts from which the tcgen05 kernel is used (measured on B200 at this model's shapes:
         #: with fewer rows there are too few 128-row tiles to fill 148 SMs and the library's split
         #: kernels win; the fused SiLU*up epilogue pays off earlier because it saves a whole pass)
@@ -276,6 +279,39 @@ class CudaKernels:
                                             M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)), self._stream())
         self._ok(rc, "gemm_tcgen05_bf16")
         return y
+
+    PRENORM_MAX_ROWS, PRENORM_MAX_K = 16, 2048
+
+    def can_linear_prenorm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether ``linear_prenorm`` takes these operands (else: ``add_rmsnorm`` then ``linear``)."""
+        return (self.fuse_prenorm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2
+                and 0 < x.shape[0] <= self.PRENORM_MAX_ROWS and x.shape[1] % 8 == 0
+                and x.shape[1] <= self.PRENORM_MAX_K)
+
+    def linear_prenorm(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                       w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(norm(residual + x) * norm_weight) @ w^T (+ bias) in one kernel for a few rows; returns (y, the
+        new fp32 residual stream, a new tensor: ``residual`` itself is left as it was)."""
+        _cuda_contig("x", x, torch.bfloat16)
+        _cuda_contig("w", w, torch.bfloat16)
+        _cuda_contig("norm_weight", norm_weight)
+        M, Kd = x.shape
+        N = w.shape[0]
+        _check(self.can_linear_prenorm(x, w) and w.shape[1] == Kd and norm_weight.shape == (Kd,),
+               "linear_prenorm: x [M<=16, K<=2048] bf16, w [N,K] bf16, norm_weight [K]")
+        if residual is not None:
+            _cuda_contig("residual", residual, torch.float32)
+            _check(residual.shape == x.shape, "linear_prenorm: residual [M,K]")
+        if bias is not None:
+            _cuda_contig("bias", bias)
+        res_out = torch.empty((M, Kd), dtype=torch.float32, device=x.device)
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        rc = self.lib.osb_gemm_skinny_prenorm_bf16(
+            _p(y), _dt(y), _p(x), _p(residual), _p(res_out), _p(norm_weight), _dt(norm_weight), ctypes.c_float(eps),
+            _p(w), _p(bias), _dt(bias) if bias is not None else 0, M, N, Kd, self._stream())
+        self._ok(rc, "gemm_skinny_prenorm")
+        return y, res_out
 
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].

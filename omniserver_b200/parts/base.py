@@ -117,6 +117,13 @@ class Norm(Part):
                          out_dtype: torch.dtype) -> torch.Tensor:
         """norm(residual[rows] + x[rows]) for the given rows only; nothing is written back."""
 
+    def fused_linear(self, x: torch.Tensor, residual: Optional[torch.Tensor], linear: Any, out_dtype: torch.dtype
+                     ) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        """(linear(norm(residual + x)), new residual) in one kernel where this norm has one for these
+        operands (a decode step's few rows), else None: the caller then runs ``forward_add`` and the
+        projection. ``linear`` has ``weight`` [N, K] and ``bias`` (or None)."""
+        return None
+
 
 class PositionEncoding(Part):
     """Turns positions into what a mixer applies to its queries and keys."""
@@ -142,11 +149,24 @@ class Mixer(Part):
     def forward(self, ctx: "Any", x: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
         """x [T, hidden] -> [T, hidden]; reads and writes its cache through ``binding``."""
 
+    def forward_prenorm(self, ctx: "Any", x: torch.Tensor, residual: Optional[torch.Tensor], norm: Norm,
+                        binding: CacheBinding) -> Tuple[torch.Tensor, torch.Tensor]:
+        """forward(norm(residual + x)) and the new residual stream. A mixer whose first projection can
+        take the norm into its kernel (``norm.fused_linear``) overrides this; the default runs both."""
+        h, residual = norm.forward_add(x, residual, ctx.act_dtype)
+        return self.forward(ctx, h, binding), residual
+
 
 class FeedForward(Part):
     @abc.abstractmethod
     def forward(self, ctx: "Any", x: torch.Tensor) -> torch.Tensor:
         """x [T, hidden] -> [T, hidden], token by token."""
+
+    def forward_prenorm(self, ctx: "Any", x: torch.Tensor, residual: Optional[torch.Tensor], norm: Norm
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """forward(norm(residual + x)) and the new residual stream (see ``Mixer.forward_prenorm``)."""
+        h, residual = norm.forward_add(x, residual, ctx.act_dtype)
+        return self.forward(ctx, h), residual
 
 
 class Block(abc.ABC):

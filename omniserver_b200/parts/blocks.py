@@ -23,10 +23,9 @@ class PreNormBlock(Block):
 
     def forward(self, ctx: Any, x: torch.Tensor, residual: Optional[torch.Tensor], binding: CacheBinding
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
-        h, residual = self.mixer_norm.forward_add(x, residual, ctx.act_dtype)
-        a = self.mixer.forward(ctx, h, binding)
-        h, residual = self.ffn_norm.forward_add(a, residual, ctx.act_dtype)
-        m = self.ffn.forward(ctx, h)
+        # each norm is handed to the part behind it, which may take it into its first projection's kernel
+        a, residual = self.mixer.forward_prenorm(ctx, x, residual, self.mixer_norm, binding)
+        m, residual = self.ffn.forward_prenorm(ctx, a, residual, self.ffn_norm)
         return m, residual
 
 

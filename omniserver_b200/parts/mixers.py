@@ -44,8 +44,17 @@ class GQAAttention(Mixer):
         return [KVCacheNeed(self.nkv, self.hd, self.window)]
 
     def forward(self, ctx: Any, x: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
+        return self._attend(ctx, self.qkv(x, ctx.act_dtype), binding)
+
+    def forward_prenorm(self, ctx: Any, x: torch.Tensor, residual, norm, binding: CacheBinding):
+        fused = norm.fused_linear(x, residual, self.qkv, ctx.act_dtype)
+        if fused is None:
+            return super().forward_prenorm(ctx, x, residual, norm, binding)
+        qkv, residual = fused
+        return self._attend(ctx, qkv, binding), residual
+
+    def _attend(self, ctx: Any, qkv: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
         k = ops.kernels()
-        qkv = self.qkv(x, ctx.act_dtype)
         tables = ctx.position_tables(self.position) if self.position is not None else None
         g = binding.group
         rot = tables.rot_dim if tables else 0

@@ -30,5 +30,11 @@ class RMSNorm(Norm):
     def forward_add_rows(self, x, residual, rows, out_dtype) -> torch.Tensor:
         return ops.kernels().add_rmsnorm_rows(x, residual, self.weight, self.eps, rows, out_dtype)
 
+    def fused_linear(self, x, residual, linear, out_dtype):
+        k = ops.kernels()
+        if not k.can_linear_prenorm(x, linear.weight):
+            return None
+        return k.linear_prenorm(x, residual, self.weight, self.eps, linear.weight, linear.bias, out_dtype)
+
 
 register_norm("rmsnorm", RMSNorm)

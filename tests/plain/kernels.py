@@ -17,6 +17,9 @@ class PlainKernels:
     SKINNY_MAX_ROWS = 0
     launches = 0
 
+    def can_linear_prenorm(self, x, w):
+        return False
+
     def check_device_errors(self) -> None:
         pass
 
