@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float bias_s[4][BN];  // the bias of a tile's columns: each epilogue warp stages a copy of its own (no CTA barrier)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
@@ -280,6 +281,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       const int buf = local & 1;
       const uint32_t aph = (uint32_t)(local >> 1) & 1u;
       const int row = m0 + q * 32 + lane;
+      if (EPI == EPI_PLAIN && bias) {
+        // while the tile is still being computed: its bias into shared memory, once, as fp32
+        __syncwarp();
+        for (int j = lane; j < BN; j += 32) {
+          const int col = n0 + j;
+          bias_s[q][j] = col < N ? (bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col])) : 0.0f;
+        }
+        __syncwarp();
+      }
       bool ok = mbar_wait(&acc_full[buf], aph, vabort);
       if (!ok && lane == 0) {
         if (!*vabort) atomicExch(err, 103);
@@ -313,10 +323,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = n0 + c0 + j;
-              if (col < N) v[j] += bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col]);
-            }
+            for (int j = 0; j < 32; ++j) v[j] += bias_s[q][c0 + j];
           }
         }
         if (row < M && n0 + c0 < ncols) store_row32(y, y_is_f32, row_off, n0 + c0, ncols, v, vec_ok);
