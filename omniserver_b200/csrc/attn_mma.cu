@@ -344,13 +344,54 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   }
 
   DTL(2);
-  {  // the group's query rows (plain loads: they must not become a copy group of their own)
+  // the group's query rows (plain loads: they must not become a copy group of their own). In the fused
+  // rotary form a thread takes the 8 elements at d and their partners at d + rot/2 and rotates them on the
+  // way, the cos/sin loads in flight together with the q loads: one round trip instead of two.
+  const bool rotate_here = fr.cos_t != nullptr && ((fr.rot >> 1) & 7) == 0;
+  {
     const int cpr = hd >> 3;
-    for (int i = tid; i < 16 * cpr; i += NTHREADS) {
-      const int r = i / cpr, c = i - r * cpr;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * hd + c * 8);
-      *reinterpret_cast<uint4*>(qs + r * stride + c * 8) = v;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    if (rotate_here) {
+      const int half = fr.rot >> 1, hc = half >> 3;            // chunks of 8 in half the rotated span
+      const int per_row = hc + (cpr - 2 * hc);                  // rotated pairs, then chunks that are not rotated
+      const float* cs = fr.cos_t + (size_t)q0 * half;
+      const float* sn = fr.sin_t + (size_t)q0 * half;
+      for (int i = tid; i < 16 * per_row; i += NTHREADS) {
+        const int r = i / per_row, c = i - r * per_row;
+        bf16* dst = qs + r * stride;
+        const bf16* src = q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * hd;
+        if (c >= hc) {  // beyond the rotated span
+          const int cc = 2 * hc + (c - hc);
+          *reinterpret_cast<uint4*>(dst + cc * 8) = r < rows ? *reinterpret_cast<const uint4*>(src + cc * 8) : zero4;
+          continue;
+        }
+        uint4 a = zero4, b = zero4;
+        if (r < rows) {
+          a = *reinterpret_cast<const uint4*>(src + c * 8);
+          b = *reinterpret_cast<const uint4*>(src + half + c * 8);
+          const float4 c0 = *reinterpret_cast<const float4*>(cs + c * 8), c1 = *reinterpret_cast<const float4*>(cs + c * 8 + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(sn + c * 8), s1 = *reinterpret_cast<const float4*>(sn + c * 8 + 4);
+          const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&a);
+          __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x1 = __bfloat1622float2(pa[e]), x2 = __bfloat1622float2(pb[e]);
+            pa[e] = __floats2bfloat162_rn(x1.x * cv[2 * e] - x2.x * sv[2 * e], x1.y * cv[2 * e + 1] - x2.y * sv[2 * e + 1]);
+            pb[e] = __floats2bfloat162_rn(x2.x * cv[2 * e] + x1.x * sv[2 * e], x2.y * cv[2 * e + 1] + x1.y * sv[2 * e + 1]);
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + c * 8) = a;
+        *reinterpret_cast<uint4*>(dst + half + c * 8) = b;
+      }
+    } else {
+      for (int i = tid; i < 16 * cpr; i += NTHREADS) {
+        const int r = i / cpr, c = i - r * cpr;
+        uint4 v = zero4;
+        if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * hd + c * 8);
+        *reinterpret_cast<uint4*>(qs + r * stride + c * 8) = v;
+      }
     }
   }
   if (!early) first_tiles();
@@ -381,7 +422,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     const bf16* ks = kvs + st * 2 * tile_elems;
     const bf16* vs = ks + tile_elems;
     if (t == 0) {
-      if (fr.cos_t != nullptr) {  // rotate the query rows in place in shared memory
+      if (fr.cos_t != nullptr && !rotate_here) {  // rotate the query rows in place in shared memory
         const int half = fr.rot >> 1;
         const float* cs = fr.cos_t + (size_t)q0 * half;
         const float* sn = fr.sin_t + (size_t)q0 * half;
