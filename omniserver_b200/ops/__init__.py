@@ -43,6 +43,10 @@ _DEVICE_ERR = {
     102: "tcgen05 GEMM: the MMA issuer waited too long for operands",
     103: "tcgen05 GEMM: the epilogue waited too long for the accumulator",
     104: "tcgen05 GEMM: the MMA issuer waited too long for a drained accumulator",
+    121: "tcgen05 GEMM (CTA pairs): the TMA producer waited too long for a free stage",
+    122: "tcgen05 GEMM (CTA pairs): the MMA issuer waited too long for operands",
+    123: "tcgen05 GEMM (CTA pairs): the epilogue waited too long for the accumulator",
+    124: "tcgen05 GEMM (CTA pairs): the MMA issuer waited too long for a drained accumulator",
     111: "tcgen05 attention: the TMA producer waited too long for a free key/value stage",
     112: "tcgen05 attention: the MMA issuer waited too long for operands",
     113: "tcgen05 attention: the softmax warps waited too long for scores or the output",
@@ -101,6 +105,10 @@ class CudaKernels:
         #: kernels win; the fused SiLU*up epilogue pays off earlier because it saves a whole pass)
         self.tcgen05_min_rows = 1024
         self.tcgen05_min_rows_swiglu = 256
+        # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
+        # one-CTA kernel: about 3,000 rows for the fused SwiGLU form, 4,000 for the others
+        self.tcgen05_pair_min_rows = 4096
+        self.tcgen05_pair_min_rows_swiglu = 3072
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> ctypes.c_void_p:
@@ -266,18 +274,22 @@ class CudaKernels:
         return self.gemm_simt(x, w, bias, out_dtype)
 
     def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                     swiglu: bool = False) -> torch.Tensor:
+                     swiglu: bool = False, pairs: Optional[bool] = None) -> torch.Tensor:
         """bf16 product on tcgen05 tensor cores with TMA-fed operands and the accumulator in TMEM.
-        ``swiglu``: w is [2I, K] (gate rows first) and the result is silu(x Wg^T) * (x Wu^T), [M, I]."""
+        ``swiglu``: w is [2I, K] (gate rows first) and the result is silu(x Wg^T) * (x Wu^T), [M, I].
+        ``pairs``: two CTAs per 256-row tile (cta_group::2); None: from ``tcgen05_pair_min_rows``."""
         _cuda_contig("x", x, torch.bfloat16)
         _cuda_contig("w", w, torch.bfloat16)
         M, K = x.shape
         N = w.shape[0]
         _check(w.shape[1] == K, "gemm_tcgen05: x [M,K], w [N,K]")
         y = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
-        rc = self.lib.osb_gemm_tcgen05_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
-                                            M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)), self._stream())
-        self._ok(rc, "gemm_tcgen05_bf16")
+        if pairs is None:
+            pairs = M >= (self.tcgen05_pair_min_rows_swiglu if swiglu else self.tcgen05_pair_min_rows)
+        fn = self.lib.osb_gemm_tcgen05_2cta_bf16 if pairs else self.lib.osb_gemm_tcgen05_bf16
+        rc = fn(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
+                M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)), self._stream())
+        self._ok(rc, "gemm_tcgen05_2cta_bf16" if pairs else "gemm_tcgen05_bf16")
         return y
 
     PRENORM_MAX_ROWS, PRENORM_MAX_K = 16, 2048

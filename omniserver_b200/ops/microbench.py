@@ -90,13 +90,14 @@ def bench_gemm_prefill(args, K, dev, peak) -> None:
             x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
             ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(3)]
             fl = 2.0 * M * N * Kd
-            us = graph_time_us(lambda i: K.gemm_tcgen05(x, ws[i], None, torch.bfloat16, swiglu=bool(mode)), 3)
+            us1 = graph_time_us(lambda i: K.gemm_tcgen05(x, ws[i], None, torch.bfloat16, swiglu=bool(mode), pairs=False), 3)
+            us = graph_time_us(lambda i: K.gemm_tcgen05(x, ws[i], None, torch.bfloat16, swiglu=bool(mode), pairs=True), 3)
             if mode:
                 lib = graph_time_us(lambda i: K.silu_mul(torch.mm(x, ws[i].t()), torch.bfloat16), 3)
             else:
                 lib = graph_time_us(lambda i: torch.mm(x, ws[i].t()), 3)
-            print(f"M={M:5d} {name:13s} N={N:6d} K={Kd:5d} | tcgen05 {us:8.1f} us {fl / us / 1e6:7.1f} TF | "
-                  f"library {lib:8.1f} us {fl / lib / 1e6:7.1f} TF", flush=True)
+            print(f"M={M:5d} {name:13s} N={N:6d} K={Kd:5d} | tcgen05 one CTA per tile {us1:8.1f} us {fl / us1 / 1e6:7.1f} TF | "
+                  f"CTA pairs {us:8.1f} us {fl / us / 1e6:7.1f} TF | library {lib:8.1f} us {fl / lib / 1e6:7.1f} TF", flush=True)
 
 
 def bench_attn_decode(args, K, dev, peak) -> None:

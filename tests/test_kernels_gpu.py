@@ -191,15 +191,18 @@ def test_skinny_gemm_with_the_norm_inside(M, N, K_, with_residual):
 
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (17, 128, 64), (128, 128, 128), (2048, 2048, 1536), (200, 264, 1536), (130, 1000, 200),
                                     (300, 1536, 8960), (33, 151936, 96), (129, 8, 72)])
-def test_gemm_tcgen05(M, N, K_):
+@pytest.mark.parametrize("pairs", [False, True])
+def test_gemm_tcgen05(M, N, K_, pairs):
     """The TMA/tcgen05/TMEM product at tile-aligned shapes and at ragged ones (rows, columns and K
-    that are no multiples of the tile)."""
+    that are no multiples of the tile); with one CTA per 128-row tile and with two CTAs sharing a
+    256-row tile (cta_group::2)."""
     x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(N, K_, dtype=torch.bfloat16, seed=1, scale=0.05)
     b = rnd(N, dtype=torch.bfloat16, seed=2)
     want0 = REF.linear(x.double(), w.double(), None, torch.float64)
     for bias in (None, b, b.float()):
         for out_dtype in (torch.bfloat16, torch.float32):
-            got = K().gemm_tcgen05(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out_dtype)
+            got = K().gemm_tcgen05(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out_dtype,
+                                   pairs=pairs)
             K().check_device_errors()
             want = want0 if bias is None else want0 + bias.double()
             # fp32 accumulation in the tensor core over K products: error grows with K and with the
@@ -209,10 +212,11 @@ def test_gemm_tcgen05(M, N, K_):
             assert torch.allclose(got.double().cpu(), want, **t)
 
 
-@pytest.mark.parametrize("M,I,K_", [(128, 64, 64), (2048, 8960, 1536), (100, 200, 96), (33, 176, 80)])
-def test_gemm_tcgen05_swiglu(M, I, K_):
+@pytest.mark.parametrize("M,I,K_", [(128, 64, 64), (2048, 8960, 1536), (100, 200, 96), (33, 176, 80), (700, 1000, 264)])
+@pytest.mark.parametrize("pairs", [False, True])
+def test_gemm_tcgen05_swiglu(M, I, K_, pairs):
     x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(2 * I, K_, dtype=torch.bfloat16, seed=1, scale=0.1)
-    got = K().gemm_tcgen05(x.to(DEV), w.to(DEV), None, torch.bfloat16, swiglu=True)
+    got = K().gemm_tcgen05(x.to(DEV), w.to(DEV), None, torch.bfloat16, swiglu=True, pairs=pairs)
     K().check_device_errors()
     assert got.shape == (M, I)
     assert_swiglu_close(got, x, w, I)
