@@ -4,7 +4,7 @@
 // with tcgen05.ld for the epilogue.
 //
 // One CTA computes a 128 x BN tile of y. Warp 0 drives TMA (one lane), warp 1 allocates TMEM and
-// issues the MMAs (one lane), warps 2-5 run the epilogue (each owns 32 TMEM lanes = 32 rows).
+// issues the MMAs (one lane), warps 2-9 run the epilogue (32 TMEM lanes = 32 rows and half of the columns each).
 // Stages of the ring are handed over with mbarriers: full[s] (TMA -> MMA, transaction bytes) and
 // empty[s] (MMA -> TMA, by tcgen05.commit); acc_full tells the epilogue the accumulator is complete.
 //
@@ -25,7 +25,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192; // 6 warps
+constexpr int NUM_THREADS = 320; // 10 warps: TMA, MMA, 8 epilogue
 constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait calls (each may block for a short hardware-defined time)
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float bias_s[4][BN];  // the bias of a tile's columns: each epilogue warp stages a copy of its own (no CTA barrier)
+  __shared__ float bias_s[8][BN];  // the bias of a tile's columns: each epilogue warp stages a copy of its own (no CTA barrier)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -270,8 +270,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue: warps 2..5
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue: warps 2..9
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int ew = warp - 2;           // two warps per quarter: each takes half of the tile's columns
+    const int c_begin = (ew >> 2) * (OUT_COLS / 2), c_end = c_begin + OUT_COLS / 2;
     const int ncols = EPI == EPI_SWIGLU ? I : N;
     const bool vec_ok = y_is_f32 ? ((ncols & 3) == 0) : ((ncols & 7) == 0);
     int local = 0;
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
         __syncwarp();
         for (int j = lane; j < BN; j += 32) {
           const int col = n0 + j;
-          bias_s[q][j] = col < N ? (bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col])) : 0.0f;
+          bias_s[ew][j] = col < N ? (bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col])) : 0.0f;
         }
         __syncwarp();
       }
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
       const size_t row_off = (size_t)row * ncols;
 #pragma unroll 1
-      for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         float v[32];
         if (EPI == EPI_SWIGLU) {
           uint32_t g[32], u[32];
@@ -313,7 +315,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
             // the two-kernel path rounds gate and up to bf16 before the activation; keep that rounding
             const float gg = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j])));
             const float uu = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j])));
-            v[j] = (gg / (1.0f + __expf(-gg))) * uu;
+            v[j] = __fdividef(gg, 1.0f + __expf(-gg)) * uu;
           }
         } else {
           uint32_t r[32];
@@ -323,7 +325,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += bias_s[q][c0 + j];
+            for (int j = 0; j < 32; ++j) v[j] += bias_s[ew][c0 + j];
           }
         }
         if (row < M && n0 + c0 < ncols) store_row32(y, y_is_f32, row_off, n0 + c0, ncols, v, vec_ok);

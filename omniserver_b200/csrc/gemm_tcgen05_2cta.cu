@@ -12,7 +12,7 @@
 // tcgen05.commit arrives on the empty / accumulator-full barriers of both CTAs (commit with a CTA mask);
 // the odd CTA's epilogue warps arrive on the even CTA's accumulator-empty barrier with a remote
 // mbarrier.arrive. Roles per CTA: warp 0 TMA producer, warp 1 tensor-memory allocation (and, in the even
-// CTA, the MMA issuer), warps 2-5 epilogue. Epilogues as in gemm_tcgen05.cu: plain (bias) and SwiGLU (the
+// CTA, the MMA issuer), warps 2-9 epilogue. Epilogues as in gemm_tcgen05.cu: plain (bias) and SwiGLU (the
 // even CTA loads gate rows, the odd CTA the matching up rows, so accumulator columns [0, BN/2) are gate
 // and [BN/2, BN) up; omniserve/kernels/fused_ops.py:111-119).
 //
@@ -26,7 +26,7 @@ using namespace tc;
 
 constexpr int BM = 128;  // rows per CTA; the pair's tile has 256
 constexpr int BK = 64;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // 10 warps: TMA, MMA, 8 epilogue
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float bias_s[4][BN];
+  __shared__ float bias_s[8][BN];  // a copy per epilogue warp (no CTA barrier)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);  // used in the even CTA only: four epilogue warps of each CTA
+      mbar_init(&acc_empty[b], 16);  // used in the even CTA only: eight epilogue warps of each CTA
     }
     mbar_init_fence();
   }
@@ -224,8 +224,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue: warps 2..5 of both CTAs
-    const int q = warp & 3;
+    // ------------------------------------------------------------------ epilogue: warps 2..9 of both CTAs
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int ew = warp - 2;           // two warps per quarter: each takes half of the tile's columns
+    const int c_begin = (ew >> 2) * (OUT_COLS / 2), c_end = c_begin + OUT_COLS / 2;
     const int ncols = EPI == EPI_SWIGLU ? I : N;
     const bool vec_ok = y_is_f32 ? ((ncols & 3) == 0) : ((ncols & 7) == 0);
     int local = 0;
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
         __syncwarp();
         for (int j = lane; j < BN; j += 32) {
           const int col = n0 + j;
-          bias_s[q][j] = col < N ? (bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col])) : 0.0f;
+          bias_s[ew][j] = col < N ? (bias_is_f32 ? ((const float*)bias)[col] : __bfloat162float(((const bf16*)bias)[col])) : 0.0f;
         }
         __syncwarp();
       }
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
       const size_t row_off = (size_t)row * ncols;
 #pragma unroll 1
-      for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         float v[32];
         if (EPI == EPI_SWIGLU) {
           uint32_t g[32], u[32];
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
             // the two-kernel path rounds gate and up to bf16 before the activation; keep that rounding
             const float gg = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j])));
             const float uu = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j])));
-            v[j] = (gg / (1.0f + __expf(-gg))) * uu;
+            v[j] = __fdividef(gg, 1.0f + __expf(-gg)) * uu;
           }
         } else {
           uint32_t r[32];
@@ -276,7 +278,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (bias) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += bias_s[q][c0 + j];
+            for (int j = 0; j < 32; ++j) v[j] += bias_s[ew][c0 + j];
           }
         }
         if (row < M && n0 + c0 < ncols) store_row32(y, y_is_f32, row_off, n0 + c0, ncols, v, vec_ok);

@@ -106,9 +106,9 @@ class CudaKernels:
         self.tcgen05_min_rows = 1024
         self.tcgen05_min_rows_swiglu = 256
         # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
-        # one-CTA kernel: about 3,000 rows for the fused SwiGLU form, 4,000 for the others
+        # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
-        self.tcgen05_pair_min_rows_swiglu = 3072
+        self.tcgen05_pair_min_rows_swiglu = 2048
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> ctypes.c_void_p:

@@ -87,6 +87,8 @@ def bench_gemm_prefill(args, K, dev, peak) -> None:
     print("== projections with many rows: tcgen05 kernel vs the vendor library (us | TFLOP/s)")
     for M in args.rows:
         for name, N, Kd, mode in shapes:
+            if args.only and name not in args.only:
+                continue
             x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
             ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(3)]
             fl = 2.0 * M * N * Kd
@@ -165,7 +167,7 @@ def bench_norm(args, K, dev, peak) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--what", default="all", choices=["all", "gemm", "gemm_prefill", "attn_decode", "attn_prefill", "norm"])
-    ap.add_argument("--only", default="", help="comma-separated projection names to restrict --what gemm to")
+    ap.add_argument("--only", default="", help="comma-separated projection names to restrict --what gemm / gemm_prefill to")
     ap.add_argument("--rows", default="2048", help="row counts for --what gemm_prefill")
     ap.add_argument("--batch", default="1,8,64")
     ap.add_argument("--ctx", type=int, default=2048)
