@@ -757,7 +757,7 @@ static inline int page_log2(int page_size) {
   while ((1 << l) < page_size) ++l;
   return l;
 }
-static int g_decode_stages = 3;  // the merging CTA keeps (max, sum) of 16 rows x splits in shared memory
+static int g_decode_stages = 0;  // 0: chosen from the grid size; 2 or 3: forced
 
 // out [T, nh*hd] bf16. Requests with one token run through the split-key decode kernel when
 // n_decode > 0 (decode_index[s] = index among them; part_o/part_ml/counters sized by
@@ -768,8 +768,10 @@ static int g_decode_stages = 3;  // the merging CTA keeps (max, sum) of 16 rows 
 // caller then skips the separate rotary/cache-write kernel); allowed only when n_multi == 0.
 // use_cluster: with 2..8 splits, launch the splits of a request as one thread-block cluster and merge
 // them through distributed shared memory (no scratch, no second phase through global memory).
-// Pipeline depth of the decode kernel for head sizes up to 128 (2 or 3 tiles in flight per CTA).
-OSB_API void osb_attn_set_decode_stages(int stages) { g_decode_stages = stages == 2 ? 2 : 3; }
+// Pipeline depth of the decode kernel for head sizes up to 128 (2 or 3 tiles in flight per CTA); 0 lets the
+// launch choose: three stages (two CTAs per SM) unless the grid is larger than two CTAs per SM can hold at
+// once, then two stages (three CTAs per SM).
+OSB_API void osb_attn_set_decode_stages(int stages) { g_decode_stages = (stages == 2 || stages == 3) ? stages : 0; }
 
 OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
@@ -812,11 +814,19 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
     if (rc != 0) return rc;
   }
   if (n_decode > 0) {
+    static int n_sms = 0;
+    if (n_sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
+    }
+    const long long decode_ctas = (long long)nsplits * nkv * ((nh / nkv + 15) / 16) * n_decode;
+    const bool two_stages = g_decode_stages == 2 || (g_decode_stages == 0 && decode_ctas > 2LL * n_sms);
     if (hd <= 64)
       rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                 nsplits, stream, fr, use_cluster != 0);
-    else if (hd <= 128 && g_decode_stages == 2)
+    else if (hd <= 128 && two_stages)
       rc = launch_decode<128, 2>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                  decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
                                  nsplits, stream, fr, use_cluster != 0);

@@ -457,10 +457,14 @@ class CudaKernels:
             chunk, nsplits = 64, 1
             use_cluster = 0
             if n_decode > 0:
-                chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len)
+                # many (request, kv head) pairs: aim at three CTAs per SM (the kernel then keeps two tiles in
+                # flight instead of three); measured 5 % faster per step at batch 64
+                units = n_decode * nkv * ((nh // nkv + 15) // 16)
+                target = 444 if units >= 64 else 296
+                chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, target)
                 if self.decode_clusters and 1 < nsplits <= 2 * self.CLUSTER_MAX_SPLITS:
                     # few enough splits: one cluster per (request, kv head), merged in shared memory
-                    chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len,
+                    chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, target,
                                                         max_splits=self.CLUSTER_MAX_SPLITS)
                     use_cluster = 1
                 if nsplits > 1 and not use_cluster:

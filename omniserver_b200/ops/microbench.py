@@ -180,7 +180,7 @@ def main() -> None:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--warps", default="0", help="K splits of the skinny GEMM to try (0 = its own choice)")
     ap.add_argument("--no-clusters", action="store_true", help="decode attention: merge splits through global memory")
-    ap.add_argument("--stages", type=int, default=3, help="pipeline depth of the decode attention kernel (2 or 3)")
+    ap.add_argument("--stages", type=int, default=0, help="pipeline depth of the decode attention kernel (2 or 3; 0: chosen by the launch)")
     ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
     args = ap.parse_args()
     args.batch = [int(b) for b in args.batch.split(",")]
