@@ -442,16 +442,24 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     }
     const int kbase = k_begin + t * TILE_N + warp * 16;  // this warp's 16 keys of the tile
     if (kbase < k_end && kbase + 15 >= lo) {
-      float sc[2][4];
-      sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = 0.0f;
-      sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.0f;
+      // two accumulator pairs (even and odd k-steps) halve the chain of dependent MMAs
+      float sc[2][4], sd[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[n][e] = sd[n][e] = 0.0f;
 #pragma unroll
       for (int k = 0; k < KS; ++k) {
         if (k < ks_n) {
           unsigned b0, b1, b2, b3;
           ldmatrix_x4(b0, b1, b2, b3, ks + (warp * 16 + lr + (lm >> 1) * 8) * stride + k * 16 + (lm & 1) * 8);
-          mma_bf16_16816(sc[0], qf[k], b0, b1);
-          mma_bf16_16816(sc[1], qf[k], b2, b3);
+          if (k & 1) {
+            mma_bf16_16816(sd[0], qf[k], b0, b1);
+            mma_bf16_16816(sd[1], qf[k], b2, b3);
+          } else {
+            mma_bf16_16816(sc[0], qf[k], b0, b1);
+            mma_bf16_16816(sc[1], qf[k], b2, b3);
+          }
         }
       }
       // every row is the same query position: the mask depends on the key only
@@ -462,39 +470,46 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
         for (int e = 0; e < 2; ++e) {
           const int key = kbase + n * 8 + c2 + e;
           const bool vis = key < k_end && key >= lo;
-          const float v0 = vis ? sc[n][e] * scale_log2 : -INFINITY;
-          const float v1 = vis ? sc[n][2 + e] * scale_log2 : -INFINITY;
+          const float v0 = vis ? (sc[n][e] + sd[n][e]) * scale_log2 : -INFINITY;
+          const float v1 = vis ? (sc[n][2 + e] + sd[n][2 + e]) * scale_log2 : -INFINITY;
           sc[n][e] = v0;
           sc[n][2 + e] = v1;
           mx0 = fmaxf(mx0, v0);
           mx1 = fmaxf(mx1, v1);
         }
       }
-      float mx[2] = {mx0, mx1};
+      // m_run is the exponent offset in use; it moves only when the maximum has grown by more than 2^8
+      // (or at the first keys), so that the accumulated output is rescaled rarely
+      float mx[2] = {mx0, mx1}, alpha[2];
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         float v = mx[hh];
         v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
         v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-        const float m_new = fmaxf(m_run[hh], v);
-        const float alpha = (m_run[hh] == -INFINITY) ? 0.0f : fast_exp2(m_run[hh] - m_new);
+        const bool grow = v > m_run[hh] + 8.0f || (m_run[hh] == -INFINITY && v > -INFINITY);
+        alpha[hh] = (grow && m_run[hh] != -INFINITY) ? fast_exp2(m_run[hh] - v) : 1.0f;
+        if (grow) m_run[hh] = v;
+        const float off = m_run[hh];
         float sum = 0.0f;
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const float x = sc[n][hh * 2 + e];
-            const float pe = (x == -INFINITY) ? 0.0f : fast_exp2(x - m_new);
+            const float pe = (x == -INFINITY) ? 0.0f : fast_exp2(x - off);
             sc[n][hh * 2 + e] = pe;
             sum += pe;
           }
         }
-        l_run[hh] = l_run[hh] * alpha + sum;
-        m_run[hh] = m_new;
+        l_run[hh] = l_run[hh] * alpha[hh] + sum;
+      }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
         for (int i = 0; i < KS * 2; ++i) {
-          o[i][hh * 2] *= alpha;
-          o[i][hh * 2 + 1] *= alpha;
+          o[i][0] *= alpha[0];
+          o[i][1] *= alpha[0];
+          o[i][2] *= alpha[1];
+          o[i][3] *= alpha[1];
         }
       }
       unsigned pa[4];

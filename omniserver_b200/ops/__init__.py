@@ -457,16 +457,20 @@ class CudaKernels:
             chunk, nsplits = 64, 1
             use_cluster = 0
             if n_decode > 0:
-                # many (request, kv head) pairs: aim at three CTAs per SM (the kernel then keeps two tiles in
-                # flight instead of three); measured 5 % faster per step at batch 64
+                # (request, kv head) pairs to spread over the SMs. Few of them: eight splits each, merged inside
+                # a thread-block cluster, one CTA per SM. More: as many splits as fill three CTAs per SM (the
+                # kernel then keeps two tiles in flight instead of three), merged inside a cluster when there
+                # are at most eight of them, else through scratch memory by the last CTA. Measured in full decode
+                # steps at batch 8 / 16 / 32 / 64.
                 units = n_decode * nkv * ((nh // nkv + 15) // 16)
-                target = 444 if units >= 64 else 296
-                chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, target)
-                if self.decode_clusters and 1 < nsplits <= 2 * self.CLUSTER_MAX_SPLITS:
-                    # few enough splits: one cluster per (request, kv head), merged in shared memory
-                    chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, target,
+                if self.decode_clusters and units * self.CLUSTER_MAX_SPLITS <= 148:
+                    chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len,
                                                         max_splits=self.CLUSTER_MAX_SPLITS)
-                    use_cluster = 1
+                    use_cluster = 1 if nsplits > 1 else 0
+                else:
+                    chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len,
+                                                        444 if units >= 24 else 296)
+                    use_cluster = 1 if self.decode_clusters and 1 < nsplits <= self.CLUSTER_MAX_SPLITS else 0
                 if nsplits > 1 and not use_cluster:
                     n_o, n_ml = n_decode * nh * nsplits * hd, n_decode * nh * nsplits * 2
                     part_o = self._scratch(scratch, "attn_part_o", n_o, qkv.device)
