@@ -16,102 +16,17 @@
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA records an error code in
 // *err, stops issuing work, waits (bounded) for the copies it already started, frees its TMEM
 // and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_utils.cuh"
 
 namespace {
+using namespace tc;
 
 constexpr int BM = 128;
 constexpr int BK = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 320; // 10 warps: TMA, MMA, 8 epilogue
-constexpr uint32_t WAIT_LIMIT = 1u << 20;  // try_wait calls (each may block for a short hardware-defined time)
 
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false when the bound was hit or another thread of the CTA gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_addr(dst)), "l"((uint64_t)map), "r"(smem_addr(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
-// 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset is unused (1),
-// descriptor version 1, layout type 2 (SWIZZLE_128B). Bits: [0,14) address >> 4, [16,30) LBO >> 4,
-// [32,46) SBO >> 4, [46,48) version, [61,64) layout type.
-__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
-  const uint64_t addr = (uint64_t)((smem_addr(tile) & 0x3FFFFu) >> 4);
-  return addr | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Instruction descriptor for kind::f16: fp32 accumulator (bits [4,6) = 1), A and B bf16
-// (bits [7,10) = [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
 
 // Stores 32 consecutive output columns of one row (fp32 values in r) as bf16 or fp32.
 __device__ __forceinline__ void store_row32(void* y, int y_is_f32, size_t row_off, int col, int ncols, const float* v,
@@ -178,17 +93,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {  // TMEM: two accumulators of BN fp32 columns x 128 lanes
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
-                 "r"((uint32_t)TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(&tmem_base_slot, (uint32_t)TMEM_COLS);
   }
-  tc_fence_before();
+  fence_before();
   __syncthreads();
-  tc_fence_after();
+  fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* vabort = &abort_flag;
 
@@ -244,7 +156,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
           ok = false;
           break;
         }
-        tc_fence_after();
+        fence_after();
         const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb, ++consumed) {
           const int s = consumed % STAGES;
@@ -255,10 +167,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
             ok = false;
             break;
           }
-          tc_fence_after();
+          fence_after();
           const unsigned char* a_src = tiles + (size_t)s * STAGE_BYTES;
-          const uint64_t adesc = make_smem_desc(a_src);
-          const uint64_t bdesc = make_smem_desc(a_src + A_BYTES);
+          const uint64_t adesc = desc_kmajor(a_src);
+          const uint64_t bdesc = desc_kmajor(a_src + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
@@ -299,7 +211,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       }
       ok = ok && !*vabort;
       if (!__all_sync(0xffffffffu, ok)) break;
-      tc_fence_after();
+      fence_after();
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
       const size_t row_off = (size_t)row * ncols;
 #pragma unroll 1
@@ -331,49 +243,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
         if (row < M && n0 + c0 < ncols) store_row32(y, y_is_f32, row_off, n0 + c0, ncols, v, vec_ok);
       }
       // this warp has read its part of the accumulator: hand the buffer back to the MMA issuer
-      tc_fence_before();
+      fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
-  tc_fence_before();
+  fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
-                 : "memory");
+    fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)TMEM_COLS);
   }
 }
 
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-      q != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = (EncodeTiledFn)p;
-  return fn;
-}
-
 // A [rows, K] bf16 row-major matrix as a 2-D tensor map with boxes of box_rows x 64 elements.
 int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return OSB_ERR_UNSUPPORTED;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? OSB_OK : OSB_ERR_BAD_SHAPE;
+  return tc::make_map_bf16(map, base, 2, dims, strides, box);
 }
 
 int sm_count() {
