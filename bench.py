@@ -27,6 +27,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -69,11 +70,10 @@ class ClockSampler:
 
     def __init__(self):
         self.proc = None
-        self.path = os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")
+        self.path = os.path.join(tempfile.gettempdir(), "osb_bench_clocks_%d.csv" % os.getpid())
 
     def start(self):
         try:
-            os.makedirs(os.path.dirname(self.path), exist_ok=True)
             self.f = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)

@@ -97,6 +97,9 @@ class CudaKernels:
         self.use_tcgen05 = True
         self.decode_clusters = True   # decode attention: merge a request's splits inside a cluster
         self.tc_prefill = True        # prompt attention on tcgen05 where the head size allows (64, 128)
+        self.decode_stream = True     # decode attention that streams K and V into MMA registers (head size 64, 128)
+        self.stream_target_ctas = 148  # CTAs of that kernel the GPU holds at once (one per SM)
+        self.stream_cluster_sizes = (2, 4)   # split counts merged inside a thread-block cluster
         # few rows: the norm before a projection can run inside the projection's kernel. Off: measured in a full
         # decode step it is slower than the two kernels (every CTA re-reads the rows of the residual stream)
         self.fuse_prenorm = False
@@ -453,6 +456,31 @@ class CudaKernels:
                 if n_decode == 0:
                     return out
                 n_multi = 0
+            if (self.decode_stream and n_decode > 0 and n_multi == 0 and hd in (64, 128) and qkv.shape[1] % 8 == 0
+                    and nh // nkv <= 8):
+                # single-token requests, head size 64 / 128: keys and values go from the pages straight into
+                # MMA registers; one CTA of eight warps per SM, so the (request, kv head) pairs get as many
+                # splits (at most 8, merged inside a cluster) as fill the SMs once
+                # up to 16 splits; 2 or 4 of them are merged inside a thread-block cluster, other counts through
+                # scratch memory by the CTA that finishes last: a cluster of CTAs that each fill an SM has to wait
+                # until that many SMs of one GPC are free at once, which for 3 or 8 cost more than it saved
+                # (measured in full decode steps at batch 8 and 24)
+                chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, self.stream_target_ctas,
+                                                    max_splits=16)
+                use_cluster = 1 if self.decode_clusters and nsplits in self.stream_cluster_sizes else 0
+                part_o = part_ml = counters = None
+                if nsplits > 1 and not use_cluster:
+                    part_o = self._scratch(scratch, "attn_part_o", n_decode * nh * nsplits * hd, qkv.device)
+                    part_ml = self._scratch(scratch, "attn_part_ml", n_decode * nh * nsplits * 2, qkv.device)
+                    counters = self._scratch(scratch, "attn_counters", n_decode * nkv, qkv.device, zero_int=True)
+                rc = self.lib.osb_attn_decode_stream(
+                    _p(out), _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
+                    _p(cu_q), _p(seq_lens), _p(decode_index), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
+                    ctypes.c_float(scale), win, _p(part_o), _p(part_ml), _p(counters), chunk, nsplits,
+                    _p(rope[0] if rope else None), _p(rope[1] if rope else None), _p(rope[2] if rope else None),
+                    int(rope[3]) if rope else 0, 1 if (use_cluster and nsplits > 1) else 0, self._stream())
+                self._ok(rc, "attn_decode_stream")
+                return out
             part_o = part_ml = counters = None
             chunk, nsplits = 64, 1
             use_cluster = 0
