@@ -351,13 +351,34 @@ def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, ps, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(12, 2, 128, 16), (28, 4, 128, 16), (6, 3, 48, 8), (4, 4, 64, 64), (40, 2, 32, 16),
-                                          (8, 1, 256, 16)])
+                                          (8, 1, 256, 16), (16, 2, 128, 16), (7, 1, 128, 32), (8, 2, 64, 4), (12, 2, 128, 8),
+                                          (6, 6, 64, 2), (24, 2, 128, 16)])
 @pytest.mark.parametrize("window", [None, 300])
 def test_decode_attention_long_contexts_split_keys(nh, nkv, hd, ps, window):
-    """Single-token requests with long and uneven contexts: the keys are split over CTAs and merged."""
+    """Single-token requests with long and uneven contexts: the keys are split over CTAs and merged. Head
+    sizes 64 and 128 with at most 8 query heads per kv head run in the kernel that streams K and V into
+    registers (pages down to 2 tokens, groups of 6, 7 and 8 heads), the others in the shared-memory kernel."""
     kv_lens = [2048, 1, 777, 64, 65, 3000, 128, 129]
     case = _paged_case([1] * len(kv_lens), kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=3)
     got, want = _run_attn(case, nh, nkv, hd, window, torch.bfloat16)
+    assert torch.allclose(got, want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("batch", [1, 3, 20, 40, 150])
+@pytest.mark.parametrize("stream", [True, False])
+def test_decode_attention_split_and_merge_paths(batch, stream):
+    """The number of requests decides how many splits a request gets and how they are merged (one split,
+    a cluster, scratch memory and the last CTA); every path of both decode kernels against the reference."""
+    nh, nkv, hd, ps = 12, 2, 128, 16
+    g = torch.Generator().manual_seed(batch)
+    kv_lens = [int(x) for x in torch.randint(1, 1400, (batch,), generator=g)]
+    kv_lens[0] = 1399
+    case = _paged_case([1] * batch, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=batch)
+    K().decode_stream = stream
+    try:
+        got, want = _run_attn(case, nh, nkv, hd, None, torch.bfloat16)
+    finally:
+        K().decode_stream = True
     assert torch.allclose(got, want, **tol(torch.bfloat16))
 
 
@@ -391,7 +412,7 @@ def test_decode_attention_finds_one_key_that_matters(window):
     nh, nkv, hd, ps, dtype = 12, 2, 128, 16, torch.bfloat16
     kv_len = 1500
     p = kv_len - 1
-    spots = [0, 63, 64, 127, 128, 255, 256, 1023, 1024, p - 1, p]
+    spots = [0, 15, 16, 17, 63, 64, 93, 94, 95, 96, 127, 128, 255, 256, 1023, 1024, p - 1, p]
     if window:
         spots = [p - window, p - window + 1, p - window + 2, 1407, 1408, p]
     for j in spots:
