@@ -127,13 +127,15 @@ def bench_attn_decode(args, K, dev, peak) -> None:
             finally:
                 ops.CudaKernels.decode_splits = orig
             gbs = B * ctx * nkv * hd * 2 * 2 / us / 1e3
-            chunk, nsp = orig(B, nkv, nh // nkv, ctx, target)
-            how = "global merge"
-            if K.decode_clusters and 1 < nsp <= 2 * K.CLUSTER_MAX_SPLITS:
-                chunk, nsp = orig(B, nkv, nh // nkv, ctx, target, max_splits=K.CLUSTER_MAX_SPLITS)
-                how = "cluster merge"
-            print(f"B={B:3d} chunk={chunk:5d} splits={nsp:3d} {how:13s} | {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}",
-                  flush=True)
+            stream = K.decode_stream and hd in (64, 128) and nh // nkv <= 8
+            if stream:
+                chunk, nsp = orig(B, nkv, nh // nkv, ctx, K.stream_target_ctas, max_splits=16)
+                how = "streaming kernel, " + ("cluster merge" if nsp in K.stream_cluster_sizes else
+                                              "one split" if nsp == 1 else "merge by the last CTA")
+            else:
+                chunk, nsp = orig(B, nkv, nh // nkv, ctx, target)
+                how = "shared-memory kernel"
+            print(f"B={B:3d} splits={nsp:3d} {how:40s} | {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}", flush=True)
 
 
 def bench_attn_prefill(args, K, dev, peak) -> None:
@@ -179,6 +181,7 @@ def main() -> None:
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--warps", default="0", help="K splits of the skinny GEMM to try (0 = its own choice)")
+    ap.add_argument("--no-stream", action="store_true", help="decode attention: the shared-memory kernel instead of the streaming one")
     ap.add_argument("--no-clusters", action="store_true", help="decode attention: merge splits through global memory")
     ap.add_argument("--stages", type=int, default=0, help="pipeline depth of the decode attention kernel (2 or 3; 0: chosen by the launch)")
     ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
@@ -192,6 +195,7 @@ def main() -> None:
     K = ops.kernels()
     K.lib.osb_attn_set_decode_stages(args.stages)
     K.decode_clusters = not args.no_clusters
+    K.decode_stream = not args.no_stream
     peak = peak_gbs()
     with torch.inference_mode():
         if args.what in ("all", "gemm"):
