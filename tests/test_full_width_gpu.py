@@ -125,3 +125,45 @@ def test_full_width_logits_match_plain_for_every_cut(dtype):
                     for p, lg in rows.items():
                         if p in base.get(rid, {}):
                             assert torch.equal(lg, base[rid][p]), f"{family.__name__}/{rid}@{p} differs bitwise from whole"
+
+
+def test_full_width_many_live_requests_bfloat16():
+    """24 live requests at the real layer sizes: their prompts packed into two steps, then four steps that
+    decode all of them at once. That is the regime of the library GEMM (17 .. rows), of the streaming decode
+    attention with several splits merged through scratch memory, and of CUDA-graph replay at a batch size
+    the other tests do not reach. Logits of every request at every decoded place against the plain model."""
+    from omniserver_b200 import EngineConfig, build_runner
+    from omniserver_b200.engine.step import StepEntry
+    n_req, n_dec = 24, 4
+    g = torch.Generator().manual_seed(9)
+    lens = [int(x) for x in torch.randint(3, 90, (n_req,), generator=g)]
+    lens[0], lens[1] = 200, 1                       # several key blocks; a prompt of one token
+    toks = [torch.randint(0, CONFIG["vocab_size"], (n + n_dec,), generator=g).tolist() for n in lens]
+    ec = EngineConfig(dtype="bfloat16", max_cache_tokens=4096, max_requests=n_req + 2)
+    runner = build_runner(config=CONFIG, seed=2, engine_config=ec, init_std=0.03, norm_noise=0.1)
+    cfg = pm.PlainConfig(CONFIG)
+    w = plain_weights(runner.model)
+    got = {i: [] for i in range(n_req)}
+    with torch.inference_mode():
+        for i in range(n_req):
+            runner.start_request(f"m{i}")
+        for part in (range(0, 12), range(12, n_req)):
+            lg = runner.step([StepEntry(f"m{i}", toks[i][:lens[i]], want=[lens[i] - 1]) for i in part]).float().cpu()
+            for j, i in enumerate(part):
+                got[i].append(lg[j])
+        for d in range(n_dec):
+            lg = runner.step([StepEntry(f"m{i}", [toks[i][lens[i] + d]], want=[0]) for i in range(n_req)]).float().cpu()
+            for i in range(n_req):
+                got[i].append(lg[i])
+        for i in range(n_req):
+            runner.end_request(f"m{i}")
+    assert all(p == 0 for p in runner.cache.pages_in_use())
+    for i in range(n_req):
+        rows = list(range(lens[i] - 1, lens[i] + n_dec))
+        hid = pm.forward(cfg, w, torch.tensor(toks[i]), return_hidden=True, rows=[rows[-1]])[1]
+        for k, p in enumerate(rows):
+            ref = pm.lm_head(hid[p:p + 1], w["embed_tokens.weight"])[0]
+            lg = got[i][k]
+            err = (lg - ref).abs().max().item()
+            assert err < 5e-2 * max(1.0, ref.abs().max().item()), f"request {i} place {p}: {err}"
+            assert ((lg - ref).norm() / ref.norm()).item() < 3e-2, f"request {i} place {p}"
