@@ -341,7 +341,8 @@ class ModelRunner:
         ctx = self.build_context(entries)
         self.logit_slots = ctx.logit_slots
         try:
-            logits = self.model.forward(ctx)
+            with ops.kernels().pinned_stream():
+                logits = self.model.forward(ctx)
         except Exception:
             # the cache is in an undefined state for these requests; give the reservations back
             for e in entries:

@@ -12,6 +12,7 @@ The object that does the work is ``kernels()``; model code calls it as
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Dict, Optional, Tuple
 
@@ -70,10 +71,11 @@ def _check(cond: bool, msg: str) -> None:
 
 
 def _cuda_contig(name: str, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> None:
+    if t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype):
+        return
     _check(t.is_cuda, f"{name} must be a CUDA tensor (there is no CPU path)")
     _check(t.is_contiguous(), f"{name} must be contiguous")
-    if dtype is not None:
-        _check(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+    _check(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
 
 
 class CudaKernels:
@@ -115,11 +117,25 @@ class CudaKernels:
         # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
+        self._pinned_stream: Optional[ctypes.c_void_p] = None
         self.tcgen05_pair_min_rows_swiglu = 2048
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> ctypes.c_void_p:
+        if self._pinned_stream is not None:
+            return self._pinned_stream
         return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    @contextlib.contextmanager
+    def pinned_stream(self):
+        """Inside the block every launch goes to the stream that is current at its start: one lookup
+        of the current stream instead of one per launch. The caller must not switch streams inside."""
+        prev = self._pinned_stream
+        self._pinned_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        try:
+            yield
+        finally:
+            self._pinned_stream = prev
 
     def err_flag(self, device: torch.device) -> torch.Tensor:
         idx = device.index if device.index is not None else torch.cuda.current_device()

@@ -8,6 +8,7 @@ is computed in float32 (or the dtype given) from the formulas cited in tests/pla
 
 from __future__ import annotations
 
+import contextlib
 from typing import Optional, Tuple
 
 import torch
@@ -19,6 +20,10 @@ class PlainKernels:
 
     def can_linear_prenorm(self, x, w):
         return False
+
+    @contextlib.contextmanager
+    def pinned_stream(self):
+        yield
 
     def check_device_errors(self) -> None:
         pass
