@@ -30,8 +30,13 @@ class RMSNorm(Norm):
     def forward_add_rows(self, x, residual, rows, out_dtype) -> torch.Tensor:
         return ops.kernels().add_rmsnorm_rows(x, residual, self.weight, self.eps, rows, out_dtype)
 
+    def rms_operands(self):
+        return self.weight, self.eps
+
     def fused_linear(self, x, residual, linear, out_dtype):
         k = ops.kernels()
+        if out_dtype == torch.bfloat16 and k.can_norm_linear_decode(x, self.weight, linear.weight, linear.bias):
+            return k.norm_linear_decode(x, residual, self.weight, self.eps, linear.weight, linear.bias)
         if not k.can_linear_prenorm(x, linear.weight):
             return None
         return k.linear_prenorm(x, residual, self.weight, self.eps, linear.weight, linear.bias, out_dtype)

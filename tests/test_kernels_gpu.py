@@ -189,6 +189,82 @@ def test_skinny_gemm_with_the_norm_inside(M, N, K_, with_residual):
     K().check_device_errors()
 
 
+@pytest.mark.parametrize("H,N", [(256, 100), (384, 1000), (2048, 300), (1536, 2048), (1536, 17)])
+@pytest.mark.parametrize("B", [1, 5, 8])
+def test_norm_linear_decode(H, N, B):
+    """The projection of a few rows that normalises them itself while its weights stream in: same
+    statements as for the skinny GEMM with the norm inside (residual sum bit for bit; one bf16 step of
+    slack on every term for rounding ties of the normalised row; the output rounded to bf16 once)."""
+    x = rnd(B, H, dtype=torch.bfloat16)
+    res = rnd(B, H, seed=3, scale=2.0)
+    gm = (1.0 + 0.2 * rnd(H, seed=4)).to(torch.bfloat16)
+    w = rnd(N, H, dtype=torch.bfloat16, seed=1, scale=H ** -0.5)
+    b = rnd(N, dtype=torch.bfloat16, seed=2)
+    k = K()
+    for bias in (None, b):
+        for with_res in (True, False):
+            res_dev = res.to(DEV) if with_res else None
+            bd = bias.to(DEV) if bias is not None else None
+            assert k.can_norm_linear_decode(x.to(DEV), gm.to(DEV), w.to(DEV), bd)
+            y, new_res = k.norm_linear_decode(x.to(DEV), res_dev, gm.to(DEV), 1e-6, w.to(DEV), bd)
+            if with_res:
+                assert torch.equal(res_dev.cpu(), res), "the old residual stream must stay as it was"
+            r = x.float() + res if with_res else x.float()
+            assert torch.equal(new_res.cpu(), r)
+            h, _ = REF.add_rmsnorm(x, res.clone() if with_res else None, gm, 1e-6, torch.bfloat16)
+            want = REF.linear(h.double(), w.double(), bias.double() if bias is not None else None, torch.float64)
+            slack = 2.0 ** -8 * (h.double().abs() @ w.double().abs().t()) + 2.0 ** -8 * want.abs() + 1e-5
+            over = (y.double().cpu() - want).abs() - slack
+            assert not (over > 0).any(), f"worst excess {float(over.max())}"
+    k.check_device_errors()
+
+
+@pytest.mark.parametrize("H,I", [(256, 512), (384, 1920), (2048, 256), (1536, 8960)])
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_ffn_decode_fused(H, I, B):
+    """The persistent feed-forward kernel (norm, gate/up with the activation, grid barrier, down) against
+    the plain parts in float64 from the same bf16-rounded intermediates. The new residual stream is the
+    fp32 sum bit for bit. The bound: the normalised row may differ by one bf16 step where a rounding tie
+    falls the other way (2^-8 on every term of gate and up), the activation and the output are rounded
+    to bf16 once each. Launched several times over: the barrier's counter stays a multiple of the grid size."""
+    x = rnd(B, H, dtype=torch.bfloat16)
+    res = rnd(B, H, seed=3, scale=2.0)
+    gm = (1.0 + 0.2 * rnd(H, seed=4)).to(torch.bfloat16)
+    wgu = rnd(2 * I, H, dtype=torch.bfloat16, seed=1, scale=H ** -0.5)
+    wd = rnd(H, I, dtype=torch.bfloat16, seed=2, scale=I ** -0.5)
+    k = K()
+    assert k.can_ffn_decode_fused(x.to(DEV), gm.to(DEV), wgu.to(DEV), wd.to(DEV))
+    h, _ = REF.add_rmsnorm(x, res.clone(), gm, 1e-6, torch.bfloat16)
+    hd, wg, wu, wdd = h.double(), wgu[:I].double(), wgu[I:].double(), wd.double()
+    g, u = hd @ wg.t(), hd @ wu.t()
+    act = (g / (1 + torch.exp(-g)) * u)
+    act_b = act.to(torch.bfloat16).double()
+    want = act_b @ wdd.t()
+    dg, du = 2.0 ** -8 * (hd.abs() @ wg.abs().t()), 2.0 ** -8 * (hd.abs() @ wu.abs().t())
+    slack_act = 1.1 * u.abs() * dg + g.abs() * du + 2.0 ** -8 * act.abs()
+    slack = slack_act @ wdd.abs().t() + 2.0 ** -8 * want.abs() + 1e-5
+    xd, wgud, wdn, gmd = x.to(DEV), wgu.to(DEV), wd.to(DEV), gm.to(DEV)
+    for with_res in (True, False, True):
+        res_dev = res.to(DEV) if with_res else None
+        y, new_res = k.ffn_decode_fused(xd, res_dev, gmd, 1e-6, wgud, wdn)
+        if with_res:
+            assert torch.equal(res_dev.cpu(), res), "the old residual stream must stay as it was"
+            assert torch.equal(new_res.cpu(), x.float() + res)
+            over = (y.double().cpu() - want).abs() - slack
+            assert not (over > 0).any(), f"worst excess {float(over.max())}"
+            # the separate kernels give the same to that bound
+            h2, _ = k.add_rmsnorm(xd, res.to(DEV), gmd, 1e-6, torch.bfloat16)
+            y2 = k.linear(k.gate_up_silu(h2, wgud, torch.bfloat16), wdn, None, torch.bfloat16)
+            assert not ((y.double() - y2.double()).cpu().abs() - 2 * slack > 0).any()
+        else:
+            assert torch.equal(new_res.cpu(), x.float())
+            assert torch.isfinite(y.float()).all()
+    k.check_device_errors()
+    bar, _ = k._fused_state(torch.device(DEV), I)
+    n_sm = torch.cuda.get_device_properties(0).multi_processor_count
+    assert int(bar.view(torch.int64)[0]) % n_sm == 0, "every CTA arrived at every grid barrier"
+
+
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (17, 128, 64), (128, 128, 128), (2048, 2048, 1536), (200, 264, 1536), (130, 1000, 200),
                                     (300, 1536, 8960), (33, 151936, 96), (129, 8, 72)])
 @pytest.mark.parametrize("pairs", [False, True])
@@ -404,6 +480,51 @@ def test_decode_attention_with_fused_rotary_and_cache_write(nh, nkv, hd, ps, rot
     K().check_device_errors()
     assert torch.equal(k2, k1) and torch.equal(v2, v1)
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("H,nh,nkv,hd,ps,rot", [(1536, 12, 2, 128, 16, 128), (256, 4, 2, 64, 8, 32), (384, 4, 1, 128, 16, 128),
+                                                (2048, 4, 4, 64, 4, 64)])
+@pytest.mark.parametrize("kv_lens,window", [([2048, 1, 777, 64, 65, 129], None), ([300], None), ([5, 900, 17, 16, 2048, 33, 1, 640], None),
+                                            ([2048, 1, 777, 64, 65, 129], 100)])
+def test_attn_decode_fused(H, nh, nkv, hd, ps, rot, kv_lens, window):
+    """The persistent attention half (norm, qkv, rotary, cache write, attention with split keys, output
+    projection, two grid barriers) against the same chain of separate kernels, each of which has its own test
+    against the plain implementation. The residual stream is the fp32 sum bit for bit; the output and the
+    stored key agree to a few bf16 roundings (the projections sum in another order); the stored value row is
+    that of the separate kernels up to one rounding of the projection."""
+    S = len(kv_lens)
+    _, kc, vc, bt, cu_q, seq_lens, tok_seq = [t.to(DEV) for t in _paged_case([1] * S, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=5)]
+    nq = (nh + 2 * nkv) * hd
+    x = rnd(S, H, dtype=torch.bfloat16).to(DEV)
+    res = rnd(S, H, seed=3, scale=2.0).to(DEV)
+    gm = (1.0 + 0.2 * rnd(H, seed=4)).to(torch.bfloat16).to(DEV)
+    wqkv = rnd(nq, H, dtype=torch.bfloat16, seed=1, scale=H ** -0.5).to(DEV)
+    bqkv = rnd(nq, dtype=torch.bfloat16, seed=2, scale=0.3).to(DEV)
+    wo = rnd(H, nh * hd, dtype=torch.bfloat16, seed=6, scale=(nh * hd) ** -0.5).to(DEV)
+    ang = rnd(S, rot // 2, seed=3, scale=3.0)
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    slot_map = torch.stack([bt[s, (kv - 1) // ps] * ps + (kv - 1) % ps for s, kv in enumerate(kv_lens)]).to(torch.int32)
+    didx = torch.arange(S, dtype=torch.int32, device=DEV)
+    k = K()
+    assert k.can_attn_decode_fused(x, gm, wqkv, bqkv, wo, kc, nh, nkv, hd, S, 0, rot)
+    # the separate kernels
+    k1, v1 = kc.clone(), vc.clone()
+    h, res_want = k.add_rmsnorm(x, res.clone(), gm, 1e-6, torch.bfloat16)
+    qkv = k.linear(h, wqkv, bqkv, torch.bfloat16)
+    a = k.paged_attention(qkv, k1, v1, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, window, 1, max(kv_lens),
+                          torch.bfloat16, decode_index=didx, n_decode=S, n_multi=0, rope=(cos, sin, slot_map, rot))
+    want = k.linear(a, wo, None, torch.bfloat16).float()
+    for _ in range(2):      # twice: the barrier counter and the merge counters are left ready for the next launch
+        k2, v2 = kc.clone(), vc.clone()
+        got, res_got = k.attn_decode_fused(x, res, gm, 1e-6, wqkv, bqkv, wo, k2, v2, bt, cu_q, seq_lens, didx, nh, nkv, hd,
+                                           hd ** -0.5, window, max(kv_lens), (cos, sin, slot_map, rot), {})
+        k.check_device_errors()
+        assert torch.equal(res_got, res_want)
+        assert torch.allclose(k2.float(), k1.float(), rtol=2.0 ** -7, atol=2.0 ** -7)
+        assert torch.allclose(v2.float(), v1.float(), rtol=2.0 ** -7, atol=2.0 ** -7)
+        err = (got.float() - want).abs()
+        assert float(err.max()) <= 2.0 ** -6 * float(want.abs().max()) + 1e-3, float(err.max())
+        assert float((got.float() - want).norm() / want.norm()) < 1e-2
 
 
 @pytest.mark.parametrize("window", [None, 100])
