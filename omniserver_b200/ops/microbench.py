@@ -1,6 +1,6 @@
 """Times single kernels at the shapes of a decode or prefill step and prints achieved bandwidth.
 
-    python -m omniserver_b200.ops.microbench [--what gemm|attn_decode|attn_prefill|norm|all]
+    python -m omniserver_b200.ops.microbench [--what gemm|gemm_prefill|attn_decode|attn_prefill|ffn_fused|norm|all]
         [--batch 1,8,64] [--ctx 2048] [--hidden 1536 --heads 12 --kv-heads 2 --head-dim 128 --inter 8960 --vocab 151936]
 
 Every timed call runs on its own copy of the weights or cache pages (enough copies to exceed the
@@ -155,6 +155,33 @@ def bench_attn_prefill(args, K, dev, peak) -> None:
     print(f"== prefill attention: {ctx} tokens, causal: {us:8.1f} us  {flops / us / 1e6:7.1f} TFLOP/s", flush=True)
 
 
+def bench_ffn_fused(args, K, dev, peak) -> None:
+    """The feed-forward half of a layer for a decode step: the persistent kernel against the three kernels it
+    replaces (add + norm, gate/up with the activation, down), each layer on weights of its own."""
+    H, I = args.hidden, args.inter
+    n_rot = max(3, int(300e6 // (3 * I * H * 2)) + 1)
+    wgu = [torch.randn(2 * I, H, device=dev, dtype=torch.bfloat16) * H ** -0.5 for _ in range(n_rot)]
+    wd = [torch.randn(H, I, device=dev, dtype=torch.bfloat16) * I ** -0.5 for _ in range(n_rot)]
+    gm = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    print("== feed-forward half, decode: norm + gate/up + silu*up + down  (us | GB/s of both weights | fraction of %.0f GB/s)" % peak)
+    for B in args.batch:
+        x = torch.randn(B, H, device=dev, dtype=torch.bfloat16)
+        res = torch.randn(B, H, device=dev)
+        cols = []
+        if K.can_ffn_decode_fused(x, gm, wgu[0], wd[0]):
+            us = graph_time_us(lambda i: K.ffn_decode_fused(x, res, gm, 1e-6, wgu[i], wd[i]), n_rot)
+            gbs = 3 * I * H * 2 / us / 1e3
+            cols.append(f"persistent: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+
+        def separate(i):
+            h, _ = K.add_rmsnorm(x, res, gm, 1e-6, torch.bfloat16)
+            K.linear(K.gate_up_silu(h, wgu[i], torch.bfloat16), wd[i], None, torch.bfloat16)
+        us = graph_time_us(separate, n_rot)
+        gbs = 3 * I * H * 2 / us / 1e3
+        cols.append(f"three kernels: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+        print(f"ffn half B={B:3d} H={H} I={I} | " + " | ".join(cols), flush=True)
+
+
 def bench_norm(args, K, dev, peak) -> None:
     H = args.hidden
     print("== add + RMSNorm, rotary + cache write")
@@ -168,7 +195,7 @@ def bench_norm(args, K, dev, peak) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--what", default="all", choices=["all", "gemm", "gemm_prefill", "attn_decode", "attn_prefill", "norm"])
+    ap.add_argument("--what", default="all", choices=["all", "gemm", "gemm_prefill", "attn_decode", "attn_prefill", "ffn_fused", "norm"])
     ap.add_argument("--only", default="", help="comma-separated projection names to restrict --what gemm / gemm_prefill to")
     ap.add_argument("--rows", default="2048", help="row counts for --what gemm_prefill")
     ap.add_argument("--batch", default="1,8,64")
@@ -206,6 +233,8 @@ def main() -> None:
             bench_attn_decode(args, K, dev, peak)
         if args.what in ("all", "attn_prefill"):
             bench_attn_prefill(args, K, dev, peak)
+        if args.what in ("all", "ffn_fused"):
+            bench_ffn_fused(args, K, dev, peak)
         if args.what in ("all", "norm"):
             bench_norm(args, K, dev, peak)
 

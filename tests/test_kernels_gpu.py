@@ -506,7 +506,11 @@ def test_attn_decode_fused(H, nh, nkv, hd, ps, rot, kv_lens, window):
     slot_map = torch.stack([bt[s, (kv - 1) // ps] * ps + (kv - 1) % ps for s, kv in enumerate(kv_lens)]).to(torch.int32)
     didx = torch.arange(S, dtype=torch.int32, device=DEV)
     k = K()
-    assert k.can_attn_decode_fused(x, gm, wqkv, bqkv, wo, kc, nh, nkv, hd, S, 0, rot)
+    k.fuse_attn_decode = True          # off by default (no faster in a full step); the kernel is kept and tested
+    try:
+        assert k.can_attn_decode_fused(x, gm, wqkv, bqkv, wo, kc, nh, nkv, hd, S, 0, rot)
+    finally:
+        k.fuse_attn_decode = False
     # the separate kernels
     k1, v1 = kc.clone(), vc.clone()
     h, res_want = k.add_rmsnorm(x, res.clone(), gm, 1e-6, torch.bfloat16)
