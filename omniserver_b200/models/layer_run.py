@@ -45,7 +45,7 @@ class FusedLayerRun:
         if m.get("kind") != "gqa_rope" or f.get("kind") != "swiglu":
             return None
         tensors = [desc["norm_attn"], desc["norm_ffn"], m["w_qkv"], m["w_o"], f["w_gate_up"], f["w_down"], binding.k_cache]
-        if any(t is None or t.dtype != torch.bfloat16 or not t.is_cuda for t in tensors):
+        if any(t is None or t.dtype != torch.bfloat16 for t in tensors):
             return None
         return (m["nh"], m["nkv"], m["hd"], m["scale"], id(m["position"]), m["b_qkv"] is None, f["intermediate_size"],
                 desc["norm_attn"].shape[0], binding.group, tuple(binding.k_cache.shape))
