@@ -1,21 +1,26 @@
-// Decode-step layers as one persistent kernel: one CTA per SM, all resident at once (cooperative launch).
+// Decode-step layers as persistent kernels: one CTA per SM, all resident at once (cooperative launch).
 //
-// A decode step of a few rows is bound by reading the weights once. Run as one kernel per
-// projection, every kernel pays its start (launch, first loads in flight) and its tail again, and the
-// memory pipe drains at each boundary. Here one warp per CTA streams the CTA's share of every weight
-// matrix through a ring of shared-memory tiles with bulk asynchronous copies, stage after stage without
-// a pause: the weights do not depend on the activations, so the stream runs ahead across the points
-// where the CTAs have to wait for one another. Eight warps consume the tiles with m16n8k16 MMAs (weight
-// rows on the M side, up to 8 batch rows on the N side, the K range of a tile split over the warps and
-// summed through shared memory). Between stages the CTAs meet at a barrier in global memory; every
-// wait is bounded and reports through the error flag instead of hanging.
+// A decode step of a few rows is bound by reading the weights once. Run as one kernel per projection, every
+// kernel pays its start (launch, first loads in flight) and its tail again, and the memory pipe drains at each
+// boundary. Here one warp per CTA streams the CTA's share of every weight matrix through a ring of
+// shared-memory tiles with bulk asynchronous copies, stage after stage without a pause: the weights do not
+// depend on the activations, so the stream runs ahead across the points where the CTAs have to wait for one
+// another. A second warp streams activations that other CTAs wrote (the input of a projection that follows a
+// grid barrier) through tiles of their own. Eight warps consume the tiles with m16n8k16 MMAs (weight rows on
+// the M side, up to 8 batch rows on the N side, the K range of a tile split over the warps and summed in a
+// fixed order through shared memory). An RMS norm in front of a projection is computed by every CTA itself.
+// Between stages the CTAs meet at a barrier in global memory; every wait is bounded and reports through the
+// error flag instead of hanging.
 //
-// Feed-forward half:   r = residual + x;  h = rmsnorm(r) * w   (every CTA, redundantly, fp32)
-//                      act = silu(h Wg^T) * (h Wu^T)            (pairs of rows of W split over the CTAs)
-//                      -- grid barrier --
-//                      y = act Wd^T                              (rows of Wd split over the CTAs)
+// Kernels:
+//   norm_linear_decode_kernel   y = (rmsnorm(res + x) * w) W^T + b          (no CTA waits for another)
+//   ffn_decode_fused_kernel     r = res + x;  h = rmsnorm(r) * w;  act = silu(h Wg^T) * (h Wu^T)
+//                               -- grid barrier --  y = act Wd^T
+//   attn_decode_fused_kernel    norm, qkv -- barrier -- rotary, cache write, attention over the cache (the
+//                               device function of attn_decode_stream.cuh) -- barrier -- y = attn Wo^T
+//   decode_layers_fused_kernel  the last two, layer after layer, as one launch
 // Formulas: omniserve/kernels/fused_ops.py:21-29, 43-57 (add + norm), 111-119 (silu * up);
-// omniserve/model/qwen2_llm.py:116-134 (the feed-forward), 137-157 (the residual stream).
+// omniserve/model/qwen2_llm.py:75-113 (attention), 116-134 (feed-forward), 137-157 (the residual stream).
 #include <type_traits>
 
 #include "attn_decode_stream.cuh"
@@ -1027,10 +1032,6 @@ int& fused_with_pdl() {
   static int v = 1;
   return v;
 }
-int& fused_geometry() {
-  static int v = 0;
-  return v;
-}
 int& fused_cooperative() {
   static int v = 1;
   return v;
@@ -1103,7 +1104,6 @@ int sm_count() {
 // the driver refuses it beside the cooperative one), and a switch for the cooperative attribute.
 OSB_API int osb_fused_pdl_state() { return fused_with_pdl(); }
 OSB_API void osb_fused_set_cooperative(int on) { fused_cooperative() = on; }
-OSB_API void osb_fused_set_geometry(int g) { fused_geometry() = g; }
 
 // 1 when the fused feed-forward has a build for these sizes.
 OSB_API int osb_ffn_decode_fused_supported(int H, int I) {
@@ -1128,7 +1128,7 @@ OSB_API int osb_ffn_decode_fused(void* y, float* res_out, const void* x, const f
   const int n_sm = sm_count();
   typedef Geometry<16, 12, 3, 3> GeoB;
   typedef Geometry<12, 7, 7, 4> GeoA;
-  if (H == 1536 && I == 8960) return fused_geometry() ? launch_ffn<12, 70, GeoA>(p, n_sm, stream) : launch_ffn<12, 70, GeoB>(p, n_sm, stream);
+  if (H == 1536 && I == 8960) return launch_ffn<12, 70, GeoB>(p, n_sm, stream);
   if (H == 256 && I == 512) return launch_ffn<2, 4, GeoB>(p, n_sm, stream);
   if (H == 384 && I == 1920) return launch_ffn<3, 15, GeoA>(p, n_sm, stream);
   return launch_ffn<16, 2, GeoB>(p, n_sm, stream);

@@ -531,6 +531,69 @@ def test_attn_decode_fused(H, nh, nkv, hd, ps, rot, kv_lens, window):
         assert float((got.float() - want).norm() / want.norm()) < 1e-2
 
 
+@pytest.mark.parametrize("H,nh,nkv,hd,I,ps,rot", [(256, 4, 2, 64, 512, 8, 32), (384, 4, 1, 128, 1920, 16, 128),
+                                                  (1536, 12, 2, 128, 8960, 16, 128)])
+@pytest.mark.parametrize("kv_lens", [[300], [5, 900, 17, 16, 2048, 33, 1, 640]])
+def test_decode_layers_fused(H, nh, nkv, hd, I, ps, rot, kv_lens):
+    """Three whole layers as ONE persistent kernel (five grid barriers per layer, the weights of all layers as one
+    stream, the residual stream alternating between two buffers) against the same layers run kernel by kernel.
+    Every layer has a cache of its own and a window of its own."""
+    S, L = len(kv_lens), 3
+    nq = (nh + 2 * nkv) * hd
+    windows = [None, 100, None]
+    _, _, _, bt, cu_q, seq_lens, tok_seq = [t.to(DEV) for t in _paged_case([1] * S, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=5)]
+    layers = []
+    for l in range(L):
+        _, kc, vc, _, _, _, _ = _paged_case([1] * S, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=5 + 7 * l)
+        layers.append(dict(
+            norm_attn=(1.0 + 0.2 * rnd(H, seed=40 + l)).to(torch.bfloat16).to(DEV),
+            w_qkv=rnd(nq, H, dtype=torch.bfloat16, seed=10 + l, scale=H ** -0.5).to(DEV),
+            b_qkv=rnd(nq, dtype=torch.bfloat16, seed=20 + l, scale=0.3).to(DEV),
+            w_o=rnd(H, nh * hd, dtype=torch.bfloat16, seed=30 + l, scale=(nh * hd) ** -0.5).to(DEV),
+            norm_ffn=(1.0 + 0.2 * rnd(H, seed=50 + l)).to(torch.bfloat16).to(DEV),
+            w_gate_up=rnd(2 * I, H, dtype=torch.bfloat16, seed=60 + l, scale=H ** -0.5).to(DEV),
+            w_down=rnd(H, I, dtype=torch.bfloat16, seed=70 + l, scale=I ** -0.5).to(DEV),
+            k_cache=kc.to(DEV), v_cache=vc.to(DEV), eps_attn=1e-6, eps_ffn=1e-5, window=windows[l]))
+    x = rnd(S, H, dtype=torch.bfloat16).to(DEV)
+    ang = rnd(S, rot // 2, seed=3, scale=3.0)
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+    slot_map = torch.stack([bt[s, (kv - 1) // ps] * ps + (kv - 1) % ps for s, kv in enumerate(kv_lens)]).to(torch.int32)
+    didx = torch.arange(S, dtype=torch.int32, device=DEV)
+    k = K()
+    # kernel by kernel, on copies of the caches
+    xx, rr, caches = x, None, []
+    for d in layers:
+        kc, vc = d["k_cache"].clone(), d["v_cache"].clone()
+        h, rr = k.add_rmsnorm(xx, rr, d["norm_attn"], d["eps_attn"], torch.bfloat16)
+        qkv = k.linear(h, d["w_qkv"], d["b_qkv"], torch.bfloat16)
+        a = k.paged_attention(qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, d["window"], 1, max(kv_lens),
+                              torch.bfloat16, decode_index=didx, n_decode=S, n_multi=0, rope=(cos, sin, slot_map, rot))
+        y = k.linear(a, d["w_o"], None, torch.bfloat16)
+        h, rr = k.add_rmsnorm(y, rr, d["norm_ffn"], d["eps_ffn"], torch.bfloat16)
+        xx = k.linear(k.gate_up_silu(h, d["w_gate_up"], torch.bfloat16), d["w_down"], None, torch.bfloat16)
+        caches.append((kc, vc))
+    k.fuse_decode_layers = True            # off by default; the kernel is kept and tested
+    try:
+        assert k.can_decode_layers_fused(x, H, nh, nkv, hd, I, S, 0, rot)
+    finally:
+        k.fuse_decode_layers = False
+    keep = [(d["k_cache"].clone(), d["v_cache"].clone()) for d in layers]
+    table = k.decode_layers_table(layers, torch.device(DEV))
+    for _ in range(2):
+        for d, (kc0, vc0) in zip(layers, keep):
+            d["k_cache"].copy_(kc0)
+            d["v_cache"].copy_(vc0)
+        got, res = k.decode_layers_fused(table, L, x, None, I, bt, slot_map, cu_q, seq_lens, didx, nh, nkv, hd, hd ** -0.5,
+                                         max(kv_lens), cos, sin, rot, {})
+        k.check_device_errors()
+        assert float((res - rr).norm() / rr.norm()) < 1e-2
+        assert float((got.float() - xx.float()).norm() / xx.float().norm()) < 3e-2
+        assert float((got.float() - xx.float()).abs().max()) <= 2.0 ** -4 * float(xx.float().abs().max()) + 1e-3
+        for d, (kc, vc) in zip(layers, caches):
+            assert float((d["k_cache"].float() - kc.float()).norm() / kc.float().norm()) < 1e-2
+            assert float((d["v_cache"].float() - vc.float()).norm() / vc.float().norm()) < 1e-2
+
+
 @pytest.mark.parametrize("window", [None, 100])
 def test_decode_attention_finds_one_key_that_matters(window):
     """As below, for the split-key decode kernel: one key dominates, placed at tile, split and window edges."""
