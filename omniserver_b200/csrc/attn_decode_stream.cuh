@@ -26,7 +26,7 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
-// through the L2 only: the last split reads back the key and value that this CTA has just stored
+// through the L2 only (the L1 is not asked to keep lines that are read once)
 __device__ __forceinline__ uint4 ld_cg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
 // K and V of one block of 16 keys as this lane needs them: [half of the block: keys 8h + g][32-dim block Db]
@@ -187,11 +187,14 @@ __device__ __forceinline__ void attn_stream_unit(
     }
   };
 
-  // Everything read so far was written by the host before the step. In the fused rotary form the blocks of
-  // every split but the last do not depend on the kernel before this one: their first loads start before the
-  // wait for it. (The last split stores the new key and value itself and reads them back.)
+  // Everything read so far was written by the host before the step.
   KVRegs<NDB> cur, nxt;
-  const bool early = fr.cos_t != nullptr && split != last_split;
+  // In the fused rotary form no block depends on the kernel before this one: the new token's own key and value,
+  // which only the last split sees, do not come from the cache (its row there is stale until this kernel has
+  // stored it) but from shared memory, where this CTA puts them, and replace that row of the loaded block.
+  const bool early = fr.cos_t != nullptr;
+  bf16* ks = qs + 8 * stride;   // rows 8 and 9 of the q tile: heads are the N side, only rows 0-7 hold queries
+  bf16* vs = qs + 9 * stride;
   // page ids of this warp's first four blocks in one round trip; then one block further every iteration
   int2 pg1 = pages_of(warp + NW), pg2 = pages_of(warp + 2 * NW), pg3 = pages_of(warp + 3 * NW);
   if (early) {
@@ -202,28 +205,38 @@ __device__ __forceinline__ void attn_stream_unit(
   STL(1);
   wait_for_q();   // until here nothing of this step's q, k, v was touched
   STL(2);
-  if (fr.cos_t != nullptr && split == last_split && ht == 0) {
+  if (fr.cos_t != nullptr && split == last_split) {
     const int slot = fr.slot_map[q0];
     const int page = slot >> log2ps, off = slot & ps_mask;
-    if (page >= 0 && page < num_pages) {
-      const size_t dst = ((((size_t)page * nkv + kvh) << log2ps) + off) * HD;
-      bf16* kd = const_cast<bf16*>(kc) + dst;
-      bf16* vd = const_cast<bf16*>(vc) + dst;
-      const bf16* ksrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + kvh) * HD;
-      const bf16* vsrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + nkv + kvh) * HD;
-      const int half = fr.rot >> 1;
-      const float* cs = fr.cos_t + (size_t)q0 * half;
-      const float* sn = fr.sin_t + (size_t)q0 * half;
-      for (int d = tid; d < half; d += NT) {
-        const float x1 = __bfloat162float(ld_q1<PERSIST>(ksrc + d)), x2 = __bfloat162float(ld_q1<PERSIST>(ksrc + d + half));
-        kd[d] = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]);
-        kd[d + half] = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
+    const bool store = ht == 0 && page >= 0 && page < num_pages;   // one CTA of the kv head stores
+    const size_t dst = store ? ((((size_t)page * nkv + kvh) << log2ps) + off) * HD : 0;
+    bf16* kd = const_cast<bf16*>(kc) + dst;
+    bf16* vd = const_cast<bf16*>(vc) + dst;
+    const bf16* ksrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + kvh) * HD;
+    const bf16* vsrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + nkv + kvh) * HD;
+    const int half = fr.rot >> 1;
+    const float* cs = fr.cos_t + (size_t)q0 * half;
+    const float* sn = fr.sin_t + (size_t)q0 * half;
+    for (int d = tid; d < half; d += NT) {
+      const float x1 = __bfloat162float(ld_q1<PERSIST>(ksrc + d)), x2 = __bfloat162float(ld_q1<PERSIST>(ksrc + d + half));
+      const bf16 a = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]), b = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
+      ks[d] = a;
+      ks[d + half] = b;
+      if (store) {
+        kd[d] = a;
+        kd[d + half] = b;
       }
-      for (int d = fr.rot + tid; d < HD; d += NT) kd[d] = ld_q1<PERSIST>(ksrc + d);
-      for (int d = tid; d < HD; d += NT) vd[d] = ld_q1<PERSIST>(vsrc + d);
     }
-    __threadfence();
-    unit_sync<PERSIST>();
+    for (int d = fr.rot + tid; d < HD; d += NT) {
+      const bf16 a = ld_q1<PERSIST>(ksrc + d);
+      ks[d] = a;
+      if (store) kd[d] = a;
+    }
+    for (int d = tid; d < HD; d += NT) {
+      const bf16 a = ld_q1<PERSIST>(vsrc + d);
+      vs[d] = a;
+      if (store) vd[d] = a;
+    }
   }
   if (!early) {
     load_block(warp, pages_of(warp), cur);
@@ -241,7 +254,7 @@ __device__ __forceinline__ void attn_stream_unit(
       const int per_row = hc + (cpr - 2 * hc);
       const float* cs = fr.cos_t + (size_t)q0 * half;
       const float* sn = fr.sin_t + (size_t)q0 * half;
-      for (int i = tid; i < 16 * per_row; i += NT) {
+      for (int i = tid; i < 8 * per_row; i += NT) {
         const int r = i / per_row, cc0 = i - r * per_row;
         bf16* dst = qs + r * stride;
         const bf16* src = q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * HD;
@@ -271,7 +284,7 @@ __device__ __forceinline__ void attn_stream_unit(
         *reinterpret_cast<uint4*>(dst + half + cc0 * 8) = b;
       }
     } else {
-      for (int i = tid; i < 16 * cpr; i += NT) {
+      for (int i = tid; i < 8 * cpr; i += NT) {
         const int r = i / cpr, cc = i - r * cpr;
         uint4 v = zero4;
         if (r < rows) v = ld_q16<PERSIST>(q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * HD + cc * 8);
@@ -313,6 +326,22 @@ __device__ __forceinline__ void attn_stream_unit(
     pg2 = pg3;
     pg3 = pg4;
     if (b / NW < 6) STL(4 + b / NW);
+    if (fr.cos_t != nullptr && split == last_split && (p - k_begin) / BLK == b && g == ((p - k_begin) & 7)) {
+      // this lane holds the new token's row of the block: take it from shared memory
+      if (((p - k_begin) & 8) == 0) {
+#pragma unroll
+        for (int db = 0; db < NDB; ++db) {
+          cur.k[0][db] = *reinterpret_cast<const uint4*>(ks + db * 32 + c * 8);
+          cur.v[0][db] = *reinterpret_cast<const uint4*>(vs + db * 32 + c * 8);
+        }
+      } else {
+#pragma unroll
+        for (int db = 0; db < NDB; ++db) {
+          cur.k[1][db] = *reinterpret_cast<const uint4*>(ks + db * 32 + c * 8);
+          cur.v[1][db] = *reinterpret_cast<const uint4*>(vs + db * 32 + c * 8);
+        }
+      }
+    }
     float st[4] = {0.0f, 0.0f, 0.0f, 0.0f}, su[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // two chains of dependent MMAs
 #pragma unroll
     for (int db = 0; db < NDB; ++db) {

@@ -122,6 +122,9 @@ template <uint32_t R> __device__ __forceinline__ void reg_take() {
 template <uint32_t R> __device__ __forceinline__ void reg_give() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
 }
+// After generic-proxy stores to global memory that another CTA will read with bulk asynchronous copies (the
+// async proxy), before the barrier that tells it so.
+__device__ __forceinline__ void publish_for_bulk_copies() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCT) : "memory"); }
 __device__ __forceinline__ uint2 lds64(const uint8_t* p) {
   uint2 v;
@@ -499,6 +502,7 @@ __global__ void __launch_bounds__(NTHREADS_ACT, 1) ffn_decode_fused_kernel(const
     }
   }
   FTL(4);
+  publish_for_bulk_copies();
   consumer_sync();   // also: every warp has its fragments out of xs, whose memory the activation tiles use next
   FTL(5);
   if (threadIdx.x == 0) grid_barrier(p.bar, target, sh, p.err);
@@ -755,6 +759,7 @@ __global__ void __launch_bounds__(NTHREADS_WIDE, 1) attn_decode_fused_kernel(con
     wait_qkv();
   }
   FTL(5);
+  publish_for_bulk_copies();
   consumer_sync();
   if (threadIdx.x == 0) grid_barrier(p.bar, target + (unsigned long long)G, sh, p.err);
   consumer_sync();
@@ -944,6 +949,7 @@ __global__ void __launch_bounds__(NTHREADS_WIDE, 1) decode_layers_fused_kernel(c
       wait_qkv();
     }
     if (l == 1) FTL(4);
+    publish_for_bulk_copies();
     consumer_sync();
     if (threadIdx.x == 0) {
       target += (unsigned long long)G;
@@ -996,6 +1002,7 @@ __global__ void __launch_bounds__(NTHREADS_WIDE, 1) decode_layers_fused_kernel(c
       }
     }
     if (l == 1) FTL(8);
+    publish_for_bulk_copies();
     consumer_sync();
     if (threadIdx.x == 0) {
       target += (unsigned long long)G;
