@@ -110,15 +110,13 @@ class CudaKernels:
         # few rows: the norm before a projection can run inside the projection's kernel. Off: measured in a full
         # decode step it is slower than the two kernels (every CTA re-reads the rows of the residual stream)
         self.fuse_prenorm = False
-        #: Row counts from which the tcgen05 kernel is used (measured on B200 at this model's shapes:
-        #: with fewer rows there are too few 128-row tiles to fill 148 SMs and the library's split
-        #: kernels win; the fused SiLU*up epilogue pays off earlier because it saves a whole pass)
         # Rows from which a plain projection runs in this repository's tcgen05 kernels. Measured, the vendor
         # library is 15-40 % faster on plain products at every row count (it spreads shapes with few tiles over
         # all SMs), so they go to the library; the fused SwiGLU product, which the library cannot do in one
-        # kernel, is 35-40 % faster here and always runs in the tcgen05 kernels.
+        # kernel, is 35-40 % faster here at many rows and still ahead of library + activation kernel at 64 rows
+        # (15.6 vs 16.2 us; at 24 rows the library pair wins, 14.0 vs 19.1 us).
         self.tcgen05_min_rows = 1 << 30
-        self.tcgen05_min_rows_swiglu = 256
+        self.tcgen05_min_rows_swiglu = 64
         # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
