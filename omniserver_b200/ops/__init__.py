@@ -167,6 +167,8 @@ class CudaKernels:
             v = int(flag.item())
             if v != 0:
                 flag.zero_()
+                for bar, _ in self._fused.values():
+                    bar.zero_()     # a CTA that gave up at a grid barrier leaves the counter between two multiples
                 raise KernelError("device-side check failed: " + _DEVICE_ERR.get(v, f"code {v}"))
 
     # ------------------------------------------------------------------ embedding
