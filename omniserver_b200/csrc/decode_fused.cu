@@ -571,14 +571,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) norm_linear_decode_kernel(const _
     return;
   }
   Consumer<Geo> co{sh, slots, xs, red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
-  uint2 nw[HT];
-#pragma unroll
-  for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
-  pdl_wait();
-  norm_rows<HT>(p.x, p.res_in, cta == 0 ? p.res_out : nullptr, nw, p.eps, p.B, xs, warp, lane);
-  consumer_sync();
   uint32_t xf[HT][2];
-  load_local_x<HT, KTW, NCH>(xf, xs, co.wk, lane);
+  if (p.norm_w != nullptr) {
+    uint2 nw[HT];
+#pragma unroll
+    for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
+    pdl_wait();
+    norm_rows<HT>(p.x, p.res_in, cta == 0 ? p.res_out : nullptr, nw, p.eps, p.B, xs, warp, lane);
+    consumer_sync();
+    load_local_x<HT, KTW, NCH>(xf, xs, co.wk, lane);
+  } else {
+    // no norm in front: the rows' fragments come straight from global memory
+    pdl_wait();
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+      for (int j = 0; j < KTW; ++j) {
+        const int k0 = ch * KC + (co.wk * KTW + j) * 16 + 4 * t;
+        uint2 v = make_uint2(0u, 0u);
+        if (g < p.B) v = __ldcg(reinterpret_cast<const uint2*>(p.x + (size_t)g * H + k0));
+        xf[ch * KTW + j][0] = v.x;
+        xf[ch * KTW + j][1] = v.y;
+      }
+  }
   pdl_trigger();
   for (int rg = r0; rg < r1; rg += RS) {
     const int nr = min(RS, r1 - rg);
@@ -1239,7 +1255,7 @@ OSB_API int osb_decode_layers_fused(const void* layers, int n_layers, void* y, f
 OSB_API int osb_norm_linear_decode_supported(int H) { return H == 1536 || H == 256 || H == 384 || H == 2048; }
 
 // y [B,N] = (rmsnorm(res_in + x) * norm_w) W^T + bias; res_out = res_in + x (fp32). B <= 8, everything bf16
-// but the residual stream.
+// but the residual stream. Without norm_w (then no res_in, no res_out): y = x W^T + bias.
 OSB_API int osb_norm_linear_decode(void* y, float* res_out, const void* x, const float* res_in, const void* norm_w,
                                    float eps, const void* w, const void* bias, int* err, int B, int N, int H,
                                    cudaStream_t stream) {
@@ -1247,6 +1263,7 @@ OSB_API int osb_norm_linear_decode(void* y, float* res_out, const void* x, const
   if (B > MAX_B || !osb_norm_linear_decode_supported(H)) return OSB_ERR_UNSUPPORTED;
   if ((((uintptr_t)res_out | (uintptr_t)x | (uintptr_t)res_in | (uintptr_t)norm_w | (uintptr_t)w) & 15) != 0)
     return OSB_ERR_BAD_SHAPE;
+  if (norm_w == nullptr && (res_in != nullptr || res_out != nullptr)) return OSB_ERR_BAD_SHAPE;
   NormLinearParams p;
   p.x = (const bf16*)x; p.res_in = res_in; p.res_out = res_out; p.norm_w = (const bf16*)norm_w; p.w = (const bf16*)w;
   p.bias = (const bf16*)bias; p.y = (bf16*)y; p.err = err; p.eps = eps; p.B = B; p.N = N;

@@ -124,6 +124,7 @@ class CudaKernels:
         self._pinned_stream: Optional[ctypes.c_void_p] = None
         self.fuse_ffn_decode = True
         self.fuse_norm_linear_decode = True
+        self.stream_linear_decode = True
         # the attention half and whole runs of layers as persistent kernels: built and tested; in a full decode step
         # they measured 3 % and 5 % slower than the separate kernels (five grid barriers per layer), so they are off
         self.fuse_attn_decode = False
@@ -254,6 +255,15 @@ class CudaKernels:
         M, K = x.shape
         N = w.shape[0]
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if (self.stream_linear_decode and out_dtype == torch.bfloat16 and 0 < M <= self.FUSED_MAX_ROWS
+                    and N <= self.STREAM_LINEAR_MAX_N and (bias is None or bias.dtype == torch.bfloat16)
+                    and bool(self.lib.osb_norm_linear_decode_supported(K))):
+                # a few rows and a matrix that one wave of CTAs covers: the weight-streaming kernel without its norm
+                y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+                rc = self.lib.osb_norm_linear_decode(_p(y), _p(None), _p(x), _p(None), _p(None), ctypes.c_float(0.0), _p(w),
+                                                     _p(bias), _p(self.err_flag(x.device)), M, N, K, self._stream())
+                self._ok(rc, "linear_decode")
+                return y
             return self._linear_bf16(x, w, bias, out_dtype)
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         rc = self.lib.osb_gemm_simt(_p(y), _dt(y), _p(x), _dt(x), _p(w), _dt(w), _p(bias),
@@ -363,6 +373,7 @@ class CudaKernels:
         return y, res_out
 
     FUSED_MAX_ROWS = 8
+    STREAM_LINEAR_MAX_N = 4096     # rows of W up to which the streaming projection without norm is used
     FUSED_MAX_SPLITS = 16
 
     def _fused_state(self, device: torch.device, width: int) -> Tuple[torch.Tensor, torch.Tensor]:
