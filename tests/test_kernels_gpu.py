@@ -69,7 +69,8 @@ def test_embed_lookup_reports_bad_id():
 
 @pytest.mark.parametrize("xdt", DTYPES)
 @pytest.mark.parametrize("wdt", DTYPES)
-@pytest.mark.parametrize("T,H,eps", [(5, 96, 1e-5), (3, 1536, 1e-6), (2, 5000, 1e-6), (1, 17, 1e-3)])
+@pytest.mark.parametrize("T,H,eps", [(5, 96, 1e-5), (3, 1536, 1e-6), (2, 5000, 1e-6), (1, 17, 1e-3), (300, 1536, 1e-6), (67, 2048, 1e-5),
+                                     (100, 256, 1e-6), (64, 1280, 1e-6)])
 def test_add_rmsnorm(xdt, wdt, T, H, eps):
     x = rnd(T, H, dtype=xdt, scale=3.0)
     res = rnd(T, H, seed=1, scale=5.0)
