@@ -44,6 +44,7 @@ MODEL_2B = {
 FULL_LAYERS = 28
 CONTEXT = 2048
 NEW_TOKENS = 256
+PAGE_SIZE = 16       # tokens per cache page (--page-size)
 SEED = 2
 
 
@@ -147,7 +148,7 @@ def run_ours(args):
     max_batch = max(args.batch, 1 if args.no_points else 64)
     ctx_total = CONTEXT + NEW_TOKENS
     pool_tokens = max_batch * (-(-ctx_total // 64) * 64) + 4096
-    ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=pool_tokens, max_requests=max_batch + 2,
+    ec = EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=pool_tokens, max_requests=max_batch + 2,
                       check_device_errors=False, cuda_graphs=not args.no_graphs)
     t0 = time.time()
     runner = build_runner(config=cfg, seed=SEED, engine_config=ec, random_on_device=True)
@@ -286,7 +287,7 @@ def run_ours(args):
         "config": {"model": "Qwen2-VL-2B text decoder (random weights)", "layers": args.layers,
                    "layers_of_model": FULL_LAYERS, "hidden_size": 1536, "heads": 12, "kv_heads": 2, "head_dim": 128,
                    "intermediate_size": 8960, "vocab_size": 151936, "tied_head": True, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "new_tokens": NEW_TOKENS, "page_size": 16, "parallelism": "single GPU",
+                   "seq_len": CONTEXT, "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE, "parallelism": "single GPU",
                    "l2": "inputs (3 GB of weights) larger than L2, no flush"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
         "points": points, "build_s": round(build_s, 1),
@@ -311,12 +312,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host")
     ap.add_argument("--only", default="all", choices=["all", "decode"],
                     help="'decode': skip the prefill repeats, the points and the end-to-end run (for profiling)")
     args = ap.parse_args()
+    globals()["PAGE_SIZE"] = args.page_size
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:
