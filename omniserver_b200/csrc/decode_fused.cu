@@ -312,6 +312,49 @@ struct Consumer {
     if (other) *other = s2;
     return s;
   }
+
+  // ---- whole stages. epi(row, n, sum) is called by the thread that holds output (row, batch row n < B).
+  // rows [r0, r1) of a projection whose activation's fragments are in registers
+  template <int KTW, int NCH, int NX, class Epi>
+  __device__ __forceinline__ void rows_local(const uint32_t (&xf)[NX][2], int r0, int r1, int B, Epi epi) {
+    for (int rg = r0; rg < r1; rg += RS) {
+      const int nr = min(RS, r1 - rg);
+      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      row_group_local<KTW, NCH, 8>(c, xf);
+      const float s = reduce(c, nullptr);
+      const int i = warp * 32 + lane;
+      const int row = i >> 3, n = i & 7;
+      if (i < 128 && row < nr && n < B) epi(rg + row, n, s);
+    }
+  }
+  // pairs [p0, p1) of a gated projection: epi(pair, n, gate sum, up sum)
+  template <int KTW, int NCH, int NX, class Epi>
+  __device__ __forceinline__ void pairs_local(const uint32_t (&xf)[NX][2], int p0, int p1, int B, Epi epi) {
+    constexpr int PG = Geo::PG;
+    for (int pg = p0; pg < p1; pg += PG) {
+      const int np = min(PG, p1 - pg);
+      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      row_group_local<KTW, NCH, PG>(c, xf);
+      float up;
+      const float gate = reduce(c, &up);
+      const int i = warp * 32 + lane;
+      const int pair = i >> 3, n = i & 7;
+      if (i < 64 && pair < np && n < B) epi(pg + pair, n, gate, up);
+    }
+  }
+  // rows [r0, r1) of a projection whose activation the activation warp streams (after act_begin())
+  template <int KTW, int NCH, class Epi>
+  __device__ __forceinline__ void rows_streamed(int r0, int r1, int B, Epi epi) {
+    for (int rg = r0; rg < r1; rg += RS) {
+      const int nr = min(RS, r1 - rg);
+      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      row_group_streamed<KTW, NCH, 8>(c);
+      const float s = reduce(c, nullptr);
+      const int i = warp * 32 + lane;
+      const int row = i >> 3, n = i & 7;
+      if (i < 128 && row < nr && n < B) epi(rg + row, n, s);
+    }
+  }
 };
 
 // All CTAs meet: every CTA adds one to a counter that only grows and waits until it reaches `target`
@@ -416,123 +459,207 @@ __device__ __forceinline__ void load_local_x(uint32_t (&xf)[HT][2], const uint8_
     }
 }
 
+// The norm in front of a projection, by every CTA itself: r = res_in + x, h = rmsnorm(r) * w into shared memory
+// (CTA 0 also writes r to res_out), then this warp's fragments of h. `wait_pdl`: the kernel's first use of
+// anything the kernel before it wrote; the norm's weights are fetched before that wait.
+template <int HT, int KTW, int NCH>
+__device__ __forceinline__ void norm_to_fragments(uint32_t (&xf)[HT][2], const bf16* x, const float* res_in, float* res_out,
+                                                  const bf16* norm_w, float eps, int B, uint8_t* xs, int warp, int lane,
+                                                  int wk, bool wait_pdl) {
+  uint2 nw[HT];
+#pragma unroll
+  for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(norm_w + (i * 32 + lane) * 4);
+  if (wait_pdl) pdl_wait();
+  norm_rows<HT>(x, res_in, blockIdx.x == 0 ? res_out : nullptr, nw, eps, B, xs, warp, lane);
+  consumer_sync();
+  load_local_x<HT, KTW, NCH>(xf, xs, wk, lane);
+}
+
+// The consumers of all CTAs meet (see grid_arrive / grid_wait). `for_bulk_copies`: what this CTA stored is read
+// by other CTAs' bulk copies next.
+struct GridSync {
+  unsigned long long* bar;
+  unsigned long long target;   // kept by thread 0
+  unsigned G;
+  Shared* sh;
+  int* err;
+  // after the kernel's wait for the kernel before it: no CTA passes the first barrier before this one arrives,
+  // so the counter is less than a grid size past the multiple that the launch started from
+  __device__ __forceinline__ void begin() {
+    if (threadIdx.x == 0) {
+      unsigned long long v;
+      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(bar) : "memory");
+      target = v - v % (unsigned long long)G;
+    }
+  }
+  __device__ __forceinline__ void arrive(bool for_bulk_copies) {
+    if (for_bulk_copies) publish_for_bulk_copies();
+    consumer_sync();
+    if (threadIdx.x == 0) {
+      grid_arrive(bar, sh);
+      target += (unsigned long long)G;
+    }
+  }
+  __device__ __forceinline__ void wait() {
+    if (threadIdx.x == 0) grid_wait(bar, target, sh, err);
+    consumer_sync();
+  }
+  __device__ __forceinline__ void sync(bool for_bulk_copies) {
+    arrive(for_bulk_copies);
+    wait();
+  }
+};
+
+// What the attention stage needs beside q, k, v of the step: the cache and the step's tables, as
+// osb_attn_decode_stream takes them.
+struct AttnTables {
+  bf16* k_cache;
+  bf16* v_cache;
+  const int* block_table;
+  const int* cu_q;
+  const int* seq_lens;
+  const int* decode_index;
+  int* counters;
+  float* part_o;
+  float* part_ml;
+  attn_stream::FusedRope rope;
+  float scale_log2;
+  int bt_stride, nh, nkv, log2ps, num_pages, window, nsplits;
+};
+
+// Rotary encoding, the new key and value into the cache, attention over the cache: units (request, kv head,
+// split of the keys), one per CTA and turn; the CTA that finishes a (request, kv head) last merges its splits.
+// Called after gs.arrive(): the first unit looks up its pages and starts its first loads before it waits
+// for the other CTAs' q, k, v.
+template <int HD>
+__device__ __forceinline__ void attention_stage(const AttnTables& a, const bf16* qkv, int NQKV, bf16* attn, int B,
+                                                GridSync& gs, uint8_t* scratch, Shared* sh) {
+  const int grp = a.nh / a.nkv;
+  const int ny = a.nkv * ((grp + 7) >> 3);
+  const int units = B * ny * a.nsplits;
+  bool waited = false;
+  auto wait_qkv = [&] {
+    if (!waited) {
+      gs.wait();
+      waited = true;
+    }
+  };
+  for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    const int split = u % a.nsplits, rest = u / a.nsplits;
+    attn_stream::attn_stream_unit<HD, false, true>(
+        wait_qkv, split, rest % ny, rest / ny, ny, scratch, &sh->s_last, attn, a.part_o, a.part_ml, qkv, NQKV, a.k_cache,
+        a.v_cache, a.block_table, a.bt_stride, a.cu_q, a.seq_lens, a.decode_index, a.counters, a.nh, a.nkv, a.log2ps,
+        a.num_pages, a.scale_log2, a.window, 0, a.nsplits, a.rope);
+    wait_qkv();        // a unit that has nothing to do returns before it waits
+    consumer_sync();   // the scratch in shared memory is used again by the next unit and by the tiles after it
+  }
+  wait_qkv();
+}
+
+// Shared memory of every kernel here: weight tiles, activation tiles (the normalised rows and the attention's
+// scratch use the same bytes at other times), the reduction buffers, the barriers.
+template <class Geo>
+struct Carve {
+  uint8_t *slots, *aslots, *xs;
+  float* red;
+  Shared* sh;
+  __device__ __forceinline__ explicit Carve(uint8_t* smem) {
+    slots = smem;
+    aslots = slots + Geo::NST * Geo::SLOT;
+    xs = aslots;
+    red = reinterpret_cast<float*>(aslots + Geo::AST * Geo::ASLOT);
+    sh = reinterpret_cast<Shared*>(red + 2 * NCW * 128);
+  }
+};
+
+template <class Geo> using WeightStreamOf = Streamer<Geo::NST, Geo::SLOT, Geo::SROW, Geo::RS, true>;
+template <class Geo> using ActStreamOf = Streamer<Geo::AST, Geo::ASLOT, Geo::SROW, Geo::RS, false>;
+
+// How a K of KT * 128 elements is cut into pieces of a tile's length
+template <int KT, class Geo>
+struct Pieces {
+  static constexpr int KTW = largest_divisor_le(KT, Geo::MAX_KTW), NCH = KT / KTW, KC = KTW * NCW * 16;
+};
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return (gate / (1.0f + expf(-gate))) * up; }
+
+// The feed-forward half: r = res_in + x; h = rmsnorm(r) * w; act = silu(h Wg^T) * (h Wu^T) -- grid barrier --
+// y = act Wd^T. The consumers' part; `first`: nothing of this kernel has waited for the kernel before it yet.
+template <int HT, int IT, class Geo>
+__device__ __forceinline__ void ffn_half(Consumer<Geo>& co, GridSync& gs, uint8_t* xs, const bf16* x, const float* res_in,
+                                         float* res_out, const bf16* norm_w, float eps, bf16* act, bf16* y, int B, int p0,
+                                         int p1, int r0, int r1, bool first) {
+  constexpr int H = HT * NCW * 16, I = IT * NCW * 16;
+  typedef Pieces<HT, Geo> PH;
+  typedef Pieces<IT, Geo> PI;
+  {
+    uint32_t xf[HT][2];
+    norm_to_fragments<HT, PH::KTW, PH::NCH>(xf, x, res_in, res_out, norm_w, eps, B, xs, co.warp, co.lane, co.wk, first);
+    if (first) gs.begin();
+    FTL(2);
+    co.template pairs_local<PH::KTW, PH::NCH>(xf, p0, p1, B, [&](int pair, int n, float gate, float up) {
+      act[(size_t)n * I + pair] = __float2bfloat16_rn(silu_mul(gate, up));
+    });
+  }
+  FTL(4);
+  gs.sync(true);   // also: every warp has its fragments out of xs, whose memory the activation tiles use next
+  FTL(6);
+  if (first) pdl_trigger();
+  co.act_begin();
+  co.template rows_streamed<PI::KTW, PI::NCH>(r0, r1, B, [&](int row, int n, float s) {
+    y[(size_t)n * H + row] = __float2bfloat16_rn(s);
+  });
+}
+
 template <int HT, int IT, class Geo>
 __global__ void __launch_bounds__(NTHREADS_ACT, 1) ffn_decode_fused_kernel(const __grid_constant__ FfnParams p) {
   constexpr int H = HT * NCW * 16, I = IT * NCW * 16;
-  constexpr int NSTAGE = Geo::NST, ASTAGE = Geo::AST, RS = Geo::RS, PG = Geo::PG, MAX_KTW = Geo::MAX_KTW;
-  constexpr int SLOT_BYTES = Geo::SLOT, ASLOT_BYTES = Geo::ASLOT;
-  typedef Streamer<Geo::NST, Geo::SLOT, Geo::SROW, Geo::RS, true> WeightStream;
-  typedef Streamer<Geo::AST, Geo::ASLOT, Geo::SROW, Geo::RS, false> ActStream;
-  constexpr int KTW_H = largest_divisor_le(HT, MAX_KTW), NCH_H = HT / KTW_H, KC_H = KTW_H * NCW * 16;
-  constexpr int KTW_I = largest_divisor_le(IT, MAX_KTW), NCH_I = IT / KTW_I, KC_I = KTW_I * NCW * 16;
-  constexpr int XS = H * 2 + 32;  // row stride of the normalised rows in shared memory
-  static_assert(MAX_B * XS <= ASTAGE * ASLOT_BYTES, "the normalised rows share the activation tiles' memory");
-
+  typedef Pieces<HT, Geo> PH;
+  typedef Pieces<IT, Geo> PI;
+  static_assert(MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows share the activation tiles' memory");
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* slots = smem;
-  uint8_t* aslots = slots + NSTAGE * SLOT_BYTES;
-  uint8_t* xs = aslots;  // used before the first activation tile is asked for
-  float* red = reinterpret_cast<float*>(aslots + ASTAGE * ASLOT_BYTES);
-  Shared* sh = reinterpret_cast<Shared*>(red + 2 * NCW * 128);
-
+  const Carve<Geo> m(smem);
+  Shared* sh = m.sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = gridDim.x;
   init_shared<Geo>(sh);
-
   int p0, p1, r0, r1;
   cta_rows(I, cta, G, p0, p1);
   cta_rows(H, cta, G, r0, r1);
 
   if (warp == W_WARP) {
     // the weights depend on nothing that runs before this kernel: the stream starts at once
-    WeightStream ws{sh, sh->full, sh->empty, slots, 0u, policy_evict_first(), lane, p.err};
+    WeightStreamOf<Geo> ws{sh, sh->full, sh->empty, m.slots, 0u, policy_evict_first(), lane, p.err};
     FTL(10);
-    ws.pairs(p.w_gate_up, H, I, p0, p1, NCH_H, KC_H);
+    ws.pairs(p.w_gate_up, H, I, p0, p1, PH::NCH, PH::KC);
     FTL(11);
-    ws.rows(p.w_down, I, r0, r1, NCH_I, KC_I);
+    ws.rows(p.w_down, I, r0, r1, PI::NCH, PI::KC);
     FTL(12);
     __syncthreads();
     if (sh->abort_flag) ws.drain();
     return;
   }
   if (warp == A_WARP) {
-    ActStream as{sh, sh->afull, sh->aempty, aslots, 0u, 0ull, lane, p.err};
+    ActStreamOf<Geo> as{sh, sh->afull, sh->aempty, m.aslots, 0u, 0ull, lane, p.err};
     wait_or_abort(&sh->act_ready, 0u, sh, p.err, ERR_GRID_WAIT);
-    as.activation(p.act, I, p.B, (r1 - r0 + RS - 1) / RS, NCH_I, KC_I);
+    as.activation(p.act, I, p.B, (r1 - r0 + Geo::RS - 1) / Geo::RS, PI::NCH, PI::KC);
     __syncthreads();
     if (sh->abort_flag) as.drain();
     return;
   }
-  Consumer<Geo> co{sh, slots, aslots, red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
-  unsigned long long target = 0;
+  Consumer<Geo> co{sh, m.slots, m.aslots, m.red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
+  GridSync gs{p.bar, 0ull, (unsigned)G, sh, p.err};
   FTL(0);
-  // the norm's weights do not depend on the kernel before: fetch them while it finishes
-  uint2 nw[HT];
-#pragma unroll
-  for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
-  pdl_wait();
-  FTL(1);
-  if (threadIdx.x == 0) {
-    // no CTA passes the first barrier before this one arrives: the counter is less than a grid size past
-    // the multiple that the launch started from
-    unsigned long long v;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.bar) : "memory");
-    target = v - v % (unsigned long long)G + (unsigned long long)G;
-  }
-
-  norm_rows<HT>(p.x, p.res_in, cta == 0 ? p.res_out : nullptr, nw, p.eps, p.B, xs, warp, lane);
-  consumer_sync();
-  FTL(2);
-
-  // ---- act = silu(h Wg^T) * (h Wu^T)
-  {
-    uint32_t xf[HT][2];
-    load_local_x<HT, KTW_H, NCH_H>(xf, xs, co.wk, lane);
-    for (int pg = p0; pg < p1; pg += PG) {
-      const int np = min(PG, p1 - pg);
-      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      co.template row_group_local<KTW_H, NCH_H, PG>(c, xf);
-      if (pg == p0) FTL(3);
-      float up;
-      const float gate = co.reduce(c, &up);
-      const int i = warp * 32 + lane;
-      const int pair = i >> 3, n = i & 7;
-      if (i < 64 && pair < np && n < p.B)
-        p.act[(size_t)n * I + pg + pair] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
-    }
-  }
-  FTL(4);
-  publish_for_bulk_copies();
-  consumer_sync();   // also: every warp has its fragments out of xs, whose memory the activation tiles use next
-  FTL(5);
-  if (threadIdx.x == 0) grid_barrier(p.bar, target, sh, p.err);
-  consumer_sync();
-  FTL(6);
-  pdl_trigger();
-  co.act_begin();
-
-  // ---- y = act Wd^T
-  for (int rg = r0; rg < r1; rg += RS) {
-    const int nr = min(RS, r1 - rg);
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    FTL(7);
-    co.template row_group_streamed<KTW_I, NCH_I, 8>(c);
-    FTL(8);
-    const float s = co.reduce(c, nullptr);
-    const int i = warp * 32 + lane;
-    const int row = i >> 3, n = i & 7;
-    if (i < 128 && row < nr && n < p.B) p.y[(size_t)n * H + rg + row] = __float2bfloat16_rn(s);
-  }
+  ffn_half<HT, IT, Geo>(co, gs, m.xs, p.x, p.res_in, p.res_out, p.norm_w, p.eps, p.act, p.y, p.B, p0, p1, r0, r1, true);
   FTL(9);
   __syncthreads();
 }
-
 
 struct NormLinearParams {
   const bf16* x;        // [B, H] branch output of the part before
   const float* res_in;  // [B, H] or null
   float* res_out;       // [B, H]
-  const bf16* norm_w;   // [H]
+  const bf16* norm_w;   // [H], or null: no norm (then no res_in, no res_out)
   const bf16* w;        // [N, H]
   const bf16* bias;     // [N] or null
   bf16* y;              // [B, N]
@@ -542,21 +669,15 @@ struct NormLinearParams {
 };
 
 // y = (rmsnorm(res_in + x) * norm_w) W^T + bias for a few rows: every CTA normalises the rows itself while
-// its rows of W are already on their way; no CTA waits for another.
+// its rows of W are already on their way; no CTA waits for another. Without norm_w: y = x W^T + bias.
 template <int HT, class Geo>
 __global__ void __launch_bounds__(NTHREADS, 1) norm_linear_decode_kernel(const __grid_constant__ NormLinearParams p) {
   constexpr int H = HT * NCW * 16;
-  constexpr int KTW = largest_divisor_le(HT, Geo::MAX_KTW), NCH = HT / KTW, KC = KTW * NCW * 16;
-  constexpr int RS = Geo::RS;
-  typedef Streamer<Geo::NST, Geo::SLOT, Geo::SROW, Geo::RS, true> WeightStream;
-  typedef Streamer<Geo::AST, Geo::ASLOT, Geo::SROW, Geo::RS, false> ActStream;
+  typedef Pieces<HT, Geo> PH;
   static_assert(MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows use the activation tiles' memory");
-
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* slots = smem;
-  uint8_t* xs = slots + Geo::NST * Geo::SLOT;
-  float* red = reinterpret_cast<float*>(xs + Geo::AST * Geo::ASLOT);
-  Shared* sh = reinterpret_cast<Shared*>(red + 2 * NCW * 128);
+  const Carve<Geo> m(smem);
+  Shared* sh = m.sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = gridDim.x;
   init_shared<Geo>(sh);
@@ -564,53 +685,71 @@ __global__ void __launch_bounds__(NTHREADS, 1) norm_linear_decode_kernel(const _
   cta_rows(p.N, cta, G, r0, r1);
 
   if (warp == W_WARP) {
-    WeightStream ws{sh, sh->full, sh->empty, slots, 0u, policy_evict_first(), lane, p.err};
-    ws.rows(p.w, H, r0, r1, NCH, KC);
+    WeightStreamOf<Geo> ws{sh, sh->full, sh->empty, m.slots, 0u, policy_evict_first(), lane, p.err};
+    ws.rows(p.w, H, r0, r1, PH::NCH, PH::KC);
     __syncthreads();
     if (sh->abort_flag) ws.drain();
     return;
   }
-  Consumer<Geo> co{sh, slots, xs, red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
+  Consumer<Geo> co{sh, m.slots, m.xs, m.red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
   uint32_t xf[HT][2];
   if (p.norm_w != nullptr) {
-    uint2 nw[HT];
-#pragma unroll
-    for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
-    pdl_wait();
-    norm_rows<HT>(p.x, p.res_in, cta == 0 ? p.res_out : nullptr, nw, p.eps, p.B, xs, warp, lane);
-    consumer_sync();
-    load_local_x<HT, KTW, NCH>(xf, xs, co.wk, lane);
+    norm_to_fragments<HT, PH::KTW, PH::NCH>(xf, p.x, p.res_in, p.res_out, p.norm_w, p.eps, p.B, m.xs, warp, lane, co.wk, true);
   } else {
     // no norm in front: the rows' fragments come straight from global memory
     pdl_wait();
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int ch = 0; ch < NCH; ++ch)
+    for (int ch = 0; ch < PH::NCH; ++ch)
 #pragma unroll
-      for (int j = 0; j < KTW; ++j) {
-        const int k0 = ch * KC + (co.wk * KTW + j) * 16 + 4 * t;
+      for (int j = 0; j < PH::KTW; ++j) {
+        const int k0 = ch * PH::KC + (co.wk * PH::KTW + j) * 16 + 4 * t;
         uint2 v = make_uint2(0u, 0u);
         if (g < p.B) v = __ldcg(reinterpret_cast<const uint2*>(p.x + (size_t)g * H + k0));
-        xf[ch * KTW + j][0] = v.x;
-        xf[ch * KTW + j][1] = v.y;
+        xf[ch * PH::KTW + j][0] = v.x;
+        xf[ch * PH::KTW + j][1] = v.y;
       }
   }
   pdl_trigger();
-  for (int rg = r0; rg < r1; rg += RS) {
-    const int nr = min(RS, r1 - rg);
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    co.template row_group_local<KTW, NCH, 8>(c, xf);
-    float s = co.reduce(c, nullptr);
-    const int i = warp * 32 + lane;
-    const int row = i >> 3, n = i & 7;
-    if (i < 128 && row < nr && n < p.B) {
-      if (p.bias) s += __bfloat162float(p.bias[rg + row]);
-      p.y[(size_t)n * p.N + rg + row] = __float2bfloat16_rn(s);
-    }
-  }
+  co.template rows_local<PH::KTW, PH::NCH>(xf, r0, r1, p.B, [&](int row, int n, float s) {
+    if (p.bias) s += __bfloat162float(p.bias[row]);
+    p.y[(size_t)n * p.N + row] = __float2bfloat16_rn(s);
+  });
   __syncthreads();
 }
 
+// The attention half of a layer for a decode step of up to 8 requests:
+//   r = res_in + x; h = rmsnorm(r) * w; qkv = h Wqkv^T + b       (rows of Wqkv split over the CTAs)
+//   -- grid barrier --  attention_stage()  -- grid barrier --
+//   y = attn Wo^T                                                 (rows of Wo split over the CTAs)
+// The rows of Wo are on their way into shared memory while the attention runs.
+// Formulas: omniserve/model/qwen2_llm.py:75-113.
+template <int HT, int OT, int HD, class Geo>
+__device__ __forceinline__ void attn_half(Consumer<Geo>& co, GridSync& gs, const Carve<Geo>& m, const bf16* x,
+                                          const float* res_in, float* res_out, const bf16* norm_w, float eps,
+                                          const bf16* b_qkv, int NQKV, bf16* qkv, bf16* attn, bf16* y, int B,
+                                          const AttnTables& tables, int q0, int q1, int r0, int r1, bool first) {
+  constexpr int H = HT * NCW * 16;
+  typedef Pieces<HT, Geo> PH;
+  typedef Pieces<OT, Geo> PO;
+  {
+    uint32_t xf[HT][2];
+    norm_to_fragments<HT, PH::KTW, PH::NCH>(xf, x, res_in, res_out, norm_w, eps, B, m.xs, co.warp, co.lane, co.wk, first);
+    if (first) gs.begin();
+    co.template rows_local<PH::KTW, PH::NCH>(xf, q0, q1, B, [&](int row, int n, float s) {
+      if (b_qkv) s += __bfloat162float(b_qkv[row]);
+      qkv[(size_t)n * NQKV + row] = __float2bfloat16_rn(s);
+    });
+  }
+  gs.arrive(false);
+  attention_stage<HD>(tables, qkv, NQKV, attn, B, gs, m.aslots, m.sh);
+  gs.sync(true);
+  if (first) pdl_trigger();
+  co.act_begin();
+  co.template rows_streamed<PO::KTW, PO::NCH>(r0, r1, B, [&](int row, int n, float s) {
+    y[(size_t)n * H + row] = __float2bfloat16_rn(s);
+  });
+}
 
 struct AttnHalfParams {
   const bf16* x;          // [B, H] branch output of the part before
@@ -627,54 +766,28 @@ struct AttnHalfParams {
   int* err;
   float eps;
   int B, NQKV;
-  // the cache and the step's tables, as osb_attn_decode_stream takes them
-  bf16* k_cache;
-  bf16* v_cache;
-  const int* block_table;
-  const int* cu_q;
-  const int* seq_lens;
-  const int* decode_index;
-  int* counters;
-  float* part_o;
-  float* part_ml;
-  attn_stream::FusedRope rope;
-  float scale_log2;
-  int bt_stride, nh, nkv, log2ps, num_pages, window, nsplits;
+  AttnTables t;
 };
 
-// The attention half of a layer for a decode step of up to 8 requests:
-//   r = residual + x; h = rmsnorm(r) * w; qkv = h Wqkv^T + b     (rows of Wqkv split over the CTAs)
-//   -- grid barrier --
-//   rotary encoding, the new key and value into the cache, attention over the cache: one
-//   (request, kv head, split of the keys) per CTA and turn, as attn_decode_stream_kernel does it; the CTA
-//   that finishes a (request, kv head) last merges its splits
-//   -- grid barrier --
-//   y = attn Wo^T                                                 (rows of Wo split over the CTAs)
-// The rows of Wo are on their way into shared memory while the attention runs.
-// Formulas: omniserve/model/qwen2_llm.py:75-113.
+// the attention's q rows, per-warp (max, sum) and outputs use the activation tiles and the reduction buffers
+template <int HD, class Geo>
+__host__ __device__ constexpr bool attention_scratch_fits() {
+  return 16 * (HD + 8) * 2 + NCW * 16 * 2 * 4 + 16 * 2 * 4 + NCW * 16 * (HD + 8) * 4 <= Geo::AST * Geo::ASLOT + 2 * NCW * 128 * 4;
+}
+
 template <int HT, int OT, int HD, class Geo>
 __global__ void __launch_bounds__(NTHREADS_WIDE, 1) attn_decode_fused_kernel(const __grid_constant__ AttnHalfParams p) {
   constexpr int H = HT * NCW * 16, OD = OT * NCW * 16;
-  constexpr int RS = Geo::RS, MAX_KTW = Geo::MAX_KTW;
-  typedef Streamer<Geo::NST, Geo::SLOT, Geo::SROW, Geo::RS, true> WeightStream;
-  typedef Streamer<Geo::AST, Geo::ASLOT, Geo::SROW, Geo::RS, false> ActStream;
-  constexpr int KTW_H = largest_divisor_le(HT, MAX_KTW), NCH_H = HT / KTW_H, KC_H = KTW_H * NCW * 16;
-  constexpr int KTW_O = largest_divisor_le(OT, MAX_KTW), NCH_O = OT / KTW_O, KC_O = KTW_O * NCW * 16;
+  typedef Pieces<HT, Geo> PH;
+  typedef Pieces<OT, Geo> PO;
   static_assert(MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows share the activation tiles' memory");
-  // the attention's q rows, per-warp (max, sum) and outputs use the activation tiles and the reduction buffers
-  static_assert(16 * (HD + 8) * 2 + NCW * 16 * 2 * 4 + 16 * 2 * 4 + NCW * 16 * (HD + 8) * 4 <=
-                    Geo::AST * Geo::ASLOT + 2 * NCW * 128 * 4, "the attention's scratch does not fit");
-
+  static_assert(attention_scratch_fits<HD, Geo>(), "the attention's scratch does not fit");
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* slots = smem;
-  uint8_t* aslots = slots + Geo::NST * Geo::SLOT;
-  uint8_t* xs = aslots;
-  float* red = reinterpret_cast<float*>(aslots + Geo::AST * Geo::ASLOT);
-  Shared* sh = reinterpret_cast<Shared*>(red + 2 * NCW * 128);
+  const Carve<Geo> m(smem);
+  Shared* sh = m.sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = gridDim.x;
   init_shared<Geo>(sh);
-
   int q0, q1, r0, r1;
   cta_rows(p.NQKV, cta, G, q0, q1);
   cta_rows(H, cta, G, r0, r1);
@@ -682,121 +795,28 @@ __global__ void __launch_bounds__(NTHREADS_WIDE, 1) attn_decode_fused_kernel(con
   if (warp >= W_WARP) reg_give<PRODUCER_REGS>();   // all four warps of the last warp group, at one place
   if (warp > A_WARP) return;
   if (warp == A_WARP) {
-    ActStream as{sh, sh->afull, sh->aempty, aslots, 0u, 0ull, lane, p.err};
+    ActStreamOf<Geo> as{sh, sh->afull, sh->aempty, m.aslots, 0u, 0ull, lane, p.err};
     wait_or_abort(&sh->act_ready, 0u, sh, p.err, ERR_GRID_WAIT);
-    as.activation(p.attn, OD, p.B, (r1 - r0 + RS - 1) / RS, NCH_O, KC_O);
+    as.activation(p.attn, OD, p.B, (r1 - r0 + Geo::RS - 1) / Geo::RS, PO::NCH, PO::KC);
     __syncthreads();
     if (sh->abort_flag) as.drain();
     return;
   }
   if (warp == W_WARP) {
-    WeightStream ws{sh, sh->full, sh->empty, slots, 0u, policy_evict_first(), lane, p.err};
-    FTL(10);
-    ws.rows(p.w_qkv, H, q0, q1, NCH_H, KC_H);
-    FTL(11);
-    ws.rows(p.w_o, OD, r0, r1, NCH_O, KC_O);
-    FTL(12);
+    WeightStreamOf<Geo> ws{sh, sh->full, sh->empty, m.slots, 0u, policy_evict_first(), lane, p.err};
+    ws.rows(p.w_qkv, H, q0, q1, PH::NCH, PH::KC);
+    ws.rows(p.w_o, OD, r0, r1, PO::NCH, PO::KC);
     __syncthreads();
     if (sh->abort_flag) ws.drain();
     return;
   }
-
   reg_take<CONSUMER_REGS>();
-  Consumer<Geo> co{sh, slots, aslots, red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
-  unsigned long long target = 0;
-  uint2 nw[HT];
-#pragma unroll
-  for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
-  FTL(0);
-  // this CTA's first (request, kv head, split): its old keys and values depend on nothing in this step
-  const int grp = p.nh / p.nkv;
-  const int ny = p.nkv * ((grp + 7) >> 3);
-  const int units = p.B * ny * p.nsplits;
-  if (cta < units) {
-    const int rest = cta / p.nsplits;
-    attn_stream::attn_stream_prefetch<HD>(cta % p.nsplits, rest % ny, rest / ny, p.k_cache, p.v_cache, p.block_table,
-                                          p.bt_stride, p.seq_lens, p.nh, p.nkv, p.log2ps, p.num_pages, p.window,
-                                          p.nsplits);
-  }
-  pdl_wait();
-  FTL(1);
-  if (threadIdx.x == 0) {
-    unsigned long long v;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.bar) : "memory");
-    target = v - v % (unsigned long long)G + (unsigned long long)G;
-  }
-  norm_rows<HT>(p.x, p.res_in, cta == 0 ? p.res_out : nullptr, nw, p.eps, p.B, xs, warp, lane);
-  consumer_sync();
-  FTL(2);
-
-  // ---- qkv = h Wqkv^T + b
-  {
-    uint32_t xf[HT][2];
-    load_local_x<HT, KTW_H, NCH_H>(xf, xs, co.wk, lane);
-    for (int rg = q0; rg < q1; rg += RS) {
-      const int nr = min(RS, q1 - rg);
-      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      co.template row_group_local<KTW_H, NCH_H, 8>(c, xf);
-      float s = co.reduce(c, nullptr);
-      const int i = warp * 32 + lane;
-      const int row = i >> 3, n = i & 7;
-      if (i < 128 && row < nr && n < p.B) {
-        if (p.b_qkv) s += __bfloat162float(p.b_qkv[rg + row]);
-        p.qkv[(size_t)n * p.NQKV + rg + row] = __float2bfloat16_rn(s);
-      }
-    }
-  }
-  FTL(3);
-  consumer_sync();
-  if (threadIdx.x == 0) grid_arrive(p.bar, sh);
-  // the first unit looks up its pages and starts its first loads before it waits for the other CTAs' q, k, v
-  bool waited = false;
-  auto wait_qkv = [&] {
-    if (!waited) {
-      if (threadIdx.x == 0) grid_wait(p.bar, target, sh, p.err);
-      consumer_sync();
-      waited = true;
-      FTL(4);
-    }
-  };
-
-  // ---- attention: units (request, kv head, split), one per CTA and turn
-  {
-    for (int u = cta; u < units; u += G) {
-      const int split = u % p.nsplits, rest = u / p.nsplits;
-      const int by = rest % ny, s = rest / ny;
-      attn_stream::attn_stream_unit<HD, false, true>(
-          wait_qkv, split, by, s, ny, aslots, &sh->s_last, p.attn, p.part_o, p.part_ml, p.qkv, p.NQKV, p.k_cache, p.v_cache,
-          p.block_table, p.bt_stride, p.cu_q, p.seq_lens, p.decode_index, p.counters, p.nh, p.nkv, p.log2ps,
-          p.num_pages, p.scale_log2, p.window, 0, p.nsplits, p.rope);
-      wait_qkv();        // a unit that has nothing to do returns before it waits
-      consumer_sync();   // the scratch in shared memory is used again by the next unit and by the tiles after it
-    }
-    wait_qkv();
-  }
-  FTL(5);
-  publish_for_bulk_copies();
-  consumer_sync();
-  if (threadIdx.x == 0) grid_barrier(p.bar, target + (unsigned long long)G, sh, p.err);
-  consumer_sync();
-  FTL(6);
-  pdl_trigger();
-
-  // ---- y = attn Wo^T
-  co.act_begin();
-  for (int rg = r0; rg < r1; rg += RS) {
-    const int nr = min(RS, r1 - rg);
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    co.template row_group_streamed<KTW_O, NCH_O, 8>(c);
-    const float s = co.reduce(c, nullptr);
-    const int i = warp * 32 + lane;
-    const int row = i >> 3, n = i & 7;
-    if (i < 128 && row < nr && n < p.B) p.y[(size_t)n * H + rg + row] = __float2bfloat16_rn(s);
-  }
-  FTL(9);
+  Consumer<Geo> co{sh, m.slots, m.aslots, m.red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
+  GridSync gs{p.bar, 0ull, (unsigned)G, sh, p.err};
+  attn_half<HT, OT, HD, Geo>(co, gs, m, p.x, p.res_in, p.res_out, p.norm_w, p.eps, p.b_qkv, p.NQKV, p.qkv, p.attn, p.y, p.B,
+                             p.t, q0, q1, r0, r1, true);
   __syncthreads();
 }
-
 
 // One layer of the schedule for decode_layers_fused_kernel: device pointers and constants.
 struct LayerDesc {
@@ -818,43 +838,27 @@ struct LayersParams {
   unsigned long long* bar;
   int* err;
   int B, NQKV;
-  const int *cu_q, *seq_lens, *decode_index;
-  const int *block_table, *slot_map;   // of the one cache group that all these layers belong to
-  int* counters;
-  float *part_o, *part_ml;
-  const float *rope_cos, *rope_sin;
-  float scale_log2;
-  int bt_stride, rope_rot, nh, nkv, nsplits;
+  AttnTables t;         // k_cache, v_cache, window, num_pages, log2ps: taken from the layer's record instead
 };
 
 // A run of pre-norm layers (attention half, feed-forward half) for a decode step of up to 8 requests as ONE
-// kernel: the stages of attn_decode_fused_kernel and ffn_decode_fused_kernel layer after layer, five grid
-// barriers per layer, with the weights of all layers as one uninterrupted stream through shared memory.
-// The residual stream alternates between two buffers (CTA 0 writes the sum that every CTA computes), the
-// halves hand their output on in y.
+// kernel: attn_half and ffn_half layer after layer, five grid barriers per layer, with the weights of all
+// layers as one uninterrupted stream through shared memory. The residual stream alternates between two
+// buffers (CTA 0 writes the sum that every CTA computes), the halves hand their output on in y.
 template <int HT, int OT, int IT, int HD, class Geo>
 __global__ void __launch_bounds__(NTHREADS_WIDE, 1) decode_layers_fused_kernel(const __grid_constant__ LayersParams p) {
   constexpr int H = HT * NCW * 16, OD = OT * NCW * 16, I = IT * NCW * 16;
-  constexpr int RS = Geo::RS, PG = Geo::PG, MAX_KTW = Geo::MAX_KTW;
-  typedef Streamer<Geo::NST, Geo::SLOT, Geo::SROW, Geo::RS, true> WeightStream;
-  typedef Streamer<Geo::AST, Geo::ASLOT, Geo::SROW, Geo::RS, false> ActStream;
-  constexpr int KTW_H = largest_divisor_le(HT, MAX_KTW), NCH_H = HT / KTW_H, KC_H = KTW_H * NCW * 16;
-  constexpr int KTW_O = largest_divisor_le(OT, MAX_KTW), NCH_O = OT / KTW_O, KC_O = KTW_O * NCW * 16;
-  constexpr int KTW_I = largest_divisor_le(IT, MAX_KTW), NCH_I = IT / KTW_I, KC_I = KTW_I * NCW * 16;
+  typedef Pieces<HT, Geo> PH;
+  typedef Pieces<OT, Geo> PO;
+  typedef Pieces<IT, Geo> PI;
   static_assert(MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows share the activation tiles' memory");
-  static_assert(16 * (HD + 8) * 2 + NCW * 16 * 2 * 4 + 16 * 2 * 4 + NCW * 16 * (HD + 8) * 4 <=
-                    Geo::AST * Geo::ASLOT + 2 * NCW * 128 * 4, "the attention's scratch does not fit");
-
+  static_assert(attention_scratch_fits<HD, Geo>(), "the attention's scratch does not fit");
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* slots = smem;
-  uint8_t* aslots = slots + Geo::NST * Geo::SLOT;
-  uint8_t* xs = aslots;
-  float* red = reinterpret_cast<float*>(aslots + Geo::AST * Geo::ASLOT);
-  Shared* sh = reinterpret_cast<Shared*>(red + 2 * NCW * 128);
+  const Carve<Geo> m(smem);
+  Shared* sh = m.sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = gridDim.x;
   init_shared<Geo>(sh);
-
   int q0, q1, r0, r1, p0, p1;
   cta_rows(p.NQKV, cta, G, q0, q1);
   cta_rows(H, cta, G, r0, r1);
@@ -863,26 +867,26 @@ __global__ void __launch_bounds__(NTHREADS_WIDE, 1) decode_layers_fused_kernel(c
   if (warp >= W_WARP) reg_give<PRODUCER_REGS>();   // all four warps of the last warp group, at one place
   if (warp > A_WARP) return;
   if (warp == A_WARP) {
-    ActStream as{sh, sh->afull, sh->aempty, aslots, 0u, 0ull, lane, p.err};
-    const int groups = (r1 - r0 + RS - 1) / RS;
+    ActStreamOf<Geo> as{sh, sh->afull, sh->aempty, m.aslots, 0u, 0ull, lane, p.err};
+    const int groups = (r1 - r0 + Geo::RS - 1) / Geo::RS;
     for (int l = 0; l < p.n_layers; ++l) {
       wait_or_abort(&sh->act_ready, 0u, sh, p.err, ERR_GRID_WAIT);
-      as.activation(p.attn, OD, p.B, groups, NCH_O, KC_O);
+      as.activation(p.attn, OD, p.B, groups, PO::NCH, PO::KC);
       wait_or_abort(&sh->act_ready, 1u, sh, p.err, ERR_GRID_WAIT);
-      as.activation(p.act, I, p.B, groups, NCH_I, KC_I);
+      as.activation(p.act, I, p.B, groups, PI::NCH, PI::KC);
     }
     __syncthreads();
     if (sh->abort_flag) as.drain();
     return;
   }
   if (warp == W_WARP) {
-    WeightStream ws{sh, sh->full, sh->empty, slots, 0u, policy_evict_first(), lane, p.err};
+    WeightStreamOf<Geo> ws{sh, sh->full, sh->empty, m.slots, 0u, policy_evict_first(), lane, p.err};
     for (int l = 0; l < p.n_layers; ++l) {
       const LayerDesc& L = p.layers[l];
-      ws.rows(L.w_qkv, H, q0, q1, NCH_H, KC_H);
-      ws.rows(L.w_o, OD, r0, r1, NCH_O, KC_O);
-      ws.pairs(L.w_gate_up, H, I, p0, p1, NCH_H, KC_H);
-      ws.rows(L.w_down, I, r0, r1, NCH_I, KC_I);
+      ws.rows(L.w_qkv, H, q0, q1, PH::NCH, PH::KC);
+      ws.rows(L.w_o, OD, r0, r1, PO::NCH, PO::KC);
+      ws.pairs(L.w_gate_up, H, I, p0, p1, PH::NCH, PH::KC);
+      ws.rows(L.w_down, I, r0, r1, PI::NCH, PI::KC);
     }
     __syncthreads();
     if (sh->abort_flag) ws.drain();
@@ -890,163 +894,25 @@ __global__ void __launch_bounds__(NTHREADS_WIDE, 1) decode_layers_fused_kernel(c
   }
 
   reg_take<CONSUMER_REGS>();
-  Consumer<Geo> co{sh, slots, aslots, red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
-  unsigned long long target = 0;
-  const int grp = p.nh / p.nkv;
-  const int ny = p.nkv * ((grp + 7) >> 3);
-  const int units = p.B * ny * p.nsplits;
+  Consumer<Geo> co{sh, m.slots, m.aslots, m.red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
+  GridSync gs{p.bar, 0ull, (unsigned)G, sh, p.err};
   const bf16* x_cur = p.x;
   const float* r_cur = p.res_in;
-  int turn = 0;   // norms so far: the next sum goes to res_a when even
-
   for (int l = 0; l < p.n_layers; ++l) {
     const LayerDesc& L = p.layers[l];
-    if (l == 1) FTL(0);
-    // ================= the attention half
-    {
-      uint2 nw[HT];
-#pragma unroll
-      for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(L.norm_attn + (i * 32 + lane) * 4);
-      if (l == 0) {
-        pdl_wait();
-        if (threadIdx.x == 0) {
-          unsigned long long v;
-          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.bar) : "memory");
-          target = v - v % (unsigned long long)G;
-        }
-      }
-      float* r_next = (turn & 1) ? p.res_b : p.res_a;
-      norm_rows<HT>(x_cur, r_cur, cta == 0 ? r_next : nullptr, nw, L.eps_attn, p.B, xs, warp, lane);
-      r_cur = r_next;
-      ++turn;
-      consumer_sync();
-      if (l == 1) FTL(1);
-      uint32_t xf[HT][2];
-      load_local_x<HT, KTW_H, NCH_H>(xf, xs, co.wk, lane);
-      for (int rg = q0; rg < q1; rg += RS) {
-        const int nr = min(RS, q1 - rg);
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        co.template row_group_local<KTW_H, NCH_H, 8>(c, xf);
-        float s = co.reduce(c, nullptr);
-        const int i = warp * 32 + lane;
-        const int row = i >> 3, n = i & 7;
-        if (i < 128 && row < nr && n < p.B) {
-          if (L.b_qkv) s += __bfloat162float(L.b_qkv[rg + row]);
-          p.qkv[(size_t)n * p.NQKV + rg + row] = __float2bfloat16_rn(s);
-        }
-      }
-    }
-    if (l == 1) FTL(2);
-    consumer_sync();
-    if (threadIdx.x == 0) {
-      grid_arrive(p.bar, sh);
-      target += (unsigned long long)G;
-    }
-    {
-      bool waited = false;
-      auto wait_qkv = [&] {
-        if (!waited) {
-          if (threadIdx.x == 0) grid_wait(p.bar, target, sh, p.err);
-          consumer_sync();
-          waited = true;
-          if (l == 1) FTL(3);
-        }
-      };
-      attn_stream::FusedRope fr{p.rope_cos, p.rope_sin, p.slot_map, p.rope_rot};
-      for (int u = cta; u < units; u += G) {
-        const int split = u % p.nsplits, rest = u / p.nsplits;
-        attn_stream::attn_stream_unit<HD, false, true>(
-            wait_qkv, split, rest % ny, rest / ny, ny, aslots, &sh->s_last, p.attn, p.part_o, p.part_ml, p.qkv, p.NQKV,
-            L.k_cache, L.v_cache, p.block_table, p.bt_stride, p.cu_q, p.seq_lens, p.decode_index, p.counters, p.nh, p.nkv,
-            L.log2ps, L.num_pages, p.scale_log2, L.window, 0, p.nsplits, fr);
-        wait_qkv();
-        consumer_sync();
-      }
-      wait_qkv();
-    }
-    if (l == 1) FTL(4);
-    publish_for_bulk_copies();
-    consumer_sync();
-    if (threadIdx.x == 0) {
-      target += (unsigned long long)G;
-      grid_barrier(p.bar, target, sh, p.err);
-    }
-    consumer_sync();
-    if (l == 1) FTL(5);
-    if (l == 0) pdl_trigger();
-    co.act_begin();
-    for (int rg = r0; rg < r1; rg += RS) {
-      const int nr = min(RS, r1 - rg);
-      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      co.template row_group_streamed<KTW_O, NCH_O, 8>(c);
-      const float s = co.reduce(c, nullptr);
-      const int i = warp * 32 + lane;
-      const int row = i >> 3, n = i & 7;
-      if (i < 128 && row < nr && n < p.B) p.y[(size_t)n * H + rg + row] = __float2bfloat16_rn(s);
-    }
-    if (l == 1) FTL(6);
-    consumer_sync();
-    if (threadIdx.x == 0) {
-      target += (unsigned long long)G;
-      grid_barrier(p.bar, target, sh, p.err);
-    }
-    consumer_sync();
-    if (l == 1) FTL(7);
-
-    // ================= the feed-forward half
-    {
-      uint2 nw[HT];
-#pragma unroll
-      for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(L.norm_ffn + (i * 32 + lane) * 4);
-      float* r_next = (turn & 1) ? p.res_b : p.res_a;
-      norm_rows<HT>(p.y, r_cur, cta == 0 ? r_next : nullptr, nw, L.eps_ffn, p.B, xs, warp, lane);
-      r_cur = r_next;
-      ++turn;
-      consumer_sync();
-      uint32_t xf[HT][2];
-      load_local_x<HT, KTW_H, NCH_H>(xf, xs, co.wk, lane);
-      for (int pg = p0; pg < p1; pg += PG) {
-        const int np = min(PG, p1 - pg);
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        co.template row_group_local<KTW_H, NCH_H, PG>(c, xf);
-        float up;
-        const float gate = co.reduce(c, &up);
-        const int i = warp * 32 + lane;
-        const int pair = i >> 3, n = i & 7;
-        if (i < 64 && pair < np && n < p.B)
-          p.act[(size_t)n * I + pg + pair] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
-      }
-    }
-    if (l == 1) FTL(8);
-    publish_for_bulk_copies();
-    consumer_sync();
-    if (threadIdx.x == 0) {
-      target += (unsigned long long)G;
-      grid_barrier(p.bar, target, sh, p.err);
-    }
-    consumer_sync();
-    if (l == 1) FTL(9);
-    co.act_begin();
-    for (int rg = r0; rg < r1; rg += RS) {
-      const int nr = min(RS, r1 - rg);
-      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      co.template row_group_streamed<KTW_I, NCH_I, 8>(c);
-      const float s = co.reduce(c, nullptr);
-      const int i = warp * 32 + lane;
-      const int row = i >> 3, n = i & 7;
-      if (i < 128 && row < nr && n < p.B) p.y[(size_t)n * H + rg + row] = __float2bfloat16_rn(s);
-    }
-    if (l == 1) FTL(10);
+    AttnTables t = p.t;
+    t.k_cache = L.k_cache;
+    t.v_cache = L.v_cache;
+    t.window = L.window;
+    t.num_pages = L.num_pages;
+    t.log2ps = L.log2ps;
+    attn_half<HT, OT, HD, Geo>(co, gs, m, x_cur, r_cur, p.res_a, L.norm_attn, L.eps_attn, L.b_qkv, p.NQKV, p.qkv, p.attn, p.y,
+                               p.B, t, q0, q1, r0, r1, l == 0);
+    gs.sync(false);    // the norm that follows reads y and the residual stream that CTA 0 wrote
+    ffn_half<HT, IT, Geo>(co, gs, m.xs, p.y, p.res_a, p.res_b, L.norm_ffn, L.eps_ffn, p.act, p.y, p.B, p0, p1, r0, r1, false);
     x_cur = p.y;
-    if (l + 1 < p.n_layers) {   // the next layer's norm reads y and the residual stream that CTA 0 wrote
-      consumer_sync();
-      if (threadIdx.x == 0) {
-        target += (unsigned long long)G;
-        grid_barrier(p.bar, target, sh, p.err);
-      }
-      consumer_sync();
-      if (l == 1) FTL(11);
-    }
+    r_cur = p.res_b;
+    if (l + 1 < p.n_layers) gs.sync(false);
   }
   __syncthreads();
 }
@@ -1194,12 +1060,12 @@ OSB_API int osb_attn_decode_fused(void* y, float* res_out, const void* x, const 
   p.x = (const bf16*)x; p.res_in = res_in; p.res_out = res_out; p.norm_w = (const bf16*)norm_w;
   p.w_qkv = (const bf16*)w_qkv; p.b_qkv = (const bf16*)b_qkv; p.w_o = (const bf16*)w_o; p.qkv = (bf16*)qkv;
   p.attn = (bf16*)attn; p.y = (bf16*)y; p.bar = bar; p.err = err; p.eps = eps; p.B = B; p.NQKV = NQKV;
-  p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache; p.block_table = block_table; p.cu_q = cu_q;
-  p.seq_lens = seq_lens; p.decode_index = decode_index; p.counters = counters; p.part_o = part_o; p.part_ml = part_ml;
-  p.rope.cos_t = rope_cos; p.rope.sin_t = rope_sin; p.rope.slot_map = rope_slot_map; p.rope.rot = rope_rot;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.bt_stride = bt_stride; p.nh = nh; p.nkv = nkv; p.log2ps = log2ps; p.num_pages = num_pages;
-  p.window = window; p.nsplits = nsplits;
+  p.t.k_cache = (bf16*)k_cache; p.t.v_cache = (bf16*)v_cache; p.t.block_table = block_table; p.t.cu_q = cu_q;
+  p.t.seq_lens = seq_lens; p.t.decode_index = decode_index; p.t.counters = counters; p.t.part_o = part_o; p.t.part_ml = part_ml;
+  p.t.rope.cos_t = rope_cos; p.t.rope.sin_t = rope_sin; p.t.rope.slot_map = rope_slot_map; p.t.rope.rot = rope_rot;
+  p.t.scale_log2 = scale * 1.4426950408889634f;
+  p.t.bt_stride = bt_stride; p.t.nh = nh; p.t.nkv = nkv; p.t.log2ps = log2ps; p.t.num_pages = num_pages;
+  p.t.window = window; p.t.nsplits = nsplits;
   typedef Geometry<16, 12, 3, 3> GeoB;
   const int n_sm = sm_count();
   if (H == 1536) return launch_fused<GeoB>(attn_decode_fused_kernel<12, 12, 128, GeoB>, p, n_sm, true, stream, NTHREADS_WIDE);
@@ -1241,10 +1107,12 @@ OSB_API int osb_decode_layers_fused(const void* layers, int n_layers, void* y, f
   LayersParams p;
   p.layers = (const LayerDesc*)layers; p.n_layers = n_layers; p.x = (const bf16*)x; p.res_in = res_in; p.res_a = res_a;
   p.res_b = res_b; p.y = (bf16*)y; p.qkv = (bf16*)qkv; p.attn = (bf16*)attn; p.act = (bf16*)act; p.bar = bar; p.err = err;
-  p.B = B; p.NQKV = NQKV; p.cu_q = cu_q; p.seq_lens = seq_lens; p.decode_index = decode_index; p.counters = counters;
-  p.block_table = block_table; p.bt_stride = bt_stride; p.slot_map = slot_map;
-  p.part_o = part_o; p.part_ml = part_ml; p.rope_cos = rope_cos; p.rope_sin = rope_sin;
-  p.scale_log2 = scale * 1.4426950408889634f; p.rope_rot = rope_rot; p.nh = nh; p.nkv = nkv; p.nsplits = nsplits;
+  p.B = B; p.NQKV = NQKV;
+  p.t.k_cache = nullptr; p.t.v_cache = nullptr; p.t.window = 0; p.t.num_pages = 0; p.t.log2ps = 0;   // per layer
+  p.t.cu_q = cu_q; p.t.seq_lens = seq_lens; p.t.decode_index = decode_index; p.t.counters = counters;
+  p.t.block_table = block_table; p.t.bt_stride = bt_stride; p.t.part_o = part_o; p.t.part_ml = part_ml;
+  p.t.rope.cos_t = rope_cos; p.t.rope.sin_t = rope_sin; p.t.rope.slot_map = slot_map; p.t.rope.rot = rope_rot;
+  p.t.scale_log2 = scale * 1.4426950408889634f; p.t.nh = nh; p.t.nkv = nkv; p.t.nsplits = nsplits;
   typedef Geometry<16, 12, 3, 3> GeoB;
   const int n_sm = sm_count();
   if (H == 1536) return launch_fused<GeoB>(decode_layers_fused_kernel<12, 12, 70, 128, GeoB>, p, n_sm, true, stream, NTHREADS_WIDE);
