@@ -42,9 +42,11 @@ constexpr int NTHREADS_WIDE = NCT + 128;
 constexpr int CONSUMER_REGS = 224, PRODUCER_REGS = 56;   // 2 * 224 + 56 = 3 * 168 per scheduler
 // How the shared memory is cut: weight tiles of RS rows by at most MAX_KTW * 128 elements along K, NST
 // of them in flight; activation tiles of MAX_B rows by the same length, AST in flight.
-template <int RS_, int MAX_KTW_, int NST_, int AST_>
+// NT: MMA column tiles of 8 batch rows each (kernels for up to 8 * NT rows; the reduction buffers grow with it).
+template <int RS_, int MAX_KTW_, int NST_, int AST_, int NT_ = 1>
 struct Geometry {
-  static constexpr int RS = RS_, PG = RS_ / 2, MAX_KTW = MAX_KTW_, NST = NST_, AST = AST_;
+  static constexpr int RS = RS_, PG = RS_ / 2, MAX_KTW = MAX_KTW_, NST = NST_, AST = AST_, NT = NT_;
+  static constexpr int RED_FLOATS = 2 * NCW * 128 * NT;   // two buffers of every warp's accumulators
   static constexpr int MAX_KC = MAX_KTW * NCW * 16;
   // row stride in a tile; = 32 mod 128, so the 8-byte fragment loads of four rows fall on different banks
   static constexpr int SROW = MAX_KC * 2 + 32;
@@ -313,6 +315,65 @@ struct Consumer {
     return s;
   }
 
+  // ---- the same for NT column tiles of 8 batch rows (plain rows only): one load of the weights' fragments
+  // feeds NT MMAs, which are as many independent chains
+  template <int KTW, int XOFF, int NT, int NX>
+  __device__ __forceinline__ void mma_tile_nt(float (&c)[NT][4], const uint32_t (&xf)[NT][NX][2]) {
+    const uint32_t slot = idx % NSTAGE, round = idx / NSTAGE;
+    wait_or_abort(&sh->full[slot], round & 1u, sh, err, ERR_TILE_WAIT);
+    const int g = lane >> 2, t = lane & 3;
+    const uint8_t* base = slots + (size_t)slot * SLOT_BYTES + (size_t)(wk * KTW * 16 + 4 * t) * 2;
+    const uint8_t* lo_p = base + (size_t)g * SROW;
+    const uint8_t* hi_p = base + (size_t)min(8 + g, RS - 1) * SROW;
+#pragma unroll
+    for (int j = 0; j < KTW; ++j) {
+      const uint2 lo = lds64(lo_p + j * 32), hi = lds64(hi_p + j * 32);
+      const unsigned a[4] = {lo.x, hi.x, lo.y, hi.y};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(c[nt], a, xf[nt][XOFF + j][0], xf[nt][XOFF + j][1]);
+    }
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&sh->empty[slot]);
+    ++idx;
+  }
+  template <int KTW, int NCH, int NT, int NX, int CH = 0>
+  __device__ __forceinline__ void row_group_local_nt(float (&c)[NT][4], const uint32_t (&xf)[NT][NX][2]) {
+    mma_tile_nt<KTW, CH * KTW>(c, xf);
+    if constexpr (CH + 1 < NCH) row_group_local_nt<KTW, NCH, NT, NX, CH + 1>(c, xf);
+  }
+  // rows [r0, r1): epi(row, n, sum) for batch rows n < B <= 8 * NT
+  template <int KTW, int NCH, int NT, int NX, class Epi>
+  __device__ __forceinline__ void rows_local_nt(const uint32_t (&xf)[NT][NX][2], int r0, int r1, int B, Epi epi) {
+    for (int rg = r0; rg < r1; rg += RS) {
+      const int nr = min(RS, r1 - rg);
+      float c[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
+      row_group_local_nt<KTW, NCH>(c, xf);
+      float* buf = red + (nred & 1u) * (NCW * 128 * NT);
+      const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        *reinterpret_cast<float2*>(buf + (nt * NCW + warp) * 128 + g * 8 + 2 * t) = make_float2(c[nt][0], c[nt][1]);
+        *reinterpret_cast<float2*>(buf + (nt * NCW + warp) * 128 + 64 + g * 8 + 2 * t) = make_float2(c[nt][2], c[nt][3]);
+      }
+      consumer_sync();
+      ++nred;
+      const int i = warp * 32 + lane;
+      if (i < 128) {
+        const int row = i >> 3;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float s = 0.0f;
+#pragma unroll
+          for (int w = 0; w < NCW; ++w) s += buf[(nt * NCW + w) * 128 + i];
+          const int n = nt * 8 + (i & 7);
+          if (row < nr && n < B) epi(rg + row, n, s);
+        }
+      }
+    }
+  }
+
   // ---- whole stages. epi(row, n, sum) is called by the thread that holds output (row, batch row n < B).
   // rows [r0, r1) of a projection whose activation's fragments are in registers
   template <int KTW, int NCH, int NX, class Epi>
@@ -568,7 +629,7 @@ struct Carve {
     aslots = slots + Geo::NST * Geo::SLOT;
     xs = aslots;
     red = reinterpret_cast<float*>(aslots + Geo::AST * Geo::ASLOT);
-    sh = reinterpret_cast<Shared*>(red + 2 * NCW * 128);
+    sh = reinterpret_cast<Shared*>(red + Geo::RED_FLOATS);
   }
 };
 
@@ -672,9 +733,9 @@ struct NormLinearParams {
 // its rows of W are already on their way; no CTA waits for another. Without norm_w: y = x W^T + bias.
 template <int HT, class Geo>
 __global__ void __launch_bounds__(NTHREADS, 1) norm_linear_decode_kernel(const __grid_constant__ NormLinearParams p) {
-  constexpr int H = HT * NCW * 16;
+  constexpr int H = HT * NCW * 16, NT = Geo::NT, XS = H * 2 + 32;
   typedef Pieces<HT, Geo> PH;
-  static_assert(MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows use the activation tiles' memory");
+  static_assert(NT * MAX_B * XS <= Geo::AST * Geo::ASLOT, "the normalised rows use the activation tiles' memory");
   extern __shared__ __align__(128) uint8_t smem[];
   const Carve<Geo> m(smem);
   Shared* sh = m.sh;
@@ -692,29 +753,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) norm_linear_decode_kernel(const _
     return;
   }
   Consumer<Geo> co{sh, m.slots, m.xs, m.red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
-  uint32_t xf[HT][2];
+  uint32_t xf[NT][HT][2];   // batch rows 8 nt .. 8 nt + 7
   if (p.norm_w != nullptr) {
-    norm_to_fragments<HT, PH::KTW, PH::NCH>(xf, p.x, p.res_in, p.res_out, p.norm_w, p.eps, p.B, m.xs, warp, lane, co.wk, true);
+    uint2 nw[HT];
+#pragma unroll
+    for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
+    pdl_wait();
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+      norm_rows<HT>(p.x + (size_t)nt * 8 * H, p.res_in ? p.res_in + (size_t)nt * 8 * H : nullptr,
+                    cta == 0 ? p.res_out + (size_t)nt * 8 * H : nullptr, nw, p.eps, p.B - nt * 8, m.xs + (size_t)nt * 8 * XS,
+                    warp, lane);
+    consumer_sync();
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) load_local_x<HT, PH::KTW, PH::NCH>(xf[nt], m.xs + (size_t)nt * 8 * XS, co.wk, lane);
   } else {
     // no norm in front: the rows' fragments come straight from global memory
     pdl_wait();
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int ch = 0; ch < PH::NCH; ++ch)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int j = 0; j < PH::KTW; ++j) {
-        const int k0 = ch * PH::KC + (co.wk * PH::KTW + j) * 16 + 4 * t;
-        uint2 v = make_uint2(0u, 0u);
-        if (g < p.B) v = __ldcg(reinterpret_cast<const uint2*>(p.x + (size_t)g * H + k0));
-        xf[ch * PH::KTW + j][0] = v.x;
-        xf[ch * PH::KTW + j][1] = v.y;
-      }
+      for (int ch = 0; ch < PH::NCH; ++ch)
+#pragma unroll
+        for (int j = 0; j < PH::KTW; ++j) {
+          const int k0 = ch * PH::KC + (co.wk * PH::KTW + j) * 16 + 4 * t;
+          uint2 v = make_uint2(0u, 0u);
+          if (nt * 8 + g < p.B) v = __ldcg(reinterpret_cast<const uint2*>(p.x + (size_t)(nt * 8 + g) * H + k0));
+          xf[nt][ch * PH::KTW + j][0] = v.x;
+          xf[nt][ch * PH::KTW + j][1] = v.y;
+        }
   }
   pdl_trigger();
-  co.template rows_local<PH::KTW, PH::NCH>(xf, r0, r1, p.B, [&](int row, int n, float s) {
+  auto store = [&](int row, int n, float s) {
     if (p.bias) s += __bfloat162float(p.bias[row]);
     p.y[(size_t)n * p.N + row] = __float2bfloat16_rn(s);
-  });
+  };
+  if constexpr (NT == 1) co.template rows_local<PH::KTW, PH::NCH>(xf[0], r0, r1, p.B, store);
+  else co.template rows_local_nt<PH::KTW, PH::NCH>(xf, r0, r1, p.B, store);
   __syncthreads();
 }
 
@@ -772,7 +848,7 @@ struct AttnHalfParams {
 // the attention's q rows, per-warp (max, sum) and outputs use the activation tiles and the reduction buffers
 template <int HD, class Geo>
 __host__ __device__ constexpr bool attention_scratch_fits() {
-  return 16 * (HD + 8) * 2 + NCW * 16 * 2 * 4 + 16 * 2 * 4 + NCW * 16 * (HD + 8) * 4 <= Geo::AST * Geo::ASLOT + 2 * NCW * 128 * 4;
+  return 16 * (HD + 8) * 2 + NCW * 16 * 2 * 4 + 16 * 2 * 4 + NCW * 16 * (HD + 8) * 4 <= Geo::AST * Geo::ASLOT + Geo::RED_FLOATS * 4;
 }
 
 template <int HT, int OT, int HD, class Geo>
@@ -928,7 +1004,7 @@ int& fused_cooperative() {
 
 template <class Geo>
 constexpr size_t fused_smem_bytes() {
-  return (size_t)Geo::NST * Geo::SLOT + (size_t)Geo::AST * Geo::ASLOT + 2 * NCW * 128 * sizeof(float) + sizeof(Shared);
+  return (size_t)Geo::NST * Geo::SLOT + (size_t)Geo::AST * Geo::ASLOT + Geo::RED_FLOATS * sizeof(float) + sizeof(Shared);
 }
 
 // One CTA per SM. `cooperative`: the CTAs wait for one another, so the launch must fail rather than start
@@ -1122,13 +1198,13 @@ OSB_API int osb_decode_layers_fused(const void* layers, int n_layers, void* y, f
 
 OSB_API int osb_norm_linear_decode_supported(int H) { return H == 1536 || H == 256 || H == 384 || H == 2048; }
 
-// y [B,N] = (rmsnorm(res_in + x) * norm_w) W^T + bias; res_out = res_in + x (fp32). B <= 8, everything bf16
+// y [B,N] = (rmsnorm(res_in + x) * norm_w) W^T + bias; res_out = res_in + x (fp32). B <= 16, everything bf16
 // but the residual stream. Without norm_w (then no res_in, no res_out): y = x W^T + bias.
 OSB_API int osb_norm_linear_decode(void* y, float* res_out, const void* x, const float* res_in, const void* norm_w,
                                    float eps, const void* w, const void* bias, int* err, int B, int N, int H,
                                    cudaStream_t stream) {
   if (B <= 0 || N <= 0) return OSB_OK;
-  if (B > MAX_B || !osb_norm_linear_decode_supported(H)) return OSB_ERR_UNSUPPORTED;
+  if (B > 2 * MAX_B || !osb_norm_linear_decode_supported(H)) return OSB_ERR_UNSUPPORTED;
   if ((((uintptr_t)res_out | (uintptr_t)x | (uintptr_t)res_in | (uintptr_t)norm_w | (uintptr_t)w) & 15) != 0)
     return OSB_ERR_BAD_SHAPE;
   if (norm_w == nullptr && (res_in != nullptr || res_out != nullptr)) return OSB_ERR_BAD_SHAPE;
@@ -1140,6 +1216,15 @@ OSB_API int osb_norm_linear_decode(void* y, float* res_out, const void* x, const
   typedef Geometry<12, 7, 4, 3> GeoT;
   typedef Geometry<16, 8, 3, 2> GeoU;
   const int n_sm = sm_count();
+  if (B > MAX_B) {   // 9 to 16 rows: two column tiles
+    typedef Geometry<16, 12, 2, 2, 2> GeoS2;
+    typedef Geometry<12, 7, 4, 3, 2> GeoT2;
+    typedef Geometry<16, 8, 2, 4, 2> GeoU2;
+    if (H == 1536) return launch_fused<GeoS2>(norm_linear_decode_kernel<12, GeoS2>, p, n_sm, false, stream);
+    if (H == 256) return launch_fused<GeoS2>(norm_linear_decode_kernel<2, GeoS2>, p, n_sm, false, stream);
+    if (H == 384) return launch_fused<GeoT2>(norm_linear_decode_kernel<3, GeoT2>, p, n_sm, false, stream);
+    return launch_fused<GeoU2>(norm_linear_decode_kernel<16, GeoU2>, p, n_sm, false, stream);
+  }
   if (H == 1536) return launch_fused<GeoS>(norm_linear_decode_kernel<12, GeoS>, p, n_sm, false, stream);
   if (H == 256) return launch_fused<GeoS>(norm_linear_decode_kernel<2, GeoS>, p, n_sm, false, stream);
   if (H == 384) return launch_fused<GeoT>(norm_linear_decode_kernel<3, GeoT>, p, n_sm, false, stream);

@@ -197,7 +197,7 @@ class CudaKernels(PersistentDecodeOps):
         M, K = x.shape
         N = w.shape[0]
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-            if (self.stream_linear_decode and out_dtype == torch.bfloat16 and 0 < M <= self.FUSED_MAX_ROWS
+            if (self.stream_linear_decode and out_dtype == torch.bfloat16 and 0 < M <= self.STREAM_LINEAR_MAX_ROWS
                     and N <= self.STREAM_LINEAR_MAX_N and (bias is None or bias.dtype == torch.bfloat16)
                     and bool(self.lib.osb_norm_linear_decode_supported(K))):
                 # a few rows and a matrix that one wave of CTAs covers: the weight-streaming kernel without its norm

@@ -15,6 +15,7 @@ from ._common import _check, _cuda_contig, _p
 
 class PersistentDecodeOps:
     FUSED_MAX_ROWS = 8
+    STREAM_LINEAR_MAX_ROWS = 16    # the projection kernel (with or without its norm) has a form with two column tiles
     STREAM_LINEAR_MAX_N = 4096     # rows of W up to which the streaming projection without norm is used
     FUSED_MAX_SPLITS = 16
 
@@ -35,21 +36,21 @@ class PersistentDecodeOps:
     def can_norm_linear_decode(self, x: torch.Tensor, norm_weight: torch.Tensor, w: torch.Tensor,
                                bias: Optional[torch.Tensor]) -> bool:
         """Whether ``norm_linear_decode`` takes these operands."""
-        return (self.fuse_norm_linear_decode and x.dim() == 2 and 0 < x.shape[0] <= self.FUSED_MAX_ROWS
+        return (self.fuse_norm_linear_decode and x.dim() == 2 and 0 < x.shape[0] <= self.STREAM_LINEAR_MAX_ROWS
                 and x.dtype == norm_weight.dtype == w.dtype == torch.bfloat16
                 and (bias is None or bias.dtype == torch.bfloat16)
                 and bool(self.lib.osb_norm_linear_decode_supported(x.shape[1])))
 
     def norm_linear_decode(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                            w: torch.Tensor, bias: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(norm(residual + x) * norm_weight) @ w^T (+ bias) for up to 8 rows as one kernel that has its rows of
+        """(norm(residual + x) * norm_weight) @ w^T (+ bias) for up to 16 rows as one kernel that has its rows of
         w on their way while it normalises; returns (y, the new fp32 residual stream, a new tensor)."""
         for name, t in (("x", x), ("norm_weight", norm_weight), ("w", w)):
             _cuda_contig(name, t, torch.bfloat16)
         B, H = x.shape
         N = w.shape[0]
         _check(self.can_norm_linear_decode(x, norm_weight, w, bias) and w.shape == (N, H) and norm_weight.shape == (H,),
-               "norm_linear_decode: x [B<=8,H] bf16, w [N,H] bf16 at a width it is built for")
+               "norm_linear_decode: x [B<=16,H] bf16, w [N,H] bf16 at a width it is built for")
         if residual is not None:
             _cuda_contig("residual", residual, torch.float32)
             _check(residual.shape == x.shape, "norm_linear_decode: residual [B,H]")

@@ -107,7 +107,8 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M,N,K_", [(1, 200, 96), (8, 1536, 1536), (64, 1000, 256), (200, 264, 1536), (3, 17920, 64)])
+@pytest.mark.parametrize("M,N,K_", [(1, 200, 96), (8, 1536, 1536), (13, 1536, 1536), (16, 300, 256), (64, 1000, 256), (200, 264, 1536),
+                                    (3, 17920, 64)])
 def test_linear_bf16_and_f32(dtype, M, N, K_):
     x, w, b = rnd(M, K_, dtype=dtype), rnd(N, K_, dtype=dtype, seed=1, scale=0.05), rnd(N, dtype=dtype, seed=2)
     for bias in (None, b):
@@ -191,7 +192,7 @@ def test_skinny_gemm_with_the_norm_inside(M, N, K_, with_residual):
 
 
 @pytest.mark.parametrize("H,N", [(256, 100), (384, 1000), (2048, 300), (1536, 2048), (1536, 17)])
-@pytest.mark.parametrize("B", [1, 5, 8])
+@pytest.mark.parametrize("B", [1, 5, 8, 9, 13, 16])
 def test_norm_linear_decode(H, N, B):
     """The projection of a few rows that normalises them itself while its weights stream in: same
     statements as for the skinny GEMM with the norm inside (residual sum bit for bit; one bf16 step of
