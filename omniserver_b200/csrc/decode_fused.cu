@@ -50,7 +50,7 @@ struct Geometry {
   static constexpr int MAX_KC = MAX_KTW * NCW * 16;
   // row stride in a tile; = 32 mod 128, so the 8-byte fragment loads of four rows fall on different banks
   static constexpr int SROW = MAX_KC * 2 + 32;
-  static constexpr int SLOT = RS * SROW, ASLOT = 8 * SROW;
+  static constexpr int SLOT = RS * SROW, ASLOT = 8 * NT * SROW;   // an activation tile holds all batch rows
   static constexpr int MAX_ST = 8;   // bound of NST and AST: the barrier arrays
   static_assert(NST <= MAX_ST && AST <= MAX_ST && (MAX_KC * 2) % 128 == 0, "");
 };
@@ -315,16 +315,16 @@ struct Consumer {
     return s;
   }
 
-  // ---- the same for NT column tiles of 8 batch rows (plain rows only): one load of the weights' fragments
-  // feeds NT MMAs, which are as many independent chains
-  template <int KTW, int XOFF, int NT, int NX>
+  // ---- the same for NT column tiles of 8 batch rows: one load of the weights' fragments feeds NT MMAs, which
+  // are as many independent chains
+  template <int KTW, int HI, int XOFF, int NT, int NX>
   __device__ __forceinline__ void mma_tile_nt(float (&c)[NT][4], const uint32_t (&xf)[NT][NX][2]) {
     const uint32_t slot = idx % NSTAGE, round = idx / NSTAGE;
     wait_or_abort(&sh->full[slot], round & 1u, sh, err, ERR_TILE_WAIT);
     const int g = lane >> 2, t = lane & 3;
     const uint8_t* base = slots + (size_t)slot * SLOT_BYTES + (size_t)(wk * KTW * 16 + 4 * t) * 2;
     const uint8_t* lo_p = base + (size_t)g * SROW;
-    const uint8_t* hi_p = base + (size_t)min(8 + g, RS - 1) * SROW;
+    const uint8_t* hi_p = base + (size_t)min(HI + g, RS - 1) * SROW;
 #pragma unroll
     for (int j = 0; j < KTW; ++j) {
       const uint2 lo = lds64(lo_p + j * 32), hi = lds64(hi_p + j * 32);
@@ -336,40 +336,114 @@ struct Consumer {
     if (lane == 0) tc::mbar_arrive(&sh->empty[slot]);
     ++idx;
   }
-  template <int KTW, int NCH, int NT, int NX, int CH = 0>
+  template <int KTW, int NCH, int HI, int NT, int NX, int CH = 0>
   __device__ __forceinline__ void row_group_local_nt(float (&c)[NT][4], const uint32_t (&xf)[NT][NX][2]) {
-    mma_tile_nt<KTW, CH * KTW>(c, xf);
-    if constexpr (CH + 1 < NCH) row_group_local_nt<KTW, NCH, NT, NX, CH + 1>(c, xf);
+    mma_tile_nt<KTW, HI, CH * KTW>(c, xf);
+    if constexpr (CH + 1 < NCH) row_group_local_nt<KTW, NCH, HI, NT, NX, CH + 1>(c, xf);
+  }
+  // the activation's fragments of all column tiles from the streamed tiles (row 8 nt + g of the tile)
+  template <int KTW, int NCH, int NT>
+  __device__ __forceinline__ void row_group_streamed_nt(float (&c)[NT][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    for (int ch = 0; ch < NCH; ++ch) {
+      const uint32_t slot = aidx % ASTAGE, round = aidx / ASTAGE;
+      wait_or_abort(&sh->afull[slot], round & 1u, sh, err, ERR_TILE_WAIT);
+      uint32_t xf[NT][KTW][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint8_t* xp = aslots + (size_t)slot * ASLOT_BYTES + (size_t)(nt * 8 + g) * SROW + (size_t)(wk * KTW * 16 + 4 * t) * 2;
+#pragma unroll
+        for (int j = 0; j < KTW; ++j) {
+          const uint2 v = lds64(xp + j * 32);
+          xf[nt][j][0] = v.x;
+          xf[nt][j][1] = v.y;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&sh->aempty[slot]);
+      ++aidx;
+      mma_tile_nt<KTW, 8, 0>(c, xf);
+    }
+  }
+  // Sum of the warps' accumulators of all column tiles: thread i < 128 gets, per tile, element (MMA row i / 8,
+  // batch row 8 nt + i % 8) in s, and with PAIR (i < 64) the element of MMA row + 8 in s2.
+  template <int NT, bool PAIR>
+  __device__ __forceinline__ void reduce_nt(const float (&c)[NT][4], float (&s)[NT], float (&s2)[NT]) {
+    float* buf = red + (nred & 1u) * (NCW * 128 * NT);
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      *reinterpret_cast<float2*>(buf + (nt * NCW + warp) * 128 + g * 8 + 2 * t) = make_float2(c[nt][0], c[nt][1]);
+      *reinterpret_cast<float2*>(buf + (nt * NCW + warp) * 128 + 64 + g * 8 + 2 * t) = make_float2(c[nt][2], c[nt][3]);
+    }
+    consumer_sync();
+    ++nred;
+    const int i = warp * 32 + lane;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      s[nt] = s2[nt] = 0.0f;
+      if (i < 128) {
+#pragma unroll
+        for (int w = 0; w < NCW; ++w) s[nt] += buf[(nt * NCW + w) * 128 + i];
+        if (PAIR && i < 64) {
+#pragma unroll
+          for (int w = 0; w < NCW; ++w) s2[nt] += buf[(nt * NCW + w) * 128 + 64 + i];
+        }
+      }
+    }
+  }
+  template <int NT>
+  __device__ __forceinline__ static void zero(float (&c)[NT][4]) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
   }
   // rows [r0, r1): epi(row, n, sum) for batch rows n < B <= 8 * NT
   template <int KTW, int NCH, int NT, int NX, class Epi>
   __device__ __forceinline__ void rows_local_nt(const uint32_t (&xf)[NT][NX][2], int r0, int r1, int B, Epi epi) {
     for (int rg = r0; rg < r1; rg += RS) {
       const int nr = min(RS, r1 - rg);
-      float c[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
-      row_group_local_nt<KTW, NCH>(c, xf);
-      float* buf = red + (nred & 1u) * (NCW * 128 * NT);
-      const int g = lane >> 2, t = lane & 3;
+      float c[NT][4], s[NT], s2[NT];
+      zero(c);
+      row_group_local_nt<KTW, NCH, 8>(c, xf);
+      reduce_nt<NT, false>(c, s, s2);
+      const int i = warp * 32 + lane, row = i >> 3;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        *reinterpret_cast<float2*>(buf + (nt * NCW + warp) * 128 + g * 8 + 2 * t) = make_float2(c[nt][0], c[nt][1]);
-        *reinterpret_cast<float2*>(buf + (nt * NCW + warp) * 128 + 64 + g * 8 + 2 * t) = make_float2(c[nt][2], c[nt][3]);
+        const int n = nt * 8 + (i & 7);
+        if (i < 128 && row < nr && n < B) epi(rg + row, n, s[nt]);
       }
-      consumer_sync();
-      ++nred;
-      const int i = warp * 32 + lane;
-      if (i < 128) {
-        const int row = i >> 3;
+    }
+  }
+  template <int KTW, int NCH, int NT, int NX, class Epi>
+  __device__ __forceinline__ void pairs_local_nt(const uint32_t (&xf)[NT][NX][2], int p0, int p1, int B, Epi epi) {
+    constexpr int PG = Geo::PG;
+    for (int pg = p0; pg < p1; pg += PG) {
+      const int np = min(PG, p1 - pg);
+      float c[NT][4], s[NT], s2[NT];
+      zero(c);
+      row_group_local_nt<KTW, NCH, PG>(c, xf);
+      reduce_nt<NT, true>(c, s, s2);
+      const int i = warp * 32 + lane, pair = i >> 3;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          float s = 0.0f;
+      for (int nt = 0; nt < NT; ++nt) {
+        const int n = nt * 8 + (i & 7);
+        if (i < 64 && pair < np && n < B) epi(pg + pair, n, s[nt], s2[nt]);
+      }
+    }
+  }
+  template <int KTW, int NCH, int NT, class Epi>
+  __device__ __forceinline__ void rows_streamed_nt(int r0, int r1, int B, Epi epi) {
+    for (int rg = r0; rg < r1; rg += RS) {
+      const int nr = min(RS, r1 - rg);
+      float c[NT][4], s[NT], s2[NT];
+      zero(c);
+      row_group_streamed_nt<KTW, NCH>(c);
+      reduce_nt<NT, false>(c, s, s2);
+      const int i = warp * 32 + lane, row = i >> 3;
 #pragma unroll
-          for (int w = 0; w < NCW; ++w) s += buf[(nt * NCW + w) * 128 + i];
-          const int n = nt * 8 + (i & 7);
-          if (row < nr && n < B) epi(rg + row, n, s);
-        }
+      for (int nt = 0; nt < NT; ++nt) {
+        const int n = nt * 8 + (i & 7);
+        if (i < 128 && row < nr && n < B) epi(rg + row, n, s[nt]);
       }
     }
   }
@@ -536,6 +610,26 @@ __device__ __forceinline__ void norm_to_fragments(uint32_t (&xf)[HT][2], const b
   load_local_x<HT, KTW, NCH>(xf, xs, wk, lane);
 }
 
+// The same for 8 * NT batch rows: fragments per column tile.
+template <int HT, int KTW, int NCH, int NT>
+__device__ __forceinline__ void norm_to_fragments_nt(uint32_t (&xf)[NT][HT][2], const bf16* x, const float* res_in,
+                                                     float* res_out, const bf16* norm_w, float eps, int B, uint8_t* xs,
+                                                     int warp, int lane, int wk, bool wait_pdl) {
+  constexpr int H = HT * NCW * 16, XS = H * 2 + 32;
+  uint2 nw[HT];
+#pragma unroll
+  for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(norm_w + (i * 32 + lane) * 4);
+  if (wait_pdl) pdl_wait();
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+    norm_rows<HT>(x + (size_t)nt * 8 * H, res_in ? res_in + (size_t)nt * 8 * H : nullptr,
+                  blockIdx.x == 0 ? res_out + (size_t)nt * 8 * H : nullptr, nw, eps, B - nt * 8, xs + (size_t)nt * 8 * XS, warp,
+                  lane);
+  consumer_sync();
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) load_local_x<HT, KTW, NCH>(xf[nt], xs + (size_t)nt * 8 * XS, wk, lane);
+}
+
 // The consumers of all CTAs meet (see grid_arrive / grid_wait). `for_bulk_copies`: what this CTA stored is read
 // by other CTAs' bulk copies next.
 struct GridSync {
@@ -653,23 +747,24 @@ __device__ __forceinline__ void ffn_half(Consumer<Geo>& co, GridSync& gs, uint8_
   constexpr int H = HT * NCW * 16, I = IT * NCW * 16;
   typedef Pieces<HT, Geo> PH;
   typedef Pieces<IT, Geo> PI;
+  constexpr int NT = Geo::NT;
+  auto store_act = [&](int pair, int n, float gate, float up) { act[(size_t)n * I + pair] = __float2bfloat16_rn(silu_mul(gate, up)); };
+  auto store_y = [&](int row, int n, float s) { y[(size_t)n * H + row] = __float2bfloat16_rn(s); };
   {
-    uint32_t xf[HT][2];
-    norm_to_fragments<HT, PH::KTW, PH::NCH>(xf, x, res_in, res_out, norm_w, eps, B, xs, co.warp, co.lane, co.wk, first);
+    uint32_t xf[NT][HT][2];
+    norm_to_fragments_nt<HT, PH::KTW, PH::NCH>(xf, x, res_in, res_out, norm_w, eps, B, xs, co.warp, co.lane, co.wk, first);
     if (first) gs.begin();
     FTL(2);
-    co.template pairs_local<PH::KTW, PH::NCH>(xf, p0, p1, B, [&](int pair, int n, float gate, float up) {
-      act[(size_t)n * I + pair] = __float2bfloat16_rn(silu_mul(gate, up));
-    });
+    if constexpr (NT == 1) co.template pairs_local<PH::KTW, PH::NCH>(xf[0], p0, p1, B, store_act);
+    else co.template pairs_local_nt<PH::KTW, PH::NCH>(xf, p0, p1, B, store_act);
   }
   FTL(4);
   gs.sync(true);   // also: every warp has its fragments out of xs, whose memory the activation tiles use next
   FTL(6);
   if (first) pdl_trigger();
   co.act_begin();
-  co.template rows_streamed<PI::KTW, PI::NCH>(r0, r1, B, [&](int row, int n, float s) {
-    y[(size_t)n * H + row] = __float2bfloat16_rn(s);
-  });
+  if constexpr (NT == 1) co.template rows_streamed<PI::KTW, PI::NCH>(r0, r1, B, store_y);
+  else co.template rows_streamed_nt<PI::KTW, PI::NCH, NT>(r0, r1, B, store_y);
 }
 
 template <int HT, int IT, class Geo>
@@ -677,7 +772,7 @@ __global__ void __launch_bounds__(NTHREADS_ACT, 1) ffn_decode_fused_kernel(const
   constexpr int H = HT * NCW * 16, I = IT * NCW * 16;
   typedef Pieces<HT, Geo> PH;
   typedef Pieces<IT, Geo> PI;
-  static_assert(MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows share the activation tiles' memory");
+  static_assert(Geo::NT * MAX_B * (H * 2 + 32) <= Geo::AST * Geo::ASLOT, "the normalised rows share the activation tiles' memory");
   extern __shared__ __align__(128) uint8_t smem[];
   const Carve<Geo> m(smem);
   Shared* sh = m.sh;
@@ -755,18 +850,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) norm_linear_decode_kernel(const _
   Consumer<Geo> co{sh, m.slots, m.xs, m.red, 0u, 0u, 0u, warp, lane, (warp + cta) & (NCW - 1), p.err};
   uint32_t xf[NT][HT][2];   // batch rows 8 nt .. 8 nt + 7
   if (p.norm_w != nullptr) {
-    uint2 nw[HT];
-#pragma unroll
-    for (int i = 0; i < HT; ++i) nw[i] = *reinterpret_cast<const uint2*>(p.norm_w + (i * 32 + lane) * 4);
-    pdl_wait();
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-      norm_rows<HT>(p.x + (size_t)nt * 8 * H, p.res_in ? p.res_in + (size_t)nt * 8 * H : nullptr,
-                    cta == 0 ? p.res_out + (size_t)nt * 8 * H : nullptr, nw, p.eps, p.B - nt * 8, m.xs + (size_t)nt * 8 * XS,
-                    warp, lane);
-    consumer_sync();
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) load_local_x<HT, PH::KTW, PH::NCH>(xf[nt], m.xs + (size_t)nt * 8 * XS, co.wk, lane);
+    norm_to_fragments_nt<HT, PH::KTW, PH::NCH>(xf, p.x, p.res_in, p.res_out, p.norm_w, p.eps, p.B, m.xs, warp, lane, co.wk, true);
   } else {
     // no norm in front: the rows' fragments come straight from global memory
     pdl_wait();
@@ -1076,13 +1160,13 @@ OSB_API int osb_ffn_decode_fused_supported(int H, int I) {
 }
 
 // y [B,H] = down(silu(gate(h)) * up(h)), h = rmsnorm(res_in + x) * norm_w; res_out = res_in + x (fp32).
-// B <= 8, bf16 weights and activations. `act` [B,I] is scratch; `bar` is a zeroed 64-bit counter that belongs
+// B <= 16, bf16 weights and activations. `act` [B,I] is scratch; `bar` is a zeroed 64-bit counter that belongs
 // to these launches alone (between launches it is a multiple of the number of SMs); `err` is the device error flag.
 OSB_API int osb_ffn_decode_fused(void* y, float* res_out, const void* x, const float* res_in, const void* norm_w,
                                  float eps, const void* w_gate_up, const void* w_down, void* act, unsigned long long* bar,
                                  int* err, int B, int H, int I, cudaStream_t stream) {
   if (B <= 0) return OSB_OK;
-  if (B > MAX_B || !osb_ffn_decode_fused_supported(H, I)) return OSB_ERR_UNSUPPORTED;
+  if (B > 2 * MAX_B || !osb_ffn_decode_fused_supported(H, I)) return OSB_ERR_UNSUPPORTED;
   if ((((uintptr_t)y | (uintptr_t)res_out | (uintptr_t)x | (uintptr_t)res_in | (uintptr_t)norm_w | (uintptr_t)w_gate_up |
         (uintptr_t)w_down | (uintptr_t)act) & 15) != 0)
     return OSB_ERR_BAD_SHAPE;
@@ -1091,6 +1175,15 @@ OSB_API int osb_ffn_decode_fused(void* y, float* res_out, const void* x, const f
   p.w_gate_up = (const bf16*)w_gate_up; p.w_down = (const bf16*)w_down; p.act = (bf16*)act; p.y = (bf16*)y;
   p.bar = bar; p.err = err; p.eps = eps; p.B = B; p.H = H; p.I = I;
   const int n_sm = sm_count();
+  if (B > MAX_B) {   // 9 to 16 rows: two column tiles, activation tiles of 16 rows, two weight tiles in flight
+    typedef Geometry<16, 12, 2, 2, 2> GeoB2;
+    typedef Geometry<12, 7, 5, 3, 2> GeoA2;
+    typedef Geometry<16, 8, 2, 2, 2> GeoC2;
+    if (H == 1536 && I == 8960) return launch_ffn<12, 70, GeoB2>(p, n_sm, stream);
+    if (H == 256 && I == 512) return launch_ffn<2, 4, GeoB2>(p, n_sm, stream);
+    if (H == 384 && I == 1920) return launch_ffn<3, 15, GeoA2>(p, n_sm, stream);
+    return launch_ffn<16, 2, GeoC2>(p, n_sm, stream);
+  }
   typedef Geometry<16, 12, 3, 3> GeoB;
   typedef Geometry<12, 7, 7, 4> GeoA;
   if (H == 1536 && I == 8960) return launch_ffn<12, 70, GeoB>(p, n_sm, stream);
@@ -1217,9 +1310,9 @@ OSB_API int osb_norm_linear_decode(void* y, float* res_out, const void* x, const
   typedef Geometry<16, 8, 3, 2> GeoU;
   const int n_sm = sm_count();
   if (B > MAX_B) {   // 9 to 16 rows: two column tiles
-    typedef Geometry<16, 12, 2, 2, 2> GeoS2;
-    typedef Geometry<12, 7, 4, 3, 2> GeoT2;
-    typedef Geometry<16, 8, 2, 4, 2> GeoU2;
+    typedef Geometry<16, 12, 2, 1, 2> GeoS2;
+    typedef Geometry<12, 7, 4, 2, 2> GeoT2;
+    typedef Geometry<16, 8, 2, 2, 2> GeoU2;
     if (H == 1536) return launch_fused<GeoS2>(norm_linear_decode_kernel<12, GeoS2>, p, n_sm, false, stream);
     if (H == 256) return launch_fused<GeoS2>(norm_linear_decode_kernel<2, GeoS2>, p, n_sm, false, stream);
     if (H == 384) return launch_fused<GeoT2>(norm_linear_decode_kernel<3, GeoT2>, p, n_sm, false, stream);

@@ -16,18 +16,20 @@ from ._common import _check, _cuda_contig, _p
 class PersistentDecodeOps:
     FUSED_MAX_ROWS = 8
     STREAM_LINEAR_MAX_ROWS = 16    # the projection kernel (with or without its norm) has a form with two column tiles
+    FFN_MAX_ROWS = 16              # and so has the feed-forward half
+    SCRATCH_ROWS = 16
     STREAM_LINEAR_MAX_N = 4096     # rows of W up to which the streaming projection without norm is used
     FUSED_MAX_SPLITS = 16
 
     def _fused_state(self, device: torch.device, width: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """What the persistent decode kernels of one device share: the words of their grid barrier and
-        an activation scratch of FUSED_MAX_ROWS rows. They run one after the other on one stream."""
+        an activation scratch of SCRATCH_ROWS rows. They run one after the other on one stream."""
         idx = device.index if device.index is not None else torch.cuda.current_device()
         st = self._fused.get(idx)
-        if st is None or st[1].numel() < self.FUSED_MAX_ROWS * width:
+        if st is None or st[1].numel() < self.SCRATCH_ROWS * width:
             with torch.inference_mode(False):
                 bar = st[0] if st is not None else torch.zeros(64, dtype=torch.int32, device=device)
-                act = torch.empty(self.FUSED_MAX_ROWS * width, dtype=torch.bfloat16, device=device)
+                act = torch.empty(self.SCRATCH_ROWS * width, dtype=torch.bfloat16, device=device)
             if st is not None:
                 self._retired.append(st[1])      # a captured graph may still write to it
             st = self._fused[idx] = (bar, act)
@@ -196,13 +198,13 @@ class PersistentDecodeOps:
     def can_ffn_decode_fused(self, x: torch.Tensor, norm_weight: torch.Tensor, w_gate_up: torch.Tensor,
                              w_down: torch.Tensor) -> bool:
         """Whether ``ffn_decode_fused`` takes these operands (else: norm, ``gate_up_silu``, ``linear``)."""
-        return (self.fuse_ffn_decode and x.dim() == 2 and 0 < x.shape[0] <= self.FUSED_MAX_ROWS
+        return (self.fuse_ffn_decode and x.dim() == 2 and 0 < x.shape[0] <= self.FFN_MAX_ROWS
                 and x.dtype == norm_weight.dtype == w_gate_up.dtype == w_down.dtype == torch.bfloat16
                 and bool(self.lib.osb_ffn_decode_fused_supported(x.shape[1], w_down.shape[1])))
 
     def ffn_decode_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                          w_gate_up: torch.Tensor, w_down: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        """down(silu(gate(h)) * up(h)) with h = norm(residual + x) * norm_weight, for up to 8 rows, as one
+        """down(silu(gate(h)) * up(h)) with h = norm(residual + x) * norm_weight, for up to 16 rows, as one
         persistent kernel that streams both weight matrices; returns (y, the new fp32 residual stream)."""
         for name, t in (("x", x), ("norm_weight", norm_weight), ("w_gate_up", w_gate_up), ("w_down", w_down)):
             _cuda_contig(name, t, torch.bfloat16)
@@ -210,7 +212,7 @@ class PersistentDecodeOps:
         I = w_down.shape[1]
         _check(self.can_ffn_decode_fused(x, norm_weight, w_gate_up, w_down) and w_gate_up.shape == (2 * I, H)
                and w_down.shape == (H, I) and norm_weight.shape == (H,),
-               "ffn_decode_fused: x [B<=8,H] bf16, w_gate_up [2I,H], w_down [H,I] at sizes it is built for")
+               "ffn_decode_fused: x [B<=16,H] bf16, w_gate_up [2I,H], w_down [H,I] at sizes it is built for")
         if residual is not None:
             _cuda_contig("residual", residual, torch.float32)
             _check(residual.shape == x.shape, "ffn_decode_fused: residual [B,H]")

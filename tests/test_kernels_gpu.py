@@ -222,7 +222,7 @@ def test_norm_linear_decode(H, N, B):
 
 
 @pytest.mark.parametrize("H,I", [(256, 512), (384, 1920), (2048, 256), (1536, 8960)])
-@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("B", [1, 3, 8, 9, 12, 16])
 def test_ffn_decode_fused(H, I, B):
     """The persistent feed-forward kernel (norm, gate/up with the activation, grid barrier, down) against
     the plain parts in float64 from the same bf16-rounded intermediates. The new residual stream is the
