@@ -14,6 +14,7 @@ from typing import Dict, List, Optional, Sequence as Seq
 
 import torch
 
+from .. import ops
 from ..config import EngineConfig, resolve, resolve_dir
 from ..config.model_config import read_config_dict
 from ..sampling import SampleHandle, Sampler
@@ -247,6 +248,8 @@ class LLMEngine:
         while self.has_unfinished():
             for d in self.step():
                 outs.setdefault(d.request_id, []).extend(d.new_token_ids)
+        if self.runner.check_device_errors:
+            ops.kernels().check_device_errors()     # the steps only looked at what had already come back
         return outs
 
     def generate(self, prompts: Seq[Seq[int]], sampling: Optional[SamplingParams] = None) -> List[List[int]]:

@@ -356,7 +356,9 @@ class ModelRunner:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
         if self.check_device_errors:
-            ops.kernels().check_device_errors()
+            # no wait for the device here: what a kernel of this step reports is raised a step or two later
+            # (or by the caller's own ``ops.kernels().check_device_errors()``, which waits)
+            ops.kernels().check_device_errors_async()
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _graphable(self, entries: Sequence[StepEntry]) -> bool:

@@ -12,6 +12,7 @@ The object that does the work is ``kernels()``; model code calls it as
 
 from __future__ import annotations
 
+import collections
 import contextlib
 import ctypes
 from typing import Dict, Optional, Tuple
@@ -39,6 +40,8 @@ class CudaKernels(PersistentDecodeOps):
         # the library GEMM (used for medium row counts) must accumulate in fp32, also across its K splits
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self._err: Dict[int, torch.Tensor] = {}
+        self._err_pending: Dict[int, collections.deque] = {}   # copies of the flags on their way to the host
+        self._err_hosts: Dict[int, list] = {}                   # pinned landing places not in use
         self.launches = 0  # kernels of this library launched so far
         self.skinny_warps = 0  # 0: the skinny GEMM picks its K split from the shape
         #: bf16 products with more rows than SKINNY_MAX_ROWS: the tcgen05/TMEM/TMA kernel (True) or the
@@ -114,6 +117,33 @@ class CudaKernels(PersistentDecodeOps):
                 for bar, _ in self._fused.values():
                     bar.zero_()     # a CTA that gave up at a grid barrier leaves the counter between two multiples
                 raise KernelError("device-side check failed: " + _DEVICE_ERR.get(v, f"code {v}"))
+
+    def check_device_errors_async(self) -> None:
+        """The same without waiting for the device: queues a copy of the error flags behind the work launched so
+        far and raises what an earlier such copy has brought back, so an error shows a step or two late."""
+        for idx, flag in self._err.items():
+            pending = self._err_pending.setdefault(idx, collections.deque())
+            while pending and pending[0][0].query():
+                _, host = pending.popleft()
+                v = int(host[0])
+                self._err_hosts.setdefault(idx, []).append(host)
+                if v != 0:
+                    flag.zero_()
+                    for bar, _ in self._fused.values():
+                        bar.zero_()
+                    pending.clear()
+                    raise KernelError("device-side check failed: " + _DEVICE_ERR.get(v, f"code {v}"))
+            if len(pending) < 4:
+                free = self._err_hosts.setdefault(idx, [])
+                if free:
+                    host = free.pop()
+                else:
+                    with torch.inference_mode(False):
+                        host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+                host.copy_(flag, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                pending.append((ev, host))
 
     # ------------------------------------------------------------------ embedding
     def embed_lookup(self, table: torch.Tensor, ids: torch.Tensor, out_dtype: torch.dtype,

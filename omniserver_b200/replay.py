@@ -26,6 +26,7 @@ from typing import Dict, Iterable, Optional
 import numpy as np
 import torch
 
+from . import ops
 from .config import EngineConfig
 from .engine.llm_engine import build_runner
 from .engine.step import ModelRunner, StepEntry
@@ -54,6 +55,8 @@ class TraceReplayer:
         logits = None
         if entries:
             out = self.runner.step(entries)
+            if self.runner.check_device_errors:
+                ops.kernels().check_device_errors()   # a replayed step is checked before the next one (this waits)
             if out.shape[0] > 0:
                 logits = out
         for rid in step.get("end", []):

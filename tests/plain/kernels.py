@@ -37,6 +37,9 @@ class PlainKernels:
     def pinned_stream(self):
         yield
 
+    def check_device_errors_async(self) -> None:
+        pass
+
     def check_device_errors(self) -> None:
         pass
 

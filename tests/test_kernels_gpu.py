@@ -67,6 +67,24 @@ def test_embed_lookup_reports_bad_id():
         K().check_device_errors()
 
 
+def test_device_errors_are_also_reported_without_waiting():
+    """The check that the engine makes after every step does not wait for the device: it queues a copy of the
+    flag and raises what an earlier copy has brought back."""
+    from omniserver_b200.ops import KernelError
+    k = K()
+    k.check_device_errors()
+    table = rnd(50, 32, dtype=torch.bfloat16).to(DEV)
+    k.embed_lookup(table, torch.tensor([3, 50], dtype=torch.int32, device=DEV), torch.bfloat16)
+    k.check_device_errors_async()          # the copy is on its way; nothing to report yet, or already there
+    torch.cuda.synchronize()
+    with pytest.raises(KernelError, match="outside the vocabulary"):
+        k.check_device_errors_async()
+    k.check_device_errors_async()          # the flag was cleared
+    torch.cuda.synchronize()
+    k.check_device_errors_async()
+    k.check_device_errors()
+
+
 @pytest.mark.parametrize("xdt", DTYPES)
 @pytest.mark.parametrize("wdt", DTYPES)
 @pytest.mark.parametrize("T,H,eps", [(5, 96, 1e-5), (3, 1536, 1e-6), (2, 5000, 1e-6), (1, 17, 1e-3), (300, 1536, 1e-6), (67, 2048, 1e-5),
