@@ -296,12 +296,250 @@ def run_ours(args):
     return 0
 
 
+def _reference_root():
+    """Where the unmodified reference package lies: the copy under baseline/_ref (it travels with the
+    repository's snapshot), else a checkout named by OMNISERVE_REFERENCE, else /root/reference."""
+    for p in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("OMNISERVE_REFERENCE", ""), "/root/reference"):
+        if p and os.path.isdir(os.path.join(p, "omniserve")):
+            return p
+    return None
+
+
 def run_reference(args):
-    # The reference has no setup.py/pyproject.toml, so pip cannot install it; its generation path
-    # also needs a downloaded checkpoint with tokenizer and vLLM's FlashAttention binary.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "omniserve has no setup.py/pyproject.toml (pip install fails) and its runner needs a downloaded "
-                      "Qwen2-VL checkpoint and tokenizer, which do not exist offline"}))
+    """The reference arm: omniserve's own LLMEngine -> Scheduler -> MultimodalRunner -> Qwen2LLM ->
+    PreallocatedKVCache (Triton norm/activation kernels, vLLM's FlashAttention, cuBLAS), unmodified, on the
+    same model sizes, batch, context and step counts. The only code of this file on that path is the adapter
+    below, which stands where omniserve's Qwen2VLAdapter loads a checkpoint, a tokenizer and a vision tower
+    (none exist offline): it holds the reference's Qwen2LLM in fp16 (its only precision) filled with random
+    weights through the reference's own load_from_hf, and hands token ids through. Nothing of
+    omniserver_b200 is imported here."""
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:400]}))
+        return 0
+
+    root = _reference_root()
+    if root is None:
+        return unavailable("no copy of the reference (baseline/_ref/omniserve) beside bench.py")
+    sys.path.insert(0, root)
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device is visible to the reference arm")
+        from omniserve import LLMEngine, Request, SamplingParams, SchedulerConfig
+        from omniserve.model import Qwen2Config, Qwen2LLM, load_from_hf
+        from omniserve.model.positions import IMAGE_TOKEN_ID
+        from omniserve.models.base import VLMAdapter
+        from omniserve.models.qwen2_vl import Qwen2VLAdapter
+        from omniserve.runners.multimodal import MultimodalRunner
+        from vllm.vllm_flash_attn.flash_attn_interface import flash_attn_varlen_func  # noqa: F401  (its attention)
+        import triton  # noqa: F401  (its norm and activation kernels)
+    except Exception as e:  # the reason must be the error raised on this machine
+        return unavailable(f"importing the reference's stack failed: {type(e).__name__}: {e}")
+
+    hbm_peak, tf_peak, peak_src = peaks()
+    cfg = dict(MODEL_2B)
+    if args.layers != FULL_LAYERS:
+        return unavailable("the reference arm runs the whole model only (omniserve's Qwen2Config is fixed at 28 layers)")
+    dev = "cuda"
+    torch.cuda.set_device(0)
+
+    class RandomWeightsAdapter(VLMAdapter):
+        """Token ids in, token ids out; the model and the position rules are omniserve's own."""
+
+        def __init__(self):
+            self.device = dev
+            self.image_token_id = IMAGE_TOKEN_ID
+            self.eos_ids = set()                    # the timed requests run to max_new_tokens, as in our arm
+            rcfg = Qwen2Config()                    # the reference's defaults are the 2B sizes
+            for ours, theirs in (("hidden_size", "hidden_size"), ("num_hidden_layers", "num_layers"),
+                                 ("num_attention_heads", "num_heads"), ("num_key_value_heads", "num_kv_heads"),
+                                 ("head_dim", "head_dim"), ("intermediate_size", "intermediate_size"),
+                                 ("vocab_size", "vocab_size")):
+                assert getattr(rcfg, theirs) == cfg[ours], (ours, getattr(rcfg, theirs), cfg[ours])
+            self._llm = Qwen2LLM(rcfg).half().to(dev)
+            g = torch.Generator(device=dev).manual_seed(SEED)
+            H, I, V = rcfg.hidden_size, rcfg.intermediate_size, rcfg.vocab_size
+            q, kv = rcfg.num_heads * rcfg.head_dim, rcfg.num_kv_heads * rcfg.head_dim
+
+            def rnd(*shape):
+                return (torch.randn(shape, generator=g, device=dev, dtype=torch.float32) * 0.02).half()
+
+            sd = {"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": torch.ones(H, device=dev).half()}
+            for i in range(rcfg.num_layers):
+                p = f"model.layers.{i}."
+                sd.update({
+                    p + "self_attn.q_proj.weight": rnd(q, H), p + "self_attn.q_proj.bias": rnd(q),
+                    p + "self_attn.k_proj.weight": rnd(kv, H), p + "self_attn.k_proj.bias": rnd(kv),
+                    p + "self_attn.v_proj.weight": rnd(kv, H), p + "self_attn.v_proj.bias": rnd(kv),
+                    p + "self_attn.o_proj.weight": rnd(H, q), p + "mlp.gate_proj.weight": rnd(I, H),
+                    p + "mlp.up_proj.weight": rnd(I, H), p + "mlp.down_proj.weight": rnd(H, I),
+                    p + "input_layernorm.weight": torch.ones(H, device=dev).half(),
+                    p + "post_attention_layernorm.weight": torch.ones(H, device=dev).half()})
+            load_from_hf(self._llm, sd)
+            self._llm = self._llm.eval()
+            self.num_layers, self.num_kv_heads, self.head_dim = rcfg.num_layers, rcfg.num_kv_heads, rcfg.head_dim
+
+        def preprocess(self, images):
+            return None, None
+
+        def encode_prompt(self, prompt, grids):
+            return list(prompt)
+
+        def embed_tokens(self, input_ids):
+            return self._llm.embed_tokens(input_ids)
+
+        def vision_embed(self, pixel_values, grids):
+            raise RuntimeError("text-only benchmark")
+
+        # the position rules and the forward are the reference adapter's own bodies, called unchanged
+        def prefill_positions(self, input_ids, grids):
+            return Qwen2VLAdapter.prefill_positions(self, input_ids, grids)
+
+        def decode_positions(self, write_pos, rope_deltas):
+            return Qwen2VLAdapter.decode_positions(self, write_pos, rope_deltas)
+
+        def llm(self, embeds, positions, attn_mask, cache, logits_indices=None):
+            return Qwen2VLAdapter.llm(self, embeds, positions, attn_mask, cache, logits_indices=logits_indices)
+
+        def detokenize(self, token_ids):
+            return ""
+
+    gen = torch.Generator().manual_seed(SEED)
+
+    def new_prompt(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+
+    try:
+        t0 = time.time()
+        adapter = RandomWeightsAdapter()
+        torch.cuda.synchronize()
+        build_s = time.time() - t0
+    except Exception as e:
+        return unavailable(f"building the reference's model failed: {type(e).__name__}: {e}")
+
+    def say(msg):
+        print(f"[bench reference] {msg}", file=sys.stderr, flush=True)
+
+    # omniserve's own benchmark packs at most 16,384 prompt tokens into one forward
+    # (benchmarks/compare/run_omniserve.py:28-29); its Triton activation kernel indexes rows in 32-bit
+    # (omniserve/kernels/fused_ops.py:111-119), which 131,072 packed rows of 17,920 columns overflow.
+    PACKED_PREFILL_TOKENS = 16384
+
+    def decode_run(B, steps, warmup, use_graph, sample_clocks=False):
+        """B requests of CONTEXT tokens through omniserve's engine; returns device-timed ms per decode step
+        (CUDA events around its runner.decode), end-to-end tokens/s through LLMEngine.step (wall clock,
+        token ids read on the host every step, as the reference does), and the first prefill step's wall time."""
+        per_step = max(1, min(B, PACKED_PREFILL_TOKENS // CONTEXT))
+        admit_steps = -(-B // per_step)
+        n_new = admit_steps + 2 * (warmup + steps) + 2
+        max_len = -(-(CONTEXT + n_new + 1) // 256) * 256       # its cache is one page of max_len tokens per request
+        say(f"batch {B}: runner (graph={use_graph}, max_len={max_len})")
+        runner = MultimodalRunner(adapter, max_running=B, max_len=max_len, use_graph=use_graph)
+        eng = LLMEngine(runner, SchedulerConfig(max_running=B, max_prefill_per_step=per_step,
+                                                max_prefill_tokens=per_step * CONTEXT, max_seq_len=4096))
+        for _ in range(B):
+            eng.add_request(Request(prompt=new_prompt(CONTEXT), sampling=SamplingParams(max_new_tokens=n_new)))
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        eng.step()                                             # up to 8 prompts packed into one prefill; one token each
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t1
+        while eng.scheduler.waiting:
+            eng.step()                                         # the next prompts; the running requests decode beside them
+        torch.cuda.synchronize()
+        say(f"batch {B}: prompts in")
+        seqs = list(eng.scheduler.running)
+        assert len(seqs) == B and all(1 <= s.num_output_tokens <= admit_steps for s in seqs)
+        for _ in range(warmup):
+            runner.decode(seqs)
+        torch.cuda.synchronize()
+        say(f"batch {B}: warm")
+        clocks = ClockSampler() if sample_clocks else None
+        if clocks:
+            clocks.start()
+            time.sleep(0.3)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        n0 = seqs[0].num_output_tokens
+        for a, b in ev:
+            a.record()
+            runner.decode(seqs)                                # what LLMEngine.step calls for a decode-only step
+            b.record()
+        torch.cuda.synchronize()
+        ck = clocks.stop() if clocks else None
+        assert seqs[0].num_output_tokens == n0 + steps
+        ms = statistics.median(a.elapsed_time(b) for a, b in ev)
+        for _ in range(warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        toks = 0
+        for _ in range(steps):
+            toks += len(eng.step())                            # one delta per request that produced a token
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t2
+        assert toks == steps * B and seqs[0].num_output_tokens == n0 + steps + warmup + steps
+        say(f"batch {B}: {ms:.3f} ms per decode step, {toks / e2e_s:.0f} tokens/s through its engine")
+        del runner, eng
+        torch.cuda.empty_cache()
+        return ms, toks / e2e_s, prefill_s, ck
+
+    graph = not args.no_graphs
+    note = ""
+    try:
+        try:
+            ms, e2e_v, _, clocks = decode_run(args.batch, args.steps, args.warmup, graph, sample_clocks=True)
+        except Exception as e:
+            if not graph:
+                raise
+            note = f"its CUDA-graph decode failed ({type(e).__name__}: {str(e)[:120]}); eager decode timed"
+            graph = False
+            torch.cuda.synchronize()
+            ms, e2e_v, _, clocks = decode_run(args.batch, args.steps, args.warmup, graph, sample_clocks=True)
+        points = {}
+        if not args.no_points:
+            for B in (1, 64):
+                pms, _, _, _ = decode_run(B, max(8, args.steps // 2), max(3, args.warmup // 2), graph)
+                points[f"decode_b{B}"] = round(B / (pms / 1e3), 1)
+        # prefill: one 2,048-token prompt through its engine (admission + packed prefill + first token)
+        pre = []
+        for _ in range(4):
+            _, _, ps, _ = decode_run(1, 1, 0, False)
+            pre.append(ps * 1e3)
+        pre_ms = statistics.median(pre[1:])
+    except Exception as e:
+        return unavailable(f"running the reference failed: {type(e).__name__}: {e}")
+
+    nums = model_numbers(cfg, FULL_LAYERS)
+    ctx_mid = CONTEXT + 1 + args.warmup + args.steps / 2
+    step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_per_token"]
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    pflops = prefill_flops(cfg, FULL_LAYERS, CONTEXT)
+    line = {
+        "impl": "reference",
+        "metric": "decode tokens/s (Qwen2-VL-2B text decoder, batch %d, 2048-token contexts)" % args.batch,
+        "value": round(args.batch / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16",
+        "data": "synthetic: uniform random token ids, random weights (seed 2)",
+        "config": {"model": "Qwen2-VL-2B text decoder (random weights), omniserve Qwen2LLM", "layers": FULL_LAYERS,
+                   "layers_of_model": FULL_LAYERS, "hidden_size": 1536, "heads": 12, "kv_heads": 2, "head_dim": 128,
+                   "intermediate_size": 8960, "vocab_size": 151936, "tied_head": True, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "new_tokens": NEW_TOKENS, "page_size": "one slot of max_len per request",
+                   "parallelism": "single GPU", "decode": "cuda graph" if graph else "eager",
+                   "l2": "inputs (3 GB of weights) larger than L2, no flush"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_v, 1), "unit": "tokens/s", "h2d_bytes_per_step": 8 * args.batch * 2,
+                "d2h_bytes_per_step": 8 * args.batch, "steps": args.steps, "tokens": args.steps * args.batch},
+        "gpu_launches": 0,
+        "prefill": {"value": round(CONTEXT / (pre_ms / 1e3), 1), "tokens": CONTEXT, "ms": round(pre_ms, 3),
+                    "frac": round(pflops / (pre_ms / 1e3) / (tf_peak * 1e12), 4), "of": peak_src},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                     "frac": round(achieved / hbm_peak, 4), "of": peak_src},
+        "points": points, "build_s": round(build_s, 1),
+    }
+    if note:
+        line["note"] = note
+    print(json.dumps(line))
     return 0
 
 

@@ -83,6 +83,12 @@ class PageTable:
     def array(self) -> np.ndarray:
         return self._a[:self._n]
 
+    def truncate(self, n: int) -> None:
+        """Forget the entries from index ``n`` on."""
+        if 0 <= n < self._n:
+            self._a[n:self._n] = -1
+            self._n = n
+
 
 @dataclass
 class RequestCache:
@@ -242,6 +248,19 @@ class CacheManager:
                 self._release(g, rc.tables[gi][pi])
                 rc.tables[gi][pi] = -1
             rc.first_live[gi] = max(rc.first_live[gi], first)
+
+    def rollback(self, request_id: str) -> None:
+        """Undoes the reservations of a step that did not run: the pages taken beyond the request's cursor go
+        back to the pool and nothing stays reserved."""
+        rc = self.requests[request_id]
+        keep = (rc.cursor + self.page_size - 1) // self.page_size
+        for gi, g in enumerate(self.groups):
+            tbl = rc.tables[gi]
+            for pi in range(keep, len(tbl)):
+                self._release(g, tbl[pi])
+            tbl.truncate(keep)
+            rc.first_live[gi] = min(rc.first_live[gi], keep)
+        rc.reserved = 0
 
     def _release(self, g: PageGroup, page: int) -> None:
         if page < 0:

@@ -18,13 +18,10 @@ from .. import ops
 from ..config import EngineConfig, resolve, resolve_dir
 from ..config.model_config import read_config_dict
 from ..sampling import SampleHandle, Sampler
-from .request import Request, SamplingParams, Sequence, Status
+from .request import PENDING_TOKEN, Request, SamplingParams, Sequence, Status
 from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput
 from .step import ModelRunner, StepEntry
 
-
-#: stands in ``Sequence.output_token_ids`` for a token that has been sampled on the device but not read yet
-PENDING_TOKEN = -1
 
 
 @dataclass
@@ -85,7 +82,7 @@ class LLMEngine:
                  eos_token_id: Optional[int] = None, detokenize=None, overlap: Optional[bool] = None):
         self.runner = runner
         self.scheduler = Scheduler(sched_config or SchedulerConfig(), runner.cache,
-                                   on_admit=lambda s: runner.start_request(s.request_id, s.rope_delta),
+                                   on_admit=lambda s: runner.start_request(s.request_id, s.prompt_positions, s.num_prompt_tokens),
                                    on_release=lambda s: runner.end_request(s.request_id))
         self.sampler = Sampler(seed)
         cfg = getattr(runner, "model_config", None)
@@ -114,6 +111,18 @@ class LLMEngine:
         seq = Sequence(request=request)
         if request.request_id in self._seqs:
             raise ValueError(f"request id {request.request_id!r} is already in use")
+        V = self.runner.vocab_size
+        if min(seq.prompt_token_ids) < 0 or max(seq.prompt_token_ids) >= V:
+            raise ValueError(f"request {request.request_id!r}: token id outside [0, {V})")
+        if seq.prompt_positions is not None:
+            self.runner.check_positions(seq.prompt_positions, seq.num_prompt_tokens)
+        if request.embed_rows is not None and len(request.embed_rows):
+            rows = [int(r) for r in request.embed_rows]
+            if min(rows) < 0 or max(rows) >= seq.num_prompt_tokens:
+                raise ValueError(f"request {request.request_id!r}: embedding row outside its prompt")
+            if request.embed_values is None or tuple(request.embed_values.shape) != (len(rows), self.runner.hidden_size):
+                raise ValueError(f"request {request.request_id!r}: embed_values must be "
+                                 f"[{len(rows)}, {self.runner.hidden_size}]")
         sp = request.sampling
         if self.eos_token_id is not None and not sp.ignore_eos and self.eos_token_id not in sp.stop_token_ids:
             sp.stop_token_ids.append(self.eos_token_id)   # omniserve/runners/multimodal.py:53-56
@@ -196,7 +205,8 @@ class LLMEngine:
             elif PENDING_TOKEN in toks:
                 raise RuntimeError(f"request {seq.request_id!r}: a token still on the device is needed on the host")
             entries.append(StepEntry(seq.request_id, toks, want=[e.count - 1] if e.wants_logits else [],
-                                     positions=seq.positions_for(e.start, stop), embed_rows=rows, embed_values=vals,
+                                     positions=self.runner.positions_for(seq.prompt_positions, seq.num_prompt_tokens, e.start, stop),
+                                     embed_rows=rows, embed_values=vals,
                                      from_device=from_device))
             if e.wants_logits:
                 wanting.append(seq)

@@ -1,10 +1,13 @@
 """Requests and the engine's per-request state.
 
 Names and meanings follow omniserve/request.py:21-115.  Differences: a prompt is token ids (the
-tokenizer is outside the engine); a request may carry (t, h, w) positions for its prompt and rows
-of embeddings that replace looked-up ones (what the reference computes from images,
-omniserve/runners/multimodal.py:123-127); ``top_p`` is accepted only at 1.0, since the reference
-declares it and never reads it (omniserve/request.py:32, omniserve/runners/multimodal.py:374-379).
+tokenizer is outside the engine); a request may carry positions for its prompt, as many columns per
+token as the model's position encoding takes, and rows of embeddings that replace looked-up ones (what
+the reference computes from images, omniserve/runners/multimodal.py:123-127); ``top_p`` is accepted
+only at 1.0, since the reference declares it and never reads it (omniserve/request.py:32,
+omniserve/runners/multimodal.py:374-379).  A generated token may stand in a sequence before its value
+is known on the host (``PENDING_TOKEN``), so the end of a request is decided on places filled and on
+the newest known value.
 """
 
 from __future__ import annotations
@@ -19,6 +22,9 @@ import numpy as np
 import torch
 
 _counter = itertools.count()
+
+#: stands in ``Sequence.output_token_ids`` for a token that has been sampled on the device but not read yet
+PENDING_TOKEN = -1
 
 
 class Status(enum.Enum):
@@ -54,8 +60,9 @@ class SamplingParams:
 class Request:
     """What a user submits. ``prompt`` is a list of token ids.
 
-    ``positions``: optional int array [3, len(prompt)]; absent means text positions (the index on
-    all axes).  ``embed_rows``/``embed_values``: prompt places whose embedding is given.
+    ``positions``: optional int array [columns, len(prompt)], what the model's position encoding takes
+    (three rows (t, h, w) for Qwen2-VL); absent means text positions.  ``embed_rows``/``embed_values``:
+    prompt places whose embedding is given.
     """
 
     prompt: Seq[int]
@@ -77,8 +84,8 @@ class Sequence:
     status: Status = Status.WAITING
     num_computed: int = 0          # tokens of prompt + outputs already in the cache
     scheduled: int = 0             # tokens the scheduler handed out for the running step
-    rope_delta: int = 0
-    prompt_positions: Optional[np.ndarray] = None
+    prompt_positions: Optional[np.ndarray] = None    # what came with the prompt; the position encoding reads it
+    finish_reason: Optional[str] = None              # "stop" or "length" once the request has ended by itself
     num_streamed: int = 0
     num_preemptions: int = 0
     admit_order: int = -1
@@ -93,11 +100,9 @@ class Sequence:
         p = self.request.positions
         if p is not None:
             p = np.asarray(p, dtype=np.int64)
-            if p.shape != (3, len(self.prompt_token_ids)):
-                raise ValueError(f"positions must be [3, {len(self.prompt_token_ids)}], got {p.shape}")
+            if p.ndim != 2 or p.shape[1] != len(self.prompt_token_ids):
+                raise ValueError(f"positions must be [columns, {len(self.prompt_token_ids)}], got {p.shape}")
             self.prompt_positions = p
-            # the next text position is max + 1 (omniserve/model/positions.py:57)
-            self.rope_delta = int(p.max()) + 1 - len(self.prompt_token_ids)
 
     # -- identity and sizes (omniserve/request.py:77-96)
     @property
@@ -144,33 +149,26 @@ class Sequence:
     def last_token_id(self) -> int:
         return self.output_token_ids[-1] if self.output_token_ids else self.prompt_token_ids[-1]
 
-    def positions_for(self, start: int, stop: int) -> Optional[np.ndarray]:
-        """Explicit positions of tokens [start, stop) if any of them needs them, else None."""
-        if self.prompt_positions is None or start >= self.num_prompt_tokens:
-            return None
-        n = self.num_prompt_tokens
-        head = self.prompt_positions[:, start:min(stop, n)]
-        if stop <= n:
-            return head
-        tail = np.arange(n, stop, dtype=np.int64) + self.rope_delta
-        return np.concatenate([head, np.broadcast_to(tail, (3, stop - n))], axis=1)
-
-    # -- generation (omniserve/request.py:98-115)
+    # -- generation (the names of omniserve/request.py:98-115)
     def append_token(self, token_id: int) -> None:
+        """A new place of the output: a token id, or PENDING_TOKEN while the value is still on the device."""
         if self.first_token_t is None:
             self.first_token_t = time.perf_counter()
         self.output_token_ids.append(int(token_id))
 
-    def maybe_finish(self) -> bool:
+    def stop_reason(self) -> Optional[str]:
+        """Why the request is over, if it is: "stop", the newest place holds a known value that is one of
+        its stop ids; "length", max_new_tokens places are filled (known or pending)."""
+        outs = self.output_token_ids
         sp = self.request.sampling
-        if self.output_token_ids and self.output_token_ids[-1] in sp.stop_token_ids:
-            self._finish()
-            return True
-        if self.num_output_tokens >= sp.max_new_tokens:
-            self._finish()
-            return True
-        return False
+        if outs and outs[-1] != PENDING_TOKEN and outs[-1] in sp.stop_token_ids:
+            return "stop"
+        return "length" if len(outs) >= sp.max_new_tokens else None
 
-    def _finish(self) -> None:
-        self.status = Status.FINISHED
-        self.finish_t = time.perf_counter()
+    def maybe_finish(self) -> bool:
+        why = self.stop_reason()
+        if why is not None:
+            self.finish_reason = why
+            self.status = Status.FINISHED
+            self.finish_t = time.perf_counter()
+        return why is not None

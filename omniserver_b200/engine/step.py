@@ -20,7 +20,6 @@ import torch
 from .. import ops
 from ..cache.manager import CacheManager
 from ..models.decoder import DecoderModel
-from ..parts.positions import ROPE_STATE
 
 
 @dataclass
@@ -28,8 +27,9 @@ class StepEntry:
     """A request's next tokens in one step.
 
     ``want``: places among ``tokens`` whose logits are wanted (may be empty).
-    ``positions``: int array [3, n] of (t, h, w) positions; None means the tokens continue the
-    request: cursor + rope_delta + offset on all axes.
+    ``positions``: int array [columns, n] of given positions, as many columns as the model's position
+    encoding takes (``ModelRunner.position_columns``); None means the tokens continue the request and the
+    encoding finds their positions from the request's state.
     ``embed_rows``/``embed_values``: places among ``tokens`` whose looked-up embedding is replaced
     by the given rows [len(embed_rows), hidden] (the hook the vision tower's output uses).
     ``from_device``: the entry brings one token, the one the sampler last kept for this request on
@@ -109,29 +109,56 @@ class ModelRunner:
         self.graph_bt_round = 32          # block-table width is rounded up to this many pages
         self._graphs: Dict[Any, Dict[str, Any]] = {}
         model.attach_cache(cache.bindings(), cache.shared_state())
-        self._has_rope_state = ROPE_STATE in cache.state.fields
+        #: rows of the positions a request may give per token (what the model's position encoding takes)
+        self.position_columns = model.position_columns
         #: per request slot, the token the sampler last kept on the device (see StepEntry.from_device)
         self.last_token: Optional[torch.Tensor] = None
         #: after a step: the request slot of each returned logits row, on the device (for Sampler.sample_async)
         self.logit_slots: Optional[torch.Tensor] = None
         self.last_h2d_bytes = 0           # size of the last step's metadata copy
+        #: set when a kernel reported an error: the text of it; the runner then refuses further steps
+        self.failed: Optional[str] = None
         if cache.state.tensors or self.device.type == "cuda":
             with torch.inference_mode(False):
                 self.last_token = torch.zeros(max(cache.state.num_slots, 1), dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ request life
-    def start_request(self, request_id: str, rope_delta: int = 0) -> None:
+    def start_request(self, request_id: str, prompt_positions: Optional[np.ndarray] = None,
+                      num_prompt_tokens: int = 0) -> None:
+        """The request takes a state slot. ``prompt_positions`` ([position_columns, num_prompt_tokens]) are
+        the positions that came with its prompt, if any: the model's position encodings turn them into
+        their rows of the request's state."""
+        if prompt_positions is not None:
+            self.check_positions(prompt_positions, num_prompt_tokens)
         rc = self.cache.begin(request_id)
-        if self._has_rope_state and self.cache.state.tensors:
-            self.cache.state.write(ROPE_STATE, rc.slot, [0, int(rope_delta)])
+        self._write_request_state(rc.slot, prompt_positions, num_prompt_tokens)
 
     def end_request(self, request_id: str) -> None:
         self.cache.finish(request_id)
 
-    def reset_request(self, request_id: str, rope_delta: int = 0) -> None:
+    def reset_request(self, request_id: str, prompt_positions: Optional[np.ndarray] = None,
+                      num_prompt_tokens: int = 0) -> None:
+        if prompt_positions is not None:
+            self.check_positions(prompt_positions, num_prompt_tokens)
         self.cache.reset(request_id)
-        if self._has_rope_state and self.cache.state.tensors:
-            self.cache.state.write(ROPE_STATE, self.cache.requests[request_id].slot, [0, int(rope_delta)])
+        self._write_request_state(self.cache.requests[request_id].slot, prompt_positions, num_prompt_tokens)
+
+    def _write_request_state(self, slot: int, prompt_positions: Optional[np.ndarray], num_prompt_tokens: int) -> None:
+        if not self.cache.state.tensors:
+            return
+        for name, row in self.model.request_state(prompt_positions, num_prompt_tokens).items():
+            if name in self.cache.state.tensors:
+                self.cache.state.write(name, slot, row)
+
+    def check_positions(self, positions: np.ndarray, n: int) -> None:
+        p = np.asarray(positions)
+        if p.shape != (self.position_columns, n):
+            raise ValueError(f"positions must be [{self.position_columns}, {n}], got {tuple(p.shape)}")
+
+    def positions_for(self, prompt_positions: Optional[np.ndarray], num_prompt_tokens: int, start: int, stop: int
+                      ) -> Optional[np.ndarray]:
+        """The ``StepEntry.positions`` of tokens [start, stop) of a request whose prompt came with positions."""
+        return self.model.positions_for(prompt_positions, num_prompt_tokens, start, stop)
 
     # ------------------------------------------------------------------ the step
     def _plan(self, entries: Sequence[StepEntry], bt_round: int = 1) -> Dict[str, Any]:
@@ -150,20 +177,15 @@ class ModelRunner:
         for e in entries:
             if not cache.has(e.request_id):
                 raise KeyError(f"request {e.request_id!r} was not started")
-        if not cache.can_reserve(list(zip(rids, q_lens))):
-            from ..cache.page_pool import OutOfPages
-            raise OutOfPages(f"the step needs more pages than are free ({cache.free_pages()} free)")
-        for r, n in zip(rids, q_lens):
-            cache.reserve(r, n)
 
+        # every entry is checked before a page is taken: a bad entry leaves the cache as it was
         cu_q = np.zeros(S + 1, dtype=np.int32)
         cu_q[1:] = np.cumsum(q_lens)
-        cursors = [cache.requests[r].cursor for r in rids]
-        kv_lens = [c + n for c, n in zip(cursors, q_lens)]
         token_ids = np.empty(T, dtype=np.int32)
         tok_src = np.full(T, -1, dtype=np.int32)
         tok_seq = np.empty(T, dtype=np.int32)
-        positions = np.zeros((3, T), dtype=np.int32)
+        C = self.position_columns
+        positions = np.zeros((C, T), dtype=np.int32)
         pos_mode = np.ones(S, dtype=np.int32)
         logit_rows: List[int] = []
         logit_slots: List[int] = []
@@ -184,8 +206,8 @@ class ModelRunner:
             tok_seq[a:b] = i
             if e.positions is not None:
                 p = np.asarray(e.positions)
-                if p.shape != (3, b - a):
-                    raise ValueError(f"request {e.request_id!r}: positions must be [3, {b - a}], got {p.shape}")
+                if p.shape != (C, b - a):
+                    raise ValueError(f"request {e.request_id!r}: positions must be [{C}, {b - a}], got {p.shape}")
                 positions[:, a:b] = p
                 pos_mode[i] = 0
             for w in e.want:
@@ -197,10 +219,18 @@ class ModelRunner:
                 rows = [int(r) for r in e.embed_rows]
                 if min(rows) < 0 or max(rows) >= b - a:
                     raise ValueError(f"request {e.request_id!r}: embedding row outside its tokens")
-                if e.embed_values.shape != (len(rows), self.hidden_size):
+                if e.embed_values is None or tuple(e.embed_values.shape) != (len(rows), self.hidden_size):
                     raise ValueError(f"request {e.request_id!r}: embed_values must be [{len(rows)}, {self.hidden_size}]")
                 ov_rows += [a + r for r in rows]
                 ov_vals.append(e.embed_values)
+
+        if not cache.can_reserve(list(zip(rids, q_lens))):
+            from ..cache.page_pool import OutOfPages
+            raise OutOfPages(f"the step needs more pages than are free ({cache.free_pages()} free)")
+        cursors = [cache.requests[r].cursor for r in rids]
+        kv_lens = [c + n for c, n in zip(cursors, q_lens)]
+        for r, n in zip(rids, q_lens):
+            cache.reserve(r, n)
         slots = np.asarray([cache.requests[r].slot for r in rids], dtype=np.int32)
         G = len(cache.groups)
         bts = [cache.block_table(g, rids, bt_round) for g in range(G)]
@@ -263,7 +293,7 @@ class ModelRunner:
         segs: List[Tuple[str, np.ndarray]] = [
             ("token_ids", token_ids.astype(np.int32)), ("cu_q", ar), ("seq_lens", cursors + 1), ("tok_seq", ar[:S]),
             ("state_slot", slots),
-            ("positions", np.zeros(3 * S, dtype=np.int32)), ("pos_mode", np.ones(S, dtype=np.int32)),
+            ("positions", np.zeros(self.position_columns * S, dtype=np.int32)), ("pos_mode", np.ones(S, dtype=np.int32)),
             ("logit_rows", ar[:S]), ("override_rows", np.zeros(0, dtype=np.int32)), ("decode_index", ar[:S]),
             ("token_src", np.where(from_dev, slots, -1).astype(np.int32)), ("logit_slots", slots),
         ]
@@ -295,7 +325,7 @@ class ModelRunner:
         ctx.T, ctx.S, ctx.num_logit_rows = T, S, plan["n_logit_rows"]
         ctx.token_ids, ctx.cu_q, ctx.seq_lens = seg("token_ids"), seg("cu_q"), seg("seq_lens")
         ctx.tok_seq, ctx.state_slot = seg("tok_seq"), seg("state_slot")
-        ctx.positions = seg("positions").view(3, T)
+        ctx.positions = seg("positions").view(self.position_columns, T)
         ctx.pos_mode, ctx.logit_rows = seg("pos_mode"), seg("logit_rows")
         ctx.block_tables = [seg(f"bt{g}").view(S, plan["bt_widths"][g]) for g in range(G)]
         ctx.slot_maps = [seg(f"sm{g}") for g in range(G)]
@@ -338,27 +368,42 @@ class ModelRunner:
         before they step again."""
         if self.use_graphs and self._graphable(entries):
             return self._graph_step(entries, copy_logits)
-        ctx = self.build_context(entries)
-        self.logit_slots = ctx.logit_slots
+        self._before_step()
         try:
+            ctx = self.build_context(entries)
+            self.logit_slots = ctx.logit_slots
             with ops.kernels().pinned_stream():
                 logits = self.model.forward(ctx)
         except Exception:
-            # the cache is in an undefined state for these requests; give the reservations back
-            for e in entries:
-                self.cache.requests[e.request_id].reserved = 0
+            self._rollback(entries)
             raise
         self._after_step(entries)
         return logits
 
+    def _rollback(self, entries: Sequence[StepEntry]) -> None:
+        """A step that failed gives back what it reserved: its requests hold the pages of their cursors again."""
+        for e in entries:
+            if self.cache.has(e.request_id):
+                self.cache.rollback(e.request_id)
+
+    def _before_step(self) -> None:
+        """What a kernel of an earlier step reported is raised here, before this step takes a page or moves a
+        cursor, and the runner refuses further steps: cursors on the device and on the host may disagree."""
+        if self.failed is not None:
+            raise RuntimeError(f"this runner stopped after a kernel error ({self.failed}); build a new one")
+        if self.check_device_errors and self.device.type == "cuda":
+            try:
+                ops.kernels().check_device_errors_async()
+            except Exception as e:
+                self.failed = str(e)
+                raise
+
     def _after_step(self, entries: Sequence[StepEntry]) -> None:
+        # no wait for the device here: what a kernel of this step reports is raised at the start of a later
+        # step (``_before_step``) or by the caller's own ``ops.kernels().check_device_errors()``, which waits
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
-        if self.check_device_errors:
-            # no wait for the device here: what a kernel of this step reports is raised a step or two later
-            # (or by the caller's own ``ops.kernels().check_device_errors()``, which waits)
-            ops.kernels().check_device_errors_async()
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _graphable(self, entries: Sequence[StepEntry]) -> bool:
@@ -380,7 +425,12 @@ class ModelRunner:
         """
         k = ops.kernels()
         round_to = self.graph_bt_round
-        plan = self._plan_decode(entries, bt_round=round_to)
+        self._before_step()
+        try:
+            plan = self._plan_decode(entries, bt_round=round_to)
+        except Exception:
+            self._rollback(entries)
+            raise
         key = (plan["S"], tuple(plan["bt_widths"]))
         slot = self._graphs.get(key)
         if slot is None:
@@ -425,8 +475,7 @@ class ModelRunner:
             slot["graph"].replay()
             k.launches += slot["launches"]
         except Exception:
-            for e in entries:
-                self.cache.requests[e.request_id].reserved = 0
+            self._rollback(entries)
             raise
         self._after_step(entries)
         o, n = slot["offs"]["logit_slots"]

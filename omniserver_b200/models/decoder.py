@@ -95,6 +95,35 @@ class DecoderModel:
                 out[n.name] = n
         return list(out.values())
 
+    # ------------------------------------------------------------------ positions (the encodings' own business)
+    @property
+    def position_columns(self) -> int:
+        """Rows of integers per token that requests may give with their prompts: what the model's position
+        encodings take (encodings that take some must agree on how many)."""
+        cols = {p.position_columns for p in self.positions.values() if p.position_columns}
+        if len(cols) > 1:
+            raise ValueError(f"the model's position encodings take different numbers of position columns: {sorted(cols)}")
+        return cols.pop() if cols else 0
+
+    def request_state(self, given: Optional[Any], num_prompt_tokens: int) -> Dict[str, Any]:
+        """State rows (field name -> values) of a request that takes its slot, from every position encoding."""
+        rows: Dict[str, Any] = {}
+        for pos in self.positions.values():
+            rows.update(pos.request_state(given if pos.position_columns else None, num_prompt_tokens))
+        return rows
+
+    def positions_for(self, given: Optional[Any], num_prompt_tokens: int, start: int, stop: int) -> Optional[Any]:
+        """The position columns to send with tokens [start, stop) of a request, or None (see PositionEncoding)."""
+        if given is None:
+            return None
+        out = None
+        for pos in self.positions.values():
+            if pos.position_columns:
+                p = pos.positions_for(given, num_prompt_tokens, start, stop)
+                if p is not None:
+                    out = p
+        return out
+
     def attach_cache(self, bindings: List[CacheBinding], shared_state: Dict[str, torch.Tensor]) -> None:
         if len(bindings) != len(self.spec.schedule):
             raise ValueError("one cache binding per schedule entry is needed")

@@ -53,19 +53,19 @@ class FusedLayerRun:
     def accepts(self, ctx: Any, x: torch.Tensor) -> bool:
         if ctx.decode_index is None:
             return False
-        tables = ctx.position_tables(self.position)
-        return ops.kernels().can_decode_layers_fused(x, self.H, self.nh, self.nkv, self.hd, self.I, ctx.n_decode,
-                                                     ctx.n_multi, tables.rot_dim)
+        rot = self.position.rotary(ctx.position_tables(self.position))
+        return rot is not None and ops.kernels().can_decode_layers_fused(
+            x, self.H, self.nh, self.nkv, self.hd, self.I, ctx.n_decode, ctx.n_multi, rot.rot_dim)
 
     def forward(self, ctx: Any, x: torch.Tensor, residual: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
         k = ops.kernels()
         if self._table is None:
             self._table = k.decode_layers_table(self._layers, x.device)
-        tables = ctx.position_tables(self.position)
+        rot = self.position.rotary(ctx.position_tables(self.position))
         g = self.group
         return k.decode_layers_fused(self._table, len(self._layers), x, residual, self.I, ctx.block_tables[g],
                                      ctx.slot_maps[g], ctx.cu_q, ctx.seq_lens, ctx.decode_index, self.nh, self.nkv,
-                                     self.hd, self.scale, ctx.max_kv_len, tables.cos, tables.sin, tables.rot_dim,
+                                     self.hd, self.scale, ctx.max_kv_len, rot.cos, rot.sin, rot.rot_dim,
                                      ctx.scratch)
 
 

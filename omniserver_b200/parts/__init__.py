@@ -1,7 +1,7 @@
 """Parts a decoder is put together from, chosen by name through registries."""
 
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, CacheBinding, FeedForward, KVCacheNeed,
-                   Mixer, Norm, ParamSpec, Part, PartSpec, PositionEncoding, StateNeed, register_block,
+                   Mixer, Norm, ParamSpec, Part, PartSpec, PositionEncoding, RotaryOperands, StateNeed, register_block,
                    register_feed_forward, register_mixer, register_norm, register_position_encoding)
 from . import blocks, embedding, feedforward, mixers, norms, positions  # noqa: F401  (fill the registries)
 from .blocks import PreNormBlock
@@ -10,4 +10,4 @@ from .feedforward import SwiGLU
 from .linear import Linear
 from .mixers import GQAAttention
 from .norms import RMSNorm
-from .positions import MRope, ROPE_STATE, RotaryTables
+from .positions import MRope, ROPE_STATE

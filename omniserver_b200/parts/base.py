@@ -130,15 +130,60 @@ class Norm(Part):
         return None
 
 
+@dataclass
+class RotaryOperands:
+    """What a rotary encoding hands a mixer for one step: cos and sin ``[T, rot_dim / 2]`` in fp32 for the
+    step's tokens. Element d < rot_dim / 2 of a head is rotated together with element d + rot_dim / 2;
+    elements from ``rot_dim`` on are left alone."""
+
+    cos: torch.Tensor
+    sin: torch.Tensor
+    rot_dim: int
+
+
 class PositionEncoding(Part):
-    """Turns positions into what a mixer applies to its queries and keys."""
+    """Turns positions into what a mixer applies to its queries and keys.
+
+    The engine knows nothing of an encoding's positions: it carries ``position_columns`` rows of integers
+    per token where a request gives them, writes the state rows ``request_state`` returns into the
+    request's slot, and asks ``positions_for`` which columns to send with a span of tokens.
+    """
+
+    #: rows of integers per token that a request may give with its prompt (0: the encoding takes none)
+    position_columns: int = 0
 
     def state_needs(self) -> List[StateNeed]:
         return []
 
+    def request_state(self, given: Optional[Any], num_prompt_tokens: int) -> Dict[str, Sequence[Any]]:
+        """When a request takes (or, after preemption, takes again) its state slot: the values of this
+        encoding's state fields for it, by field name. ``given``: the positions that came with the
+        prompt, ``[position_columns, num_prompt_tokens]``, or None. Fields not named start at zero."""
+        return {}
+
+    def positions_for(self, given: Optional[Any], num_prompt_tokens: int, start: int, stop: int) -> Optional[Any]:
+        """The columns ``[position_columns, stop - start]`` to send with tokens [start, stop) of a request
+        (its prompt followed by what it generated), or None where the encoding finds the positions
+        itself from its state. The default sends what was given and can say nothing past the prompt."""
+        if given is None or start >= num_prompt_tokens:
+            return None
+        if stop > num_prompt_tokens:
+            raise ValueError("this position encoding cannot continue given positions past the prompt")
+        return given[:, start:stop]
+
     @abc.abstractmethod
     def prepare(self, ctx: "Any", state: Dict[str, torch.Tensor]) -> Any:
         """Once per step: per-token tables shared by every layer that uses this encoding."""
+
+    def rotary(self, tables: Any) -> Optional[RotaryOperands]:
+        """The step's tables as a rotation of element pairs (d, d + rot_dim / 2), which the attention
+        kernels can apply themselves while they write the cache; None for any other encoding."""
+        return None
+
+    def apply(self, ctx: "Any", tables: Any, qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int
+              ) -> None:
+        """For an encoding that is no such rotation: changes the queries and keys in ``qkv``
+        ``[T, (num_heads + 2 num_kv_heads) * head_dim]`` in place. The default leaves them alone."""
 
     def finish_step(self, ctx: "Any", state: Dict[str, torch.Tensor]) -> None:
         """Once per step after all layers ran (advance cursors and the like)."""

@@ -53,21 +53,28 @@ class GQAAttention(Mixer):
                 "nh": self.nh, "nkv": self.nkv, "hd": self.hd, "scale": self.scale, "window": self.window,
                 "position": self.position}
 
+    def _rotary(self, ctx: Any):
+        """(the step's tables of this mixer's encoding, the same as rotary operands or None)."""
+        if self.position is None:
+            return None, None
+        tables = ctx.position_tables(self.position)
+        return tables, self.position.rotary(tables)
+
     def forward_prenorm(self, ctx: Any, x: torch.Tensor, residual, norm, binding: CacheBinding):
         # a decode step of a few single-token requests: norm, projections, rotary encoding, cache write and
         # attention as one persistent kernel, if the norm is one that the kernel computes
         k = ops.kernels()
         rms = norm.rms_operands()
-        tables = ctx.position_tables(self.position) if self.position is not None else None
-        if (rms is not None and tables is not None and binding.writes and ctx.decode_index is not None
+        _, rot = self._rotary(ctx)
+        if (rms is not None and rot is not None and binding.writes and ctx.decode_index is not None
                 and self.out.bias is None
                 and k.can_attn_decode_fused(x, rms[0], self.qkv.weight, self.qkv.bias, self.out.weight, binding.k_cache,
-                                            self.nh, self.nkv, self.hd, ctx.n_decode, ctx.n_multi, tables.rot_dim)):
+                                            self.nh, self.nkv, self.hd, ctx.n_decode, ctx.n_multi, rot.rot_dim)):
             g = binding.group
             return k.attn_decode_fused(x, residual, rms[0], rms[1], self.qkv.weight, self.qkv.bias, self.out.weight,
                                        binding.k_cache, binding.v_cache, ctx.block_tables[g], ctx.cu_q, ctx.seq_lens,
                                        ctx.decode_index, self.nh, self.nkv, self.hd, self.scale, self.window,
-                                       ctx.max_kv_len, (tables.cos, tables.sin, ctx.slot_maps[g], tables.rot_dim),
+                                       ctx.max_kv_len, (rot.cos, rot.sin, ctx.slot_maps[g], rot.rot_dim),
                                        ctx.scratch)
         fused = norm.fused_linear(x, residual, self.qkv, ctx.act_dtype)
         if fused is None:
@@ -77,22 +84,25 @@ class GQAAttention(Mixer):
 
     def _attend(self, ctx: Any, qkv: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
         k = ops.kernels()
-        tables = ctx.position_tables(self.position) if self.position is not None else None
+        tables, rot = self._rotary(ctx)
+        if self.position is not None and rot is None:
+            # an encoding that is no rotation of element pairs changes q and k itself, before the cache write
+            self.position.apply(ctx, tables, qkv, self.nh, self.nkv, self.hd)
         g = binding.group
-        rot = tables.rot_dim if tables else 0
+        rot_dim = rot.rot_dim if rot is not None else 0
         # A step of single-token requests lets the decode attention kernel rotate q and k and store
         # the new key and value itself; otherwise a kernel of its own does that for all tokens first.
-        fuse = (rot > 0 and binding.writes and ctx.decode_index is not None
+        fuse = (rot_dim > 0 and binding.writes and ctx.decode_index is not None
                 and k.can_fuse_rope_decode(qkv, binding.k_cache, self.nh, self.nkv, self.hd, ctx.n_decode, ctx.n_multi))
         if not fuse:
-            k.rope_kv_write(qkv, tables.cos if tables else None, tables.sin if tables else None,
+            k.rope_kv_write(qkv, rot.cos if rot_dim else None, rot.sin if rot_dim else None,
                             binding.k_cache, binding.v_cache, ctx.slot_maps[g] if binding.writes else None,
-                            self.nh, self.nkv, self.hd, rot)
+                            self.nh, self.nkv, self.hd, rot_dim)
         a = k.paged_attention(qkv, binding.k_cache, binding.v_cache, ctx.block_tables[g], ctx.cu_q, ctx.seq_lens,
                               ctx.tok_seq, self.nh, self.nkv, self.hd, self.scale, self.window,
                               ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype, decode_index=ctx.decode_index,
                               n_decode=ctx.n_decode, n_multi=ctx.n_multi, scratch=ctx.scratch,
-                              rope=(tables.cos, tables.sin, ctx.slot_maps[g], rot) if fuse else None)
+                              rope=(rot.cos, rot.sin, ctx.slot_maps[g], rot_dim) if fuse else None)
         return self.out(a, ctx.act_dtype)
 
 

@@ -12,22 +12,18 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import ops
-from .base import PositionEncoding, StateNeed, register_position_encoding
+from .base import PositionEncoding, RotaryOperands, StateNeed, register_position_encoding
 
 ROPE_STATE = "rope_cursor"  # per-request state row: (cursor, rope_delta), int32
 
 
-class RotaryTables:
-    """Per-step cos/sin [T, rot/2] fp32 shared by all layers using one encoding."""
-
-    def __init__(self, cos: torch.Tensor, sin: torch.Tensor, rot_dim: int):
-        self.cos, self.sin, self.rot_dim = cos, sin, rot_dim
-
-
 class MRope(PositionEncoding):
+    position_columns = 3    # (t, h, w)
+
     def __init__(self, head_dim: int, theta: float, sections: Sequence[int], rot_dim: Optional[int] = None):
         self.head_dim = int(head_dim)
         self.rot_dim = int(rot_dim) if rot_dim is not None else self.head_dim
@@ -58,11 +54,36 @@ class MRope(PositionEncoding):
             self._dev[k] = (self._inv_freq_cpu.to(device), self._axis_cpu.to(device))
         return self._dev[k]
 
-    def prepare(self, ctx: Any, state: Dict[str, torch.Tensor]) -> RotaryTables:
+    @staticmethod
+    def rope_delta(given: Optional[Any], num_prompt_tokens: int) -> int:
+        """The next text position is max + 1 (omniserve/model/positions.py:57): the offset between a
+        token's index in the request and its position once the prompt is over."""
+        return 0 if given is None else int(np.asarray(given).max()) + 1 - int(num_prompt_tokens)
+
+    def request_state(self, given: Optional[Any], num_prompt_tokens: int) -> Dict[str, Sequence[int]]:
+        return {ROPE_STATE: [0, self.rope_delta(given, num_prompt_tokens)]}
+
+    def positions_for(self, given: Optional[Any], num_prompt_tokens: int, start: int, stop: int) -> Optional[Any]:
+        # tokens after the prompt sit at index + rope_delta on all axes (omniserve/models/qwen2_vl.py:108-112);
+        # the kernel finds that from the state row, so columns are sent only for spans that touch the prompt
+        n = int(num_prompt_tokens)
+        if given is None or start >= n:
+            return None
+        given = np.asarray(given)
+        head = given[:, start:min(stop, n)]
+        if stop <= n:
+            return head
+        tail = np.arange(n, stop, dtype=np.int64) + self.rope_delta(given, n)
+        return np.concatenate([head, np.broadcast_to(tail, (3, stop - n))], axis=1)
+
+    def prepare(self, ctx: Any, state: Dict[str, torch.Tensor]) -> RotaryOperands:
         inv_freq, axis_of = self._consts(ctx.device)
         cos, sin = ops.kernels().rope_tables(ctx.positions, ctx.pos_mode, ctx.tok_seq, ctx.cu_q, ctx.state_slot,
                                              state[ROPE_STATE], inv_freq, axis_of)
-        return RotaryTables(cos, sin, self.rot_dim)
+        return RotaryOperands(cos, sin, self.rot_dim)
+
+    def rotary(self, tables: RotaryOperands) -> RotaryOperands:
+        return tables
 
     def finish_step(self, ctx: Any, state: Dict[str, torch.Tensor]) -> None:
         ops.kernels().advance_cursor(state[ROPE_STATE], ctx.state_slot, ctx.cu_q)

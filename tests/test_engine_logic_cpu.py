@@ -166,3 +166,110 @@ def test_overlapped_steps_and_stop_tokens(tmp_path, cpu_kernels):
         assert [outs[i] for i in ids] == want
         assert [s.output_token_ids for s in eng.sequences()] == want
         assert all(p == 0 for p in eng.runner.cache.pages_in_use())
+
+
+def test_a_bad_entry_leaves_the_cache_as_it_was(tmp_path, cpu_kernels):
+    """A step with one bad entry (a token id outside the vocabulary, a wanted place outside the entry, positions
+    of the wrong shape, an unknown request) raises before any page is taken: nothing stays reserved for the
+    other requests of the batch, no page is lost, and the same requests step normally afterwards."""
+    import numpy as np
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_a")
+    cfg, w = plain_model(d)
+    runner = _runner(d, 256)
+    toks = _requests(cfg.V, [30, 20], seed=4)
+    for rid in toks:
+        runner.start_request(rid)
+    runner.step([StepEntry("r0", toks["r0"][:10], []), StepEntry("r1", toks["r1"][:5], [])])
+    held = runner.cache.pages_in_use()
+    bad_steps = [
+        [StepEntry("r0", toks["r0"][10:28], [0]), StepEntry("r1", [3, cfg.V, 5], [0])],
+        [StepEntry("r0", toks["r0"][10:28], [0]), StepEntry("r1", [3, 4], [2])],
+        [StepEntry("r0", toks["r0"][10:28], [0]), StepEntry("r1", [3, 4], [0], positions=np.zeros((2, 2), dtype=np.int64))],
+    ]
+    for entries in bad_steps:
+        with pytest.raises(ValueError):
+            runner.step(entries)
+        runner.cache.check_invariants()
+        assert all(rc.reserved == 0 for rc in runner.cache.requests.values())
+        assert runner.cache.pages_in_use() == held
+    with pytest.raises(KeyError):
+        runner.step([StepEntry("r0", toks["r0"][10:28], [0]), StepEntry("nobody", [1], [0])])
+    assert all(rc.reserved == 0 for rc in runner.cache.requests.values()) and runner.cache.pages_in_use() == held
+    # the requests go on as if nothing had happened
+    a = runner.step([StepEntry("r0", toks["r0"][10:], list(range(20))), StepEntry("r1", toks["r1"][5:], list(range(15)))])
+    want0, want1 = pm.forward(cfg, w, torch.tensor(toks["r0"])), pm.forward(cfg, w, torch.tensor(toks["r1"]))
+    assert (a[:20] - want0[10:]).abs().max() < 5e-5 and (a[20:] - want1[5:]).abs().max() < 5e-5
+
+
+def test_a_step_that_fails_after_planning_gives_its_pages_back(tmp_path, cpu_kernels, monkeypatch):
+    """When the forward pass itself raises, the pages the step took beyond the requests' cursors go back to the
+    pool and nothing stays reserved."""
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_c")      # a window: tables with pages already given back
+    cfg, _ = plain_model(d)
+    runner = _runner(d, 512)
+    toks = _requests(cfg.V, [90, 40], seed=6)
+    for rid in toks:
+        runner.start_request(rid)
+    runner.step([StepEntry("r0", toks["r0"][:50], []), StepEntry("r1", toks["r1"][:7], [])])
+    held = runner.cache.pages_in_use()
+    tables = {r: [list(t) for t in rc.tables] for r, rc in runner.cache.requests.items()}
+
+    def boom(ctx):
+        raise RuntimeError("forward failed")
+    monkeypatch.setattr(runner.model, "forward", boom)
+    with pytest.raises(RuntimeError, match="forward failed"):
+        runner.step([StepEntry("r0", toks["r0"][50:], [0]), StepEntry("r1", toks["r1"][7:], [0])])
+    monkeypatch.undo()
+    runner.cache.check_invariants()
+    assert runner.cache.pages_in_use() == held
+    assert {r: [list(t) for t in rc.tables] for r, rc in runner.cache.requests.items()} == tables
+    assert all(rc.reserved == 0 for rc in runner.cache.requests.values())
+
+
+def test_token_ids_and_positions_are_checked_when_a_request_is_added(tmp_path, cpu_kernels):
+    import numpy as np
+    from omniserver_b200 import Request
+    d = make_model_dir(tmp_path, "tiny_a")
+    cfg, _ = plain_model(d)
+    eng = _engine(d, False)
+    with pytest.raises(ValueError, match="token id"):
+        eng.add_request(Request(prompt=[1, 2, cfg.V]))
+    with pytest.raises(ValueError, match="positions"):
+        eng.add_request(Request(prompt=[1, 2, 3], positions=np.zeros((2, 3), dtype=np.int64)))
+    with pytest.raises(ValueError, match="embed"):
+        eng.add_request(Request(prompt=[1, 2, 3], embed_rows=[1], embed_values=torch.zeros(1, cfg.H + 1)))
+    assert not eng.has_unfinished()
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_preemption_of_a_request_with_given_positions_and_embeddings(overlap, tmp_path, cpu_kernels):
+    """A request whose prompt carries positions (a 4 x 6 grid span) and given embedding rows is preempted while
+    it decodes (the pool is too small for both requests) and recomputed from its prompt plus the tokens it
+    had produced: the span's rows and positions are applied again, the generated tokens sit at index +
+    delta, and the tokens equal the plain model's greedy decoding."""
+    from omniserver_b200 import Request, SamplingParams
+    d = make_model_dir(tmp_path, "tiny_b")
+    cfg, w = plain_model(d)
+    L, start, n_new = 40, 6, 14
+    prompt = _requests(cfg.V, [L], seed=12)["r0"]
+    pos, delta = pm.image_span_positions(L, start, 1, 4, 6)
+    rows = list(range(start, start + 24))
+    vals = torch.randn(24, cfg.H, generator=torch.Generator().manual_seed(3))
+    other = _requests(cfg.V, [30], seed=13)["r0"]
+    want_img = pm.generate(cfg, w, prompt, n_new, prompt_pos=pos, rope_delta=delta, override_rows=torch.tensor(rows),
+                           override_vals=vals)
+    want_txt = pm.generate(cfg, w, other, n_new)
+    # 6 pages of 16 tokens: both prompts fit (3 + 2 pages), their decoding does not: 54 + 44 tokens need 7
+    eng = _engine(d, overlap, max_tokens=96, max_running=2, max_prefill_per_step=2, max_prefill_tokens=64)
+    a = eng.add_request(Request(prompt=other, sampling=SamplingParams(max_new_tokens=n_new)))
+    b = eng.add_request(Request(prompt=prompt, positions=pos.numpy(), embed_rows=rows, embed_values=vals,
+                                sampling=SamplingParams(max_new_tokens=n_new)))
+    outs = eng.run_until_complete()
+    seq_b = [s for s in eng.sequences() if s.request_id == b][0]
+    assert eng.counters["preemptions"] >= 1 and seq_b.num_preemptions >= 1
+    assert seq_b.num_output_tokens > 0
+    assert outs[b] == want_img and outs[a] == want_txt
+    eng.runner.cache.check_invariants()
+    assert all(p == 0 for p in eng.runner.cache.pages_in_use())

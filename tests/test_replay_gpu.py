@@ -126,12 +126,12 @@ def test_positions_and_embeddings_given_with_the_prompt(tmp_path):
         if pick:
             e["embeds"] = {"rows": [r - a for r in pick], "values": vals[[r - start for r in pick]].tolist()}
         steps.append({"step": i, "entries": [e], "end": []})
-    # then decoded tokens continue at cursor + rope_delta on all axes
+    # then decoded tokens continue at cursor + delta on all axes: the encoding derives that from the prompt's positions
     extra = requests_for(cfg.V, (6,), seed=6)["r0"]
     runner = runner_for(d, "float32", 128)
     from omniserver_b200.engine.step import StepEntry
     with torch.inference_mode():
-        runner.start_request("img", rope_delta=delta)
+        runner.start_request("img", pos.numpy(), L)
         outs = []
         for st in steps:
             e = st["entries"][0]

@@ -67,19 +67,49 @@ def _register():
             return torch.where(pick[:, None] == 0, y0, y1).to(x.dtype)
 
     class NoRotation(PositionEncoding):
-        """A position encoding that leaves queries and keys alone (rotary width 0)."""
+        """A position encoding that leaves queries and keys alone: it has no tables and is no rotation."""
 
         def __init__(self):
             pass
 
         def prepare(self, ctx, state):
-            from omniserver_b200.parts import RotaryTables
-            return RotaryTables(None, None, 0)
+            return None
+
+    class ShiftedIndexScale(PositionEncoding):
+        """Another encoding, nothing like a rotation: every query and key is scaled by 1 + slope * p, where p
+        is the token's position: one column given with the prompt, and index + shift for the tokens after it,
+        with the shift kept in a state field of the encoding's own."""
+
+        position_columns = 1
+
+        def __init__(self, slope):
+            self.slope = float(slope)
+
+        def state_needs(self):
+            return [StateNeed("toy_shift", (1,), torch.int32, shared=True)]
+
+        def request_state(self, given, num_prompt_tokens):
+            shift = 0 if given is None else int(given.max()) + 1 - num_prompt_tokens
+            return {"toy_shift": [shift]}
+
+        def prepare(self, ctx, state):
+            # tokens with given positions read their column; the others sit at their index in the request + shift
+            q_len = ctx.cu_q[1:] - ctx.cu_q[:-1]
+            first = (ctx.seq_lens - q_len)[ctx.tok_seq.long()]
+            offset = torch.arange(ctx.T, device=ctx.device, dtype=torch.int32) - ctx.cu_q[ctx.tok_seq.long()]
+            derived = first + offset + state["toy_shift"][ctx.state_slot.long(), 0][ctx.tok_seq.long()]
+            given = ctx.pos_mode[ctx.tok_seq.long()] == 0
+            return torch.where(given, ctx.positions[0], derived)
+
+        def apply(self, ctx, tables, qkv, num_heads, num_kv_heads, head_dim):
+            n = (num_heads + num_kv_heads) * head_dim
+            qkv[:, :n] = (qkv[:, :n].float() * (1.0 + self.slope * tables.float())[:, None]).to(qkv.dtype)
 
     if "toy_decay" not in pb.MIXERS:
         pb.register_mixer("toy_decay", DecayMixer)
         pb.register_feed_forward("toy_routed", RoutedFFN)
         pb.register_position_encoding("toy_none", NoRotation)
+        pb.register_position_encoding("toy_scale", ShiftedIndexScale)
 
 
 def _spec():
@@ -216,3 +246,76 @@ def test_toy_model_in_bfloat16_runs_on_the_fast_kernels():
     got = torch.cat([a, b])
     rel = ((got - want).norm() / want.norm()).item()
     assert rel < 3e-2, rel
+
+
+def test_a_position_encoding_with_one_column_and_state_of_its_own():
+    """An encoding defined in the test: one position column per token, a state field of its own that its
+    ``request_state`` fills from the prompt's positions, and a change of q and k that is no rotation. The
+    engine's files know none of this; it carries the column, writes the state row and asks the encoding
+    which columns to send with a span."""
+    import numpy as np
+    from omniserver_b200.cache import CacheManager
+    from omniserver_b200.engine.step import ModelRunner, StepEntry
+    from omniserver_b200.models import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
+    from omniserver_b200.parts.base import PartSpec
+    from omniserver_b200.weights import fill_random
+    _register()
+    slope = 0.01
+    norm = PartSpec("rmsnorm", {"dim": H, "eps": 1e-5})
+    scale = PartSpec("toy_scale", {"slope": slope})
+    attn = PartSpec("gqa_attention", {"hidden_size": H, "num_heads": NH, "num_kv_heads": NKV, "head_dim": HD})
+    swiglu = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I})
+    layers = [LayerSpec(f"layers.{i}.", attn, swiglu, norm, norm, position=scale) for i in range(2)]
+    spec = ModelSpec("ToyScaleForTests", V, H, layers, [ScheduleEntry(0), ScheduleEntry(1)], norm, tie_word_embeddings=True)
+    model = DecoderModel(spec)
+    assert model.position_columns == 1
+    fill_random(model, 11, torch.float32, DEV, std=0.08, norm_noise=0.1, store_dtype=torch.float32)
+    cache = CacheManager(model.entry_needs(), model.shared_state_needs(), 16, 16, 2, torch.float32, DEV)
+    assert "toy_shift" in cache.state.fields
+    runner = ModelRunner(model, cache, torch.float32, DEV)
+
+    n_prompt, n_more = 21, 5
+    toks = torch.randint(0, V, (n_prompt + n_more,), generator=torch.Generator().manual_seed(3)).tolist()
+    given = np.concatenate([np.arange(8), 8 + 3 * np.arange(n_prompt - 8)])[None, :]    # the prompt's own positions
+    shift = int(given.max()) + 1 - n_prompt
+    pos_all = torch.tensor(np.concatenate([given[0], np.arange(n_prompt, n_prompt + n_more) + shift]), dtype=torch.float32)
+
+    def plain():
+        f = lambda t: t.detach().float().cpu()
+        T = len(toks)
+        x = f(model.embed.weight)[torch.tensor(toks)]
+        res = None
+        for blk in model.blocks:
+            res = pm.add_residual(res, x)
+            y = pm.rms_norm(res, f(blk.mixer_norm.weight), 1e-5)
+            qkv = y @ f(blk.mixer.qkv.weight).T + f(blk.mixer.qkv.bias)
+            s = (1.0 + slope * pos_all)[:, None, None]
+            q = qkv[:, :NH * HD].view(T, NH, HD) * s
+            k = qkv[:, NH * HD:(NH + NKV) * HD].view(T, NKV, HD) * s
+            v = qkv[:, (NH + NKV) * HD:].view(T, NKV, HD)
+            x = pm.o_proj(pm.attention(q, k, v), f(blk.mixer.out.weight))
+            res = pm.add_residual(res, x)
+            y = pm.rms_norm(res, f(blk.ffn_norm.weight), 1e-5)
+            gu = f(blk.ffn.gate_up.weight)
+            x = pm.swiglu(y, gu[:I], gu[I:], f(blk.ffn.down.weight))
+        res = pm.add_residual(res, x)
+        return pm.lm_head(pm.rms_norm(res, f(model.final_norm.weight), 1e-5), f(model.embed.weight))
+
+    want = plain()
+    with torch.inference_mode():
+        runner.start_request("r", given, n_prompt)
+        assert int(cache.state.tensors["toy_shift"][cache.requests["r"].slot, 0]) == shift
+        outs, a = [], 0
+        for n in (7, 2, 9, 6):      # the last portion reaches 3 tokens past the prompt
+            b = a + n
+            outs.append(runner.step([StepEntry("r", toks[a:b], list(range(n)),
+                                               positions=runner.positions_for(given, n_prompt, a, b)
+                                               if b <= n_prompt else None if a >= n_prompt else
+                                               np.concatenate([given[:, a:], (np.arange(n_prompt, b) + shift)[None, :]], axis=1))]).cpu())
+            a = b
+        for t in toks[a:]:
+            outs.append(runner.step([StepEntry("r", [t], [0])]).cpu())
+        runner.end_request("r")
+    assert (torch.cat(outs) - want).abs().max() < 1e-4
+    with pytest.raises(ValueError):
+        runner.start_request("bad", np.zeros((3, 4), dtype=np.int64), 4)    # three columns where the model takes one
