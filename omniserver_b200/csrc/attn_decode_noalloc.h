@@ -33,6 +33,8 @@
 // Arguments as osb_paged_attn_bf16: out [T, nh*hd] bf16; q rows of q_row_stride elements;
 // caches [pages, kv_heads, page_size, head_dim] bf16; block_table [S, bt_stride]; cu_q [S+1];
 // seq_lens [S]; decode_index [S]; chunk a multiple of 64; nsplits = ceil(max kv length / chunk).
+// n_decode must be larger than every value in decode_index: the call sizes its regions of the array
+// from it and does not read decode_index on the host.
 // Returns 0, a cudaError value, or a status >= 10001.
 #pragma once
 #include <cuda_runtime.h>

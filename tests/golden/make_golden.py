@@ -57,7 +57,9 @@ def weights_checksum(sd):
     return torch.tensor([float(sd[k].double().abs().sum()) for k in sorted(sd)], dtype=torch.float64)
 
 
-def run_case(name, config, init, ids, grid, out_dir):
+def run_case(name, config, init, ids, grid, out_dir, decode_tail=0):
+    """``decode_tail``: the last so many ids are tokens after the prompt; their positions come from the
+    reference adapter's own decode rule (omniserve/models/qwen2_vl.py:108-112) at cache indices L .. L+tail-1."""
     from omniserve.model.positions import mrope_position_ids
     from omniserve.model.qwen2_llm import Qwen2Config, Qwen2LLM, load_from_hf
     from safetensors.torch import load_file, save_file
@@ -80,6 +82,8 @@ def run_case(name, config, init, ids, grid, out_dir):
     for layer in m.layers:
         layer.mlp.down_proj.forward_prequant = None  # skips the fp16 cast, never called
 
+    tail_ids = ids[ids.shape[0] - decode_tail:] if decode_tail else ids[:0]
+    ids = ids[:ids.shape[0] - decode_tail]
     L = ids.shape[0]
     override_rows = torch.zeros(0, dtype=torch.int32)
     override_vals = torch.zeros(0, config["hidden_size"])
@@ -93,6 +97,14 @@ def run_case(name, config, init, ids, grid, out_dir):
         override_rows = (ids == config["image_token_id"]).nonzero().flatten().to(torch.int32)
         g = torch.Generator().manual_seed(1234)
         override_vals = torch.randn(len(override_rows), config["hidden_size"], generator=g)
+    if decode_tail:
+        from omniserve.models.qwen2_vl import Qwen2VLAdapter
+        # the adapter's method reads nothing of the adapter: called unbound, one "slot" per decoded token
+        tail_pos = Qwen2VLAdapter.decode_positions(None, torch.arange(L, L + decode_tail),
+                                                   torch.full((decode_tail,), delta))       # [3, tail, 1]
+        pos = torch.cat([pos, tail_pos.reshape(3, 1, decode_tail)], dim=2)
+        ids = torch.cat([ids, tail_ids])
+        L = ids.shape[0]
     with torch.no_grad():
         emb = m.embed_tokens(ids[None]).clone()
         if len(override_rows):
@@ -128,6 +140,9 @@ def main():
     # B text only too (untied head, 1 kv head)
     ids_b2 = torch.randint(0, 989, (40,), generator=g)
     run_case("tiny_b_text", TINY_B, TINY_B_INIT, ids_b2, None, args.out)
+    # B with the image span, followed by 6 tokens placed by the reference's decode rule (cursor + rope_delta)
+    ids_b3 = torch.cat([ids_b, torch.randint(0, 989, (6,), generator=g)])
+    run_case("tiny_b_image_decode", TINY_B, TINY_B_INIT, ids_b3, (1, 8, 12), args.out, decode_tail=6)
 
 
 if __name__ == "__main__":

@@ -180,3 +180,56 @@ def test_full_width_many_live_requests_bfloat16():
             err = (lg - ref).abs().max().item()
             assert err < 5e-2 * max(1.0, ref.abs().max().item()), f"request {i} place {p}: {err}"
             assert ((lg - ref).norm() / ref.norm()).item() < 3e-2, f"request {i} place {p}"
+
+
+_PLAIN_ROWS = {}
+
+
+def _plain_rows(cfg, w, key, toks, rows):
+    """Plain logits of one request at the given rows, kept for the tests that share requests."""
+    if key not in _PLAIN_ROWS:
+        hid = pm.forward(cfg, w, torch.tensor(toks), return_hidden=True, rows=[rows[-1]])[1]
+        _PLAIN_ROWS[key] = {p: pm.lm_head(hid[p:p + 1], w["embed_tokens.weight"])[0] for p in rows}
+    return _PLAIN_ROWS[key]
+
+
+@pytest.mark.parametrize("n_req", [8, 16])
+def test_benchmarked_decode_steps_match_plain(n_req):
+    """The configuration that the benchmark times, with two layers: 8 and 16 requests with contexts of about
+    2,040 tokens decode together for 12 steps, so that every context crosses 2,048 tokens and a page's edge at
+    a step of its own. Default switches: CUDA graphs, the weight-streaming kernels for up to 8 rows and their
+    forms with two column tiles for 9 to 16 rows, the streaming decode attention with its splits merged in a
+    cluster or through scratch memory. Logits of every request at every decoded place against the plain model."""
+    from omniserver_b200 import EngineConfig, build_runner
+    from omniserver_b200.engine.step import StepEntry
+    n_dec = 12
+    g = torch.Generator().manual_seed(21)
+    lens = [2040 - 3 * i for i in range(16)][:n_req]       # 2040, 2037, ...: they cross 2,048 at different steps
+    toks = [torch.randint(0, CONFIG["vocab_size"], (n + n_dec,), generator=g).tolist() for n in [2040 - 3 * i for i in range(16)]][:n_req]
+    ec = EngineConfig(dtype="bfloat16", max_cache_tokens=n_req * 2112, max_requests=n_req + 2)
+    runner = build_runner(config=CONFIG, seed=2, engine_config=ec, init_std=0.03, norm_noise=0.1)
+    assert runner.use_graphs
+    cfg = pm.PlainConfig(CONFIG)
+    w = plain_weights(runner.model)
+    got = {i: [] for i in range(n_req)}
+    with torch.inference_mode():
+        for i in range(n_req):
+            runner.start_request(f"b{i}")
+            got[i].append(runner.step([StepEntry(f"b{i}", toks[i][:lens[i]], want=[lens[i] - 1])]).float().cpu()[0])
+        for d in range(n_dec):
+            lg = runner.step([StepEntry(f"b{i}", [toks[i][lens[i] + d]], want=[0]) for i in range(n_req)]).float().cpu()
+            for i in range(n_req):
+                got[i].append(lg[i])
+        from omniserver_b200 import ops
+        ops.kernels().check_device_errors()
+        for i in range(n_req):
+            runner.end_request(f"b{i}")
+    assert len(runner._graphs) >= 1 and all(p == 0 for p in runner.cache.pages_in_use())
+    for i in range(n_req):
+        rows = list(range(lens[i] - 1, lens[i] + n_dec))
+        want = _plain_rows(cfg, w, ("bench", i), toks[i], rows)
+        for k, p in enumerate(rows):
+            ref, lg = want[p], got[i][k]
+            err = (lg - ref).abs().max().item()
+            assert err < 5e-2 * max(1.0, ref.abs().max().item()), f"request {i} place {p}: {err}"
+            assert ((lg - ref).norm() / ref.norm()).item() < 3e-2, f"request {i} place {p}"

@@ -16,7 +16,8 @@ from plain import model as pm
 from tiny_configs import ALL
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-CASES = [("tiny_a_text", "tiny_a"), ("tiny_b_image", "tiny_b"), ("tiny_b_text", "tiny_b")]
+CASES = [("tiny_a_text", "tiny_a"), ("tiny_b_image", "tiny_b"), ("tiny_b_text", "tiny_b"),
+         ("tiny_b_image_decode", "tiny_b")]
 
 
 @pytest.mark.parametrize("case,cfg_name", CASES)
@@ -44,3 +45,15 @@ def test_image_span_positions_match_reference_positions():
     pos, delta = pm.image_span_positions(64, 10, 1, 4, 6)
     assert torch.equal(pos.int(), gold["positions"])
     assert delta == int(gold["rope_delta"][0]) == -18
+
+
+def test_positions_after_the_prompt_match_the_reference_decode_rule():
+    """The six tokens after the 64-token prompt of the golden case got their positions from the reference
+    adapter's decode rule (cache index + rope_delta on all axes); the plain implementation's extension of the
+    prompt's positions gives the same columns."""
+    gold = load_file(os.path.join(GOLDEN, "tiny_b_image_decode.safetensors"))
+    prompt_pos, delta = pm.image_span_positions(64, 10, 1, 4, 6)
+    assert delta == int(gold["rope_delta"][0])
+    assert gold["positions"].shape == (3, 70)
+    assert torch.equal(pm.extend_positions(prompt_pos, delta, 70).int(), gold["positions"])
+    assert torch.equal(gold["positions"][:, 64:], (torch.arange(64, 70) + delta).int().expand(3, 6))

@@ -5,14 +5,17 @@ out all device memory at start-up, a plug-in inside another process's allocator,
 allocator call is not allowed. ``osb_attn_decode_noalloc`` keeps the scratch memory of the split-key
 decode kernel in a fixed array inside the library instead of taking it from the caller. This test
 calls it twice in a row (the array keeps the first call's contents) and checks both results against
-the regular entry point, which gets its scratch from the caller. It runs last so that a failure
-here leaves every other test already run; it passes alone in a fresh process as well.
+the regular entry point, which gets its scratch from the caller, and against the plain fp32 attention
+of tests/plain/kernels.py, which shares nothing with either. It runs last so that a failure here
+leaves every other test already run; it passes alone in a fresh process as well.
 """
 
 import ctypes
 
 import pytest
 import torch
+
+from plain.kernels import PlainKernels
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -69,6 +72,53 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice(nh, nkv, hd, ps, win
         # same kernels, same split boundaries, same merge order: within the tolerance of the bf16 kernel tests
         assert torch.allclose(out.float(), want.float(), rtol=1.6e-2, atol=2e-3), f"call {trial}"
         assert torch.isfinite(out.float()).all()
+        # and the plain attention in fp32 on the CPU: a fault of the kernel itself would show here
+        cpu = [t.cpu() for t in (qkv, kc, vc, bt, cu_q, seq_lens, tok_seq)]
+        plain = PlainKernels().paged_attention(cpu[0].float(), cpu[1].float(), cpu[2].float(), cpu[3], cpu[4], cpu[5],
+                                               cpu[6], nh, nkv, hd, scale, window, 1, max_kv, torch.float32)
+        assert torch.allclose(out.float().cpu(), plain, rtol=1.6e-2, atol=4e-3), f"call {trial} against plain"
+
+
+def test_no_alloc_entry_point_with_one_split_uses_no_scratch():
+    """Short contexts: one split, nothing is merged, the array is not touched."""
+    from omniserver_b200 import ops
+    lib = ops.kernels().lib
+    nh, nkv, hd, ps = 8, 2, 64, 16
+    kv_lens = [5, 64, 33, 1]
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, didx = _case(kv_lens, nh, nkv, hd, ps, seed=4)
+    S = len(kv_lens)
+    out = torch.full((S, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.osb_attn_decode_noalloc(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kc), _ptr(vc), _ptr(bt), bt.shape[1],
+                                     _ptr(cu_q), _ptr(seq_lens), _ptr(didx), S, nh, nkv, hd, ps, kc.shape[0],
+                                     ctypes.c_float(hd ** -0.5), 0, S, 64, 1, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    cpu = [t.cpu() for t in (qkv, kc, vc, bt, cu_q, seq_lens, tok_seq)]
+    plain = PlainKernels().paged_attention(cpu[0].float(), cpu[1].float(), cpu[2].float(), cpu[3], cpu[4], cpu[5], cpu[6],
+                                           nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens), torch.float32)
+    assert torch.allclose(out.float().cpu(), plain, rtol=1.6e-2, atol=4e-3)
+
+
+def test_no_alloc_entry_point_refuses_bad_shapes():
+    """A chunk that is no multiple of 64, more splits than the kernel merges, a head size it has no form for:
+    a status, nothing launched, the output untouched."""
+    from omniserver_b200 import ops
+    lib = ops.kernels().lib
+    nh, nkv, hd, ps = 8, 2, 64, 16
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, didx = _case([300, 200], nh, nkv, hd, ps, seed=5)
+    out = torch.zeros(2, nh * hd, dtype=torch.bfloat16, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(hd_, chunk, nsplits):
+        return lib.osb_attn_decode_noalloc(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kc), _ptr(vc), _ptr(bt), bt.shape[1],
+                                           _ptr(cu_q), _ptr(seq_lens), _ptr(didx), 2, nh, nkv, hd_, ps, kc.shape[0],
+                                           ctypes.c_float(0.125), 0, 2, chunk, nsplits, stream)
+    assert call(hd, 100, 3) == 10002          # chunk % 64 != 0
+    assert call(hd, 64, 129) == 10002         # more than 128 splits
+    assert call(40, 64, 5) == 10003           # a head size that is no multiple of 16
+    torch.cuda.synchronize()
+    assert not out.any()
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
