@@ -1,19 +1,25 @@
 """Benchmark of the engine's headline metric: decoded tokens per second on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--model 2b|7b|72b] [--layers L]
+                    [--workload decode|mixed] [--profile] [--impl ours|reference]
 
 Default run: the Qwen2-VL-2B text decoder's layer sizes with random weights (seed 2), bfloat16,
 a batch of 8 requests each holding a 2,048-token context, pages of 16 tokens.  A "step" is one
 decode step of the whole batch.  It prints one JSON line:
 
 * ``value``: decoded tokens per second, timed with CUDA events around K steps of the step
-  function plus sampling (the device time of the steps including the gaps between kernels);
+  function plus sampling (the device time of the steps including the gaps between kernels): the
+  median of --trials such runs;
 * ``e2e``: the same through the Python entry point (LLMEngine.step): scheduler, host token ids in
   (pinned staging buffer, one host-to-device copy per step) and sampled ids out;
 * ``prefill``: one 2,048-token prompt through the step function; ``frac`` = flops / time / bf16 peak;
 * ``roofline``: bytes a decode step has to read (every weight once, the live requests' keys and
   values) / its time, against the measured copy bandwidth;
-* ``points``: decode at batch 1 and 64.
+* ``points``: decode at batch 1 and 64 (tokens/s, ms per step, fraction of the roofline), and for the 7B and
+  72B sizes of the same architecture: the 7B decode point and mixed continuous-batching run (64 requests,
+  prompts of 128 to 4,096 tokens, 256 new tokens, portions of 2,048), the 72B decode points and prefill;
+* ``roofline.kernels`` / ``prefill.kernels``: time, achieved rate and fraction per class of kernels (matrix
+  products, attention, ...) from events recorded inside real steps.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else 6.65 TB/s and 1.59 PFLOP/s.
 Weights (3 GB) and caches are far larger than the L2 (126 MB), so no flush is needed between steps.
@@ -130,168 +136,88 @@ def prefill_flops(cfg, layers, T):
 
 
 def run_ours(args):
+    """Our arm: the measurements of omniserver_b200.benchmark (the same code as ``python -m omniserver_b200.cli bench``)
+    put together into the one JSON line of the contract."""
     import torch
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
-    from omniserver_b200 import EngineConfig, LLMEngine, Request, SamplingParams, SchedulerConfig, build_runner, ops
-    from omniserver_b200.engine.step import StepEntry
-    from omniserver_b200.sampling import Sampler
-
-    hbm_peak, tf_peak, peak_src = peaks()
-    cfg = dict(MODEL_2B)
-    cfg["num_hidden_layers"] = args.layers
-    nums = model_numbers(cfg, args.layers)
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
-    g = torch.Generator().manual_seed(SEED)
-    max_batch = max(args.batch, 1 if args.no_points else 64)
-    ctx_total = CONTEXT + NEW_TOKENS
-    pool_tokens = max_batch * (-(-ctx_total // 64) * 64) + 4096
-    ec = EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=pool_tokens, max_requests=max_batch + 2,
-                      check_device_errors=False, cuda_graphs=not args.no_graphs)
-    t0 = time.time()
-    runner = build_runner(config=cfg, seed=SEED, engine_config=ec, random_on_device=True)
-    torch.cuda.synchronize()
-    build_s = time.time() - t0
-    K = ops.kernels()
-    sampler_k = K
-
-    def new_prompt(n):
-        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
-
-    # ------------------------------------------------------------------ prefill: one 2,048-token prompt
-    def prefill_once(rid):
-        runner.start_request(rid)
-        lg = runner.step([StepEntry(rid, new_prompt(CONTEXT), want=[CONTEXT - 1])])
-        return lg
-
-    with torch.inference_mode():
-        for i in range(0 if args.only == "decode" else 3):
-            prefill_once(f"pw{i}")
-            runner.end_request(f"pw{i}")
-        torch.cuda.synchronize()
-        times = []
-        for i in range(1 if args.only == "decode" else 5):
-            toks = new_prompt(CONTEXT)
-            torch.cuda.nvtx.range_push("timed_prefill")
-            runner.start_request(f"p{i}")
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            runner.step([StepEntry(f"p{i}", toks, want=[CONTEXT - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            torch.cuda.nvtx.range_pop()
-            times.append(e0.elapsed_time(e1))
-            runner.end_request(f"p{i}")
-        pre_ms = statistics.median(times)
-    pflops = prefill_flops(cfg, args.layers, CONTEXT)
-    prefill = {"value": round(CONTEXT / (pre_ms / 1e3), 1), "tokens": CONTEXT, "ms": round(pre_ms, 3),
-               "frac": round(pflops / (pre_ms / 1e3) / (tf_peak * 1e12), 4), "tflops": round(pflops / (pre_ms / 1e3) / 1e12, 1),
-               "peak_tflops": tf_peak, "of": peak_src}
-
-    # ------------------------------------------------------------------ decode through the step function
-    def decode_run(B, steps, warmup, sample_clocks=False):
-        """Decode steps through the step function, the way the engine drives it: the sampled tokens stay on
-        the device for the next step's embedding lookup and are read on the host one step later, so the
-        host's planning of step t+1 overlaps the device's work on step t. Every step copies its metadata
-        from pinned host memory and brings its tokens back to the host."""
-        rids = [f"d{B}_{i}" for i in range(B)]
-        sampler = Sampler(SEED)
-        with torch.inference_mode():
-            for r in rids:
-                runner.start_request(r)
-                lg = runner.step([StepEntry(r, new_prompt(CONTEXT), want=[CONTEXT - 1])], copy_logits=False)
-                sampler.sample_async(lg, None, runner.last_token, runner.logit_slots).result()
-            entries = [StepEntry(r, [0], want=[0], from_device=True) for r in rids]
-
-            def launch():
-                lg = runner.step(entries, copy_logits=False)
-                return sampler.sample_async(lg, None, runner.last_token, runner.logit_slots)
-
-            def run(n):
-                prev, got = None, 0
-                for _ in range(n):
-                    h = launch()
-                    if prev is not None:
-                        got += len(prev.result())
-                    prev = h
-                got += len(prev.result())
-                return got
-
-            run(warmup)
-            torch.cuda.synchronize()
-            clocks = ClockSampler() if sample_clocks else None
-            if clocks:
-                clocks.start()
-                time.sleep(0.3)
-            l0 = K.launches
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            torch.cuda.nvtx.range_push("timed_decode")
-            e0.record()
-            got = run(steps)
-            e1.record()
-            torch.cuda.synchronize()
-            torch.cuda.nvtx.range_pop()
-            assert got == steps * B
-            ms = e0.elapsed_time(e1) / steps
-            launches = K.launches - l0
-            ck = clocks.stop() if clocks else None
-            ctx_mid = CONTEXT + warmup + steps / 2
-            for r in rids:
-                runner.end_request(r)
-        return ms, launches, ck, ctx_mid
-
-    ms, launches, clocks, ctx_mid = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
-    value = args.batch / (ms / 1e3)
-    step_bytes = nums["weight_bytes"] + args.batch * ctx_mid * nums["kv_per_token"]
-    achieved = step_bytes / (ms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-                "frac": round(achieved / hbm_peak, 4), "bytes_per_step": int(step_bytes), "of": peak_src}
-
+    from omniserver_b200 import benchmark as bm
+    torch.cuda.set_device(0)
+    pk = bm.read_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+    model = args.model
+    big = model == "72b"
+    batches = (1, 8, 16) if big else (1, 8, 64)
+    batch = args.batch
+    points_on = not args.no_points and args.only == "all"
+    max_batch = max([batch] + (list(batches) if points_on else []))
+    new_tokens = 128 if big else NEW_TOKENS
+    b = bm.Bench(model, args.layers, max_batch, CONTEXT, new_tokens, args.page_size, pk, graphs=not args.no_graphs)
+    fast = args.only == "decode"
+    prefill = b.prefill(CONTEXT, trials=1 if fast else 5, warmup=0 if fast else 3)
+    main = b.decode(batch, args.steps, args.warmup, trials=1 if fast else args.trials, clocks=True)
     points = {}
-    if not args.no_points and args.only == "all":
-        for B in (1, 64):
-            pms, _, _, _ = decode_run(B, max(8, args.steps // 2), max(3, args.warmup // 2))
-            points[f"decode_b{B}"] = round(B / (pms / 1e3), 1)
-
-    # ------------------------------------------------------------------ end to end through LLMEngine
     e2e = None
-    with torch.inference_mode():
-        # all prompts enter in one step, so that every request decodes in every timed step
-        eng = LLMEngine(runner, SchedulerConfig(max_running=args.batch, max_prefill_per_step=args.batch,
-                                                max_prefill_tokens=CONTEXT * args.batch, max_seq_len=4096), seed=SEED)
-        n_new = args.warmup + args.steps + 1
-        for i in range(args.batch if args.only == "all" else 0):
-            eng.add_request(Request(prompt=new_prompt(CONTEXT),
-                                    sampling=SamplingParams(max_new_tokens=n_new, ignore_eos=True)))
-        while any(s.num_streamed < 1 + args.warmup for s in eng.sequences()):
-            eng.step()
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        n_steps = e2e_tokens = 0
-        while eng.has_unfinished():
-            e2e_tokens += sum(len(d.new_token_ids) for d in eng.step())     # tokens that reached the host
-            n_steps += 1
-        torch.cuda.synchronize()
-        e2e_s = max(time.perf_counter() - t1, 1e-9)
-    e2e = {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": runner.last_h2d_bytes,
-           "d2h_bytes_per_step": 4 * args.batch, "steps": n_steps, "tokens": e2e_tokens}
-
+    kernels = None
+    if points_on:
+        for B in batches:
+            if B != batch:
+                r = b.decode(B, max(8, args.steps // 2), max(3, args.warmup // 2), trials=args.trials)
+                points[f"decode_b{B}"] = round(r["tokens_per_s"], 1)
+                points[f"decode_b{B}_ms"] = round(r["ms_per_step"], 4)
+                points[f"decode_b{B}_frac"] = round(r["frac"], 4)
+    if not fast:
+        e2e = b.e2e_decode(batch, args.steps, args.warmup)
+        if args.profile or points_on:
+            kernels = b.profile(batch)
     line = {
-        "metric": "decode tokens/s (Qwen2-VL-2B text decoder, batch %d, 2048-token contexts)" % args.batch,
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights (seed 2)",
-        "config": {"model": "Qwen2-VL-2B text decoder (random weights)", "layers": args.layers,
-                   "layers_of_model": FULL_LAYERS, "hidden_size": 1536, "heads": 12, "kv_heads": 2, "head_dim": 128,
-                   "intermediate_size": 8960, "vocab_size": 151936, "tied_head": True, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "new_tokens": NEW_TOKENS, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-                   "l2": "inputs (3 GB of weights) larger than L2, no flush"},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
-        "points": points, "build_s": round(build_s, 1),
+        "metric": "decode tokens/s (Qwen2-VL-%s text decoder, batch %d, %d-token contexts)" % (model.upper(), batch, CONTEXT),
+        "value": round(main["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights (seed %d)" % b.seed,
+        "config": bm.config_of(b, batch), "clocks": main["clocks"], "e2e": e2e, "gpu_launches": main["launches"],
+        "trials_ms": main["trials_ms"], "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(main["achieved_gbs"], 1), "peak": pk[0], "unit": "GB/s",
+                     "frac": round(main["frac"], 4), "bytes_per_step": main["bytes_per_step"], "of": pk[2]},
+        "points": points, "build_s": round(b.build_s, 1),
     }
+    if kernels is not None:
+        line["roofline"]["kernels"] = kernels.get("decode")
+        line["prefill"]["kernels"] = kernels.get("prefill")
+    b.close()
+    # the other sizes of the architecture: the 7B mixed run and decode point, the 72B decode points and prefill
+    if points_on and model == "2b" and not args.no_other_sizes:
+        try:
+            b7 = bm.Bench("7b", None, 64, 4096, 320, args.page_size, pk, graphs=not args.no_graphs,
+                          pool_tokens=64 * 4416 + 4096, max_requests=64)
+            r = b7.decode(8, max(8, args.steps // 2), max(3, args.warmup // 2), trials=args.trials)
+            points.update({"7b_decode_b8": round(r["tokens_per_s"], 1), "7b_decode_b8_ms": round(r["ms_per_step"], 4),
+                           "7b_decode_b8_frac": round(r["frac"], 4)})
+            m = b7.mixed()
+            points.update({"7b_mixed_output_tok_s": m["output_tokens_per_s"], "7b_mixed_prefill_tok_s": m["prefill_tokens_per_s"],
+                           "7b_mixed_frac": m["roofline_frac"], "7b_mixed_wall_s": m["wall_s"]})
+            b7.close()
+        except Exception as e:      # a point that cannot be measured is left out, with the reason
+            points["7b_error"] = f"{type(e).__name__}: {str(e)[:160]}"
+        try:
+            need = bm.model_numbers(bm.MODELS["72b"])["stored_bytes"] + 16 * 2304 * bm.model_numbers(bm.MODELS["72b"])["kv_per_token"]
+            if bm.free_gpu_bytes() < need + (6 << 30):
+                raise MemoryError("%.0f GB free, the 72B sizes need %.0f GB" % (bm.free_gpu_bytes() / 1e9, need / 1e9))
+            b72 = bm.Bench("72b", None, 16, CONTEXT, 128, args.page_size, pk, graphs=not args.no_graphs)
+            for B in (1, 8, 16):
+                r = b72.decode(B, 8, 3, trials=1)
+                points.update({f"72b_decode_b{B}": round(r["tokens_per_s"], 1), f"72b_decode_b{B}_ms": round(r["ms_per_step"], 3),
+                               f"72b_decode_b{B}_frac": round(r["frac"], 4)})
+            p72 = b72.prefill(CONTEXT, trials=3, warmup=1)
+            points.update({"72b_prefill_tok_s": p72["value"], "72b_prefill_ms": p72["ms"], "72b_prefill_frac": p72["frac"]})
+            b72.close()
+        except Exception as e:
+            points["72b_error"] = f"{type(e).__name__}: {str(e)[:160]}"
+    if args.workload == "mixed":
+        bmx = bm.Bench(model, args.layers, 64, 4096, 320, args.page_size, pk, graphs=not args.no_graphs,
+                       pool_tokens=64 * 4416 + 4096, max_requests=64)
+        line["mixed"] = bmx.mixed()
+        bmx.close()
     print(json.dumps(line))
     return 0
 
@@ -549,7 +475,13 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--model", default="2b", choices=["2b", "7b", "72b"], help="layer sizes of the Qwen2-VL text decoder")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--trials", type=int, default=3, help="timed runs of --steps decode steps; the median is reported")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                    help="'mixed': also 64 requests, prompts of 128..4096 tokens, 256 new tokens, portions of 2,048")
+    ap.add_argument("--profile", action="store_true", help="per-kernel-class times inside real steps (no graphs)")
+    ap.add_argument("--no-other-sizes", action="store_true", help="skip the 7B and 72B points of the default run")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
@@ -559,6 +491,8 @@ def main():
     args = ap.parse_args()
     globals()["PAGE_SIZE"] = args.page_size
     if args.impl == "reference":
+        if args.layers is None:
+            args.layers = FULL_LAYERS
         return run_reference(args)
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % args.gpus)

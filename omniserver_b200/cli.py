@@ -6,6 +6,9 @@ benchmarks/compare/run_omniserve.py:44-61, omniserve/server.py:185-192).
     python -m omniserver_b200.cli generate --model DIR --prompt-file prompts.jsonl --temperature 0.8 --seed 1 --out out.json
     python -m omniserver_b200.cli random-model --config config.json --seed 0 --out DIR
     python -m omniserver_b200.cli replay --model DIR --dtype float32 --out LOGITS_DIR --max-tokens 4096 < steps.jsonl
+    python -m omniserver_b200.cli bench decode --model 2b --batch 8 --steps 64 --trials 3 [--profile]
+    python -m omniserver_b200.cli bench prefill --model 7b --tokens 2048
+    python -m omniserver_b200.cli bench mixed --model 7b --requests 64 --max-running 64
 
 Prompts are token ids: the tokenizer is outside the engine. ``--prompt-file`` holds one JSON list
 of ids per line.
@@ -94,6 +97,44 @@ def cmd_replay(args) -> int:
     return replay_main(argv)
 
 
+def cmd_bench(args) -> int:
+    """Throughput of random-weight models of the architecture's sizes (see omniserver_b200/benchmark.py); JSON out."""
+    import torch
+
+    from . import benchmark as bm
+    if not torch.cuda.is_available():
+        raise SystemExit("bench: no CUDA device is visible")
+    pk = bm.read_peaks(args.peaks) if args.peaks else (*bm.FALLBACK_PEAKS, "fallback")
+    if args.what == "mixed":
+        b = bm.Bench(args.model, args.layers, args.max_running, args.prompt_hi, args.max_new_tokens + 64, args.page_size, pk,
+                     graphs=not args.no_cuda_graph, pool_tokens=args.max_running * (args.prompt_hi + args.max_new_tokens + 64) + 4096,
+                     max_requests=args.max_running)
+        out = b.mixed(args.requests, args.prompt_lo, args.prompt_hi, args.max_new_tokens, args.chunk, args.max_running)
+    elif args.what == "prefill":
+        b = bm.Bench(args.model, args.layers, 1, args.tokens, 64, args.page_size, pk, graphs=not args.no_cuda_graph)
+        out = b.prefill(args.tokens, trials=args.trials)
+        if args.profile:
+            out["kernels"] = b.profile(1, prefill_tokens=args.tokens)["prefill"]
+    else:
+        b = bm.Bench(args.model, args.layers, args.batch, args.ctx, args.max_new_tokens, args.page_size, pk,
+                     graphs=not args.no_cuda_graph)
+        r = b.decode(args.batch, args.steps, args.warmup, trials=args.trials)
+        out = {"tokens_per_s": round(r["tokens_per_s"], 1), "ms_per_step": round(r["ms_per_step"], 4), "trials_ms": r["trials_ms"],
+               "bytes_per_step": r["bytes_per_step"], "achieved_gbs": round(r["achieved_gbs"], 1), "frac": round(r["frac"], 4),
+               "launches": r["launches"]}
+        if args.profile:
+            out["kernels"] = b.profile(args.batch)["decode"]
+    out["config"] = bm.config_of(b, args.batch if args.what == "decode" else (args.max_running if args.what == "mixed" else 1))
+    out["peaks"] = {"hbm_gbs": pk[0], "bf16_tflops": pk[1], "of": pk[2]}
+    text = json.dumps(out, indent=2 if args.out else None)
+    if args.out:
+        with open(args.out, "w") as f:
+            f.write(text)
+    else:
+        print(text)
+    return 0
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="omniserver_b200", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="command", required=True)
@@ -129,6 +170,29 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--std", type=float, default=0.02)
     r.add_argument("--norm-noise", type=float, default=0.0)
     r.set_defaults(fn=cmd_random_model)
+
+    b = sub.add_parser("bench", help="throughput with random weights: decode steps, a prompt, or a mixed run")
+    b.add_argument("what", choices=["decode", "prefill", "mixed"])
+    b.add_argument("--model", default="2b", choices=["2b", "7b", "72b"], help="layer sizes of the Qwen2-VL text decoder")
+    b.add_argument("--layers", type=int, default=None, help="fewer layers than the model has")
+    b.add_argument("--batch", type=int, default=8)
+    b.add_argument("--ctx", type=int, default=2048, help="tokens each request holds when decoding starts")
+    b.add_argument("--tokens", type=int, default=2048, help="prompt length of 'prefill'")
+    b.add_argument("--steps", type=int, default=64)
+    b.add_argument("--warmup", type=int, default=8)
+    b.add_argument("--trials", type=int, default=3)
+    b.add_argument("--requests", type=int, default=64)
+    b.add_argument("--max-running", type=int, default=64)
+    b.add_argument("--prompt-lo", type=int, default=128)
+    b.add_argument("--prompt-hi", type=int, default=4096)
+    b.add_argument("--chunk", type=int, default=2048, help="most prompt tokens per step of 'mixed'")
+    b.add_argument("--max-new-tokens", type=int, default=256)
+    b.add_argument("--page-size", type=int, default=16)
+    b.add_argument("--no-cuda-graph", action="store_true")
+    b.add_argument("--profile", action="store_true", help="time per class of kernels inside real steps")
+    b.add_argument("--peaks", default=None, help="a MEASURED_PEAKS.json (hbm_gbs, bf16_tflops) for the fractions")
+    b.add_argument("--out", type=str, default=None)
+    b.set_defaults(fn=cmd_bench)
 
     p = sub.add_parser("replay", help="feed token ids from stdin step by step and write logits (see bin/trace_run)")
     p.add_argument("--model", required=True)

@@ -21,7 +21,509 @@
 // and the merges (eight warps through shared memory; splits through distributed shared memory of a cluster,
 // or through scratch memory by the CTA that finishes last) are those of attn_decode_kernel in attn_mma.cu;
 // semantics as there (omniserve/model/qwen2_llm.py:96-112, omniserve/cache/kv_prealloc.py:138-142).
-#include "attn_decode_stream.cuh"
+#include <cooperative_groups.h>
+
+#include "mma_utils.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace attn_stream {
+constexpr int NW = 8;              // warps per CTA
+constexpr int NT = NW * 32;
+constexpr int BLK = 16;            // keys per block
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct FusedRope {
+  const float* cos_t;
+  const float* sin_t;
+  const int* slot_map;
+  int rot;
+};
+
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+  unsigned d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+// through the L2 only (the L1 is not asked to keep lines that are read once)
+__device__ __forceinline__ uint4 ld_cg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+
+// K and V of one block of 16 keys as this lane needs them: [half of the block: keys 8h + g][32-dim block Db]
+template <int NDB>
+struct KVRegs {
+  uint4 k[2][NDB], v[2][NDB];
+};
+
+
+// One (request, kv head, split of the keys): the whole CTA (eight warps). ``wait_for_q`` waits for the kernel in front
+// (programmatic dependent launch); nothing of this step's q, k, v is touched before it.
+template <int HD, bool CLUSTER, class WaitFn>
+__device__ __forceinline__ void attn_stream_unit(
+    WaitFn&& wait_for_q, int split_, int by_, int s_, int ny_, unsigned char* smem_raw, int* s_last_p,
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+    int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+    const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int log2ps, int num_pages,
+    float scale_log2, int window, int chunk, int nsplits, FusedRope fr) {
+  constexpr int NDB = HD / 32;     // 32-dim blocks
+  constexpr int stride = HD + 8;   // q rows in shared memory, bf16
+  constexpr int ostride = HD + 8;  // merge rows, fp32
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                     // [16][stride]
+  float* wml = reinterpret_cast<float*>(qs + 16 * stride);          // [NW][16][2], then the CTA's own [16][2]
+  float* cml = wml + NW * 16 * 2;
+  float* wo = cml + 16 * 2;                                         // [NW][16][ostride], then the CTA's own [16][ostride]
+  float* co = wo + NW * 16 * ostride;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int split = split_, s = s_;
+  const int grp = nh / nkv;
+  const int head_tiles = (grp + 7) >> 3;
+  const int kvh = by_ / head_tiles, ht = by_ - kvh * head_tiles;
+  const int q0 = cu_q[s];
+  if (cu_q[s + 1] - q0 != 1) return;
+  const int rows = min(8, grp - ht * 8);
+  const int head0 = kvh * grp + ht * 8;
+  const int kv_len = seq_lens[s];
+  const int p = kv_len - 1;
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  // The visible keys [lo, kv_len) of this request are cut into nsplits equal parts of whole 16-key blocks, from
+  // this request's own length: the splits stay balanced whatever the longest request of the batch is.
+  (void)chunk;
+  const int lo16 = (lo / BLK) * BLK;
+  const int per = ((kv_len - lo16 + nsplits - 1) / nsplits + BLK - 1) / BLK * BLK;
+  const int first_split = 0, last_split = (p - lo16) / per;
+  const bool active = split <= last_split;
+  if (!CLUSTER && !active) return;
+  const int k_begin = lo16 + split * per;
+  const int k_end = min(k_begin + per, kv_len);
+  const int nblk = active ? (k_end - k_begin + BLK - 1) / BLK : 0;
+  const int* bt = block_table + (size_t)s * bt_stride;
+  const int ps_mask = (1 << log2ps) - 1;
+  const size_t page_stride = ((size_t)nkv << log2ps) * HD;
+  const size_t head_off = ((size_t)kvh << log2ps) * HD;
+
+  // the pages of this lane's two keys (g and g + 8) of block b, or -1 (outside [lo, k_end), page given back)
+  auto pages_of = [&](int b) -> int2 {
+    int2 pg = make_int2(-1, -1);
+    const int key = k_begin + b * BLK + g;
+    if (b < nblk) {
+      if (key < k_end && key >= lo) pg.x = bt[key >> log2ps];
+      if (key + 8 < k_end && key + 8 >= lo) pg.y = bt[(key + 8) >> log2ps];
+      if (pg.x >= num_pages) pg.x = -1;
+      if (pg.y >= num_pages) pg.y = -1;
+    }
+    return pg;
+  };
+  // asks the L2 for block b (no registers held): the loads that follow later then come from the L2. Lanes c = 0, 1
+  // take the two 128-byte halves of key g's row, lanes c = 2, 3 those of key g + 8.
+  auto prefetch_block = [&](int b, int2 pg) {
+    const int page = (c >> 1) ? pg.y : pg.x;
+    if (page < 0 || (c & 1) * 64 >= HD) return;
+    const int key = k_begin + b * BLK + g + 8 * (c >> 1);
+    const size_t off = (size_t)page * page_stride + head_off + (size_t)(key & ps_mask) * HD + (c & 1) * 64;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + off));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + off));
+  };
+  // loads of block b: zeros for keys outside [lo, k_end) and for pages given back
+  auto load_block = [&](int b, int2 pg, KVRegs<NDB>& r) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int key = k_begin + b * BLK + h * 8 + g;
+      const int page = h ? pg.y : pg.x;
+      const size_t off = page >= 0 ? (size_t)page * page_stride + head_off + (size_t)(key & ps_mask) * HD + c * 8 : 0;
+#pragma unroll
+      for (int db = 0; db < NDB; ++db) {
+        r.k[h][db] = page >= 0 ? ld_cg16(kc + off + db * 32) : make_uint4(0u, 0u, 0u, 0u);
+        r.v[h][db] = page >= 0 ? ld_cg16(vc + off + db * 32) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+
+  // Everything read so far was written by the host before the step.
+  KVRegs<NDB> cur, nxt;
+  // In the fused rotary form no block depends on the kernel before this one: the new token's own key and value,
+  // which only the last split sees, do not come from the cache (its row there is stale until this kernel has
+  // stored it) but from shared memory, where this CTA puts them, and replace that row of the loaded block.
+  const bool early = fr.cos_t != nullptr;
+  bf16* ks = qs + 8 * stride;   // rows 8 and 9 of the q tile: heads are the N side, only rows 0-7 hold queries
+  bf16* vs = qs + 9 * stride;
+  // page ids of this warp's first four blocks in one round trip; then one block further every iteration
+  int2 pg1 = pages_of(warp + NW), pg2 = pages_of(warp + 2 * NW), pg3 = pages_of(warp + 3 * NW);
+  if (early) {
+    load_block(warp, pages_of(warp), cur);
+    prefetch_block(warp + NW, pg1);
+    prefetch_block(warp + 2 * NW, pg2);
+  }
+  wait_for_q();   // until here nothing of this step's q, k, v was touched
+  if (fr.cos_t != nullptr && split == last_split) {
+    const int slot = fr.slot_map[q0];
+    const int page = slot >> log2ps, off = slot & ps_mask;
+    const bool store = ht == 0 && page >= 0 && page < num_pages;   // one CTA of the kv head stores
+    const size_t dst = store ? ((((size_t)page * nkv + kvh) << log2ps) + off) * HD : 0;
+    bf16* kd = const_cast<bf16*>(kc) + dst;
+    bf16* vd = const_cast<bf16*>(vc) + dst;
+    const bf16* ksrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + kvh) * HD;
+    const bf16* vsrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + nkv + kvh) * HD;
+    const int half = fr.rot >> 1;
+    const float* cs = fr.cos_t + (size_t)q0 * half;
+    const float* sn = fr.sin_t + (size_t)q0 * half;
+    for (int d = tid; d < half; d += NT) {
+      const float x1 = __bfloat162float(ksrc[d]), x2 = __bfloat162float(ksrc[d + half]);
+      const bf16 a = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]), b = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
+      ks[d] = a;
+      ks[d + half] = b;
+      if (store) {
+        kd[d] = a;
+        kd[d + half] = b;
+      }
+    }
+    for (int d = fr.rot + tid; d < HD; d += NT) {
+      const bf16 a = ksrc[d];
+      ks[d] = a;
+      if (store) kd[d] = a;
+    }
+    for (int d = tid; d < HD; d += NT) {
+      const bf16 a = vsrc[d];
+      vs[d] = a;
+      if (store) vd[d] = a;
+    }
+  }
+  if (!early) {
+    load_block(warp, pages_of(warp), cur);
+    prefetch_block(warp + NW, pg1);
+    prefetch_block(warp + 2 * NW, pg2);
+  }
+
+  // the group's query rows into shared memory, rotated on the way in the fused rotary form
+  {
+    constexpr int cpr = HD >> 3;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    const bool rotate_here = fr.cos_t != nullptr && ((fr.rot >> 1) & 7) == 0;
+    if (rotate_here) {
+      const int half = fr.rot >> 1, hc = half >> 3;
+      const int per_row = hc + (cpr - 2 * hc);
+      const float* cs = fr.cos_t + (size_t)q0 * half;
+      const float* sn = fr.sin_t + (size_t)q0 * half;
+      for (int i = tid; i < 8 * per_row; i += NT) {
+        const int r = i / per_row, cc0 = i - r * per_row;
+        bf16* dst = qs + r * stride;
+        const bf16* src = q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * HD;
+        if (cc0 >= hc) {
+          const int cc = 2 * hc + (cc0 - hc);
+          *reinterpret_cast<uint4*>(dst + cc * 8) = r < rows ? *reinterpret_cast<const uint4*>(src + cc * 8) : zero4;
+          continue;
+        }
+        uint4 a = zero4, b = zero4;
+        if (r < rows) {
+          a = *reinterpret_cast<const uint4*>(src + cc0 * 8);
+          b = *reinterpret_cast<const uint4*>(src + half + cc0 * 8);
+          const float4 c0 = *reinterpret_cast<const float4*>(cs + cc0 * 8), c1 = *reinterpret_cast<const float4*>(cs + cc0 * 8 + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(sn + cc0 * 8), s1 = *reinterpret_cast<const float4*>(sn + cc0 * 8 + 4);
+          const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&a);
+          __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x1 = __bfloat1622float2(pa[e]), x2 = __bfloat1622float2(pb[e]);
+            pa[e] = __floats2bfloat162_rn(x1.x * cv[2 * e] - x2.x * sv[2 * e], x1.y * cv[2 * e + 1] - x2.y * sv[2 * e + 1]);
+            pb[e] = __floats2bfloat162_rn(x2.x * cv[2 * e] + x1.x * sv[2 * e], x2.y * cv[2 * e + 1] + x1.y * sv[2 * e + 1]);
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + cc0 * 8) = a;
+        *reinterpret_cast<uint4*>(dst + half + cc0 * 8) = b;
+      }
+    } else {
+      for (int i = tid; i < 8 * cpr; i += NT) {
+        const int r = i / cpr, cc = i - r * cpr;
+        uint4 v = zero4;
+        if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * HD + cc * 8);
+        *reinterpret_cast<uint4*>(qs + r * stride + cc * 8) = v;
+      }
+      if (fr.cos_t != nullptr) {  // a rotated span that is no multiple of 16: rotate in place
+        __syncthreads();
+        const int half = fr.rot >> 1;
+        const float* cs = fr.cos_t + (size_t)q0 * half;
+        const float* sn = fr.sin_t + (size_t)q0 * half;
+        for (int i = tid; i < rows * half; i += NT) {
+          const int r = i / half, d = i - r * half;
+          bf16* row = qs + r * stride;
+          const float x1 = __bfloat162float(row[d]), x2 = __bfloat162float(row[d + half]);
+          row[d] = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]);
+          row[d + half] = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // Heads are the N side of both products (at most 8 per kv head), keys and dims the M side:
+  //   S^T[16 keys x 8 heads]  = K[16 keys x dims] Q^T          (A = K straight from the loads, B = Q from smem)
+  //   O^T[16 dims x 8 heads] += V^T[16 dims x 16 keys] P^T      (A = V through movmatrix, B = P through movmatrix)
+  // Lane (g, c) owns heads 2c, 2c+1: of S^T the keys g and g + 8 of the block; of O^T, in row block (db, jj),
+  // the dims 32 db + 8 (g / 2) + 4 jj + g % 2 and that + 2.
+  float ot[NDB * 2][4];
+#pragma unroll
+  for (int i = 0; i < NDB * 2; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};  // per head 2c, 2c+1; l_run: this lane's keys only
+
+  for (int b = warp; b < nblk; b += NW) {
+    const int2 pg4 = pages_of(b + 4 * NW);  // used one iteration later
+    load_block(b + NW, pg1, nxt);          // in flight while this block is computed (zeros beyond the last block)
+    prefetch_block(b + 3 * NW, pg3);
+    pg1 = pg2;
+    pg2 = pg3;
+    pg3 = pg4;
+    if (fr.cos_t != nullptr && split == last_split && (p - k_begin) / BLK == b && g == ((p - k_begin) & 7)) {
+      // this lane holds the new token's row of the block: take it from shared memory
+      if (((p - k_begin) & 8) == 0) {
+#pragma unroll
+        for (int db = 0; db < NDB; ++db) {
+          cur.k[0][db] = *reinterpret_cast<const uint4*>(ks + db * 32 + c * 8);
+          cur.v[0][db] = *reinterpret_cast<const uint4*>(vs + db * 32 + c * 8);
+        }
+      } else {
+#pragma unroll
+        for (int db = 0; db < NDB; ++db) {
+          cur.k[1][db] = *reinterpret_cast<const uint4*>(ks + db * 32 + c * 8);
+          cur.v[1][db] = *reinterpret_cast<const uint4*>(vs + db * 32 + c * 8);
+        }
+      }
+    }
+    float st[4] = {0.0f, 0.0f, 0.0f, 0.0f}, su[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // two chains of dependent MMAs
+#pragma unroll
+    for (int db = 0; db < NDB; ++db) {
+      const uint4 qv = *reinterpret_cast<const uint4*>(qs + g * stride + db * 32 + c * 8);  // head g
+      const unsigned a0[4] = {cur.k[0][db].x, cur.k[1][db].x, cur.k[0][db].y, cur.k[1][db].y};
+      const unsigned a1[4] = {cur.k[0][db].z, cur.k[1][db].z, cur.k[0][db].w, cur.k[1][db].w};
+      mma_bf16_16816(st, a0, qv.x, qv.y);
+      mma_bf16_16816(su, a1, qv.z, qv.w);
+    }
+    // st[0], st[1]: key g, heads 2c, 2c+1; st[2], st[3]: key g + 8. Every head is the same query position: the
+    // mask depends on the key only.
+    const int kbase = k_begin + b * BLK;
+    const bool vis0 = kbase + g < k_end && kbase + g >= lo, vis1 = kbase + g + 8 < k_end && kbase + g + 8 >= lo;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      st[e] = vis0 ? (st[e] + su[e]) * scale_log2 : -INFINITY;
+      st[2 + e] = vis1 ? (st[2 + e] + su[2 + e]) * scale_log2 : -INFINITY;
+    }
+    float alpha[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {  // head 2c + e: maximum over the block's 16 keys (this lane's two, then the lanes g)
+      float v = fmaxf(st[e], st[2 + e]);
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+      // m_run is the exponent offset in use; it moves only when the maximum has grown by more than 2^8
+      const bool grow = v > m_run[e] + 8.0f || (m_run[e] == -INFINITY && v > -INFINITY);
+      alpha[e] = (grow && m_run[e] != -INFINITY) ? fast_exp2(m_run[e] - v) : 1.0f;
+      if (grow) m_run[e] = v;
+      const float off = m_run[e];
+      const float p0 = st[e] == -INFINITY ? 0.0f : fast_exp2(st[e] - off);
+      const float p1 = st[2 + e] == -INFINITY ? 0.0f : fast_exp2(st[2 + e] - off);
+      st[e] = p0;
+      st[2 + e] = p1;
+      l_run[e] = l_run[e] * alpha[e] + p0 + p1;
+    }
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+      for (int i = 0; i < NDB * 2; ++i) {
+        ot[i][0] *= alpha[0];
+        ot[i][1] *= alpha[1];
+        ot[i][2] *= alpha[0];
+        ot[i][3] *= alpha[1];
+      }
+    }
+    // P (keys x heads) transposed across the warp is the B operand: keys 2c, 2c+1 (and + 8) of head g
+    const unsigned pb0 = movmatrix_trans(pack_bf16(st[0], st[1]));
+    const unsigned pb1 = movmatrix_trans(pack_bf16(st[2], st[3]));
+#pragma unroll
+    for (int db = 0; db < NDB; ++db) {
+      const unsigned t00 = movmatrix_trans(cur.v[0][db].x), t01 = movmatrix_trans(cur.v[0][db].y);
+      const unsigned t02 = movmatrix_trans(cur.v[0][db].z), t03 = movmatrix_trans(cur.v[0][db].w);
+      const unsigned t10 = movmatrix_trans(cur.v[1][db].x), t11 = movmatrix_trans(cur.v[1][db].y);
+      const unsigned t12 = movmatrix_trans(cur.v[1][db].z), t13 = movmatrix_trans(cur.v[1][db].w);
+      const unsigned va0[4] = {t00, t01, t10, t11};  // rows g: piece 0, rows g + 8: piece 1; keys 0-7 | 8-15
+      const unsigned va1[4] = {t02, t03, t12, t13};
+      mma_bf16_16816(ot[db * 2], va0, pb0, pb1);
+      mma_bf16_16816(ot[db * 2 + 1], va1, pb0, pb1);
+    }
+    cur = nxt;
+  }
+  pdl_trigger();
+
+  // merge the warps (each saw different keys) in warp order through shared memory
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    float l = l_run[e];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    const int r = 2 * c + e;  // head
+    if (r < rows) {
+      if (g == 0) {
+        wml[(warp * 16 + r) * 2] = m_run[e];
+        wml[(warp * 16 + r) * 2 + 1] = l;
+      }
+#pragma unroll
+      for (int db = 0; db < NDB; ++db)
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int d = db * 32 + (g >> 1) * 8 + jj * 4 + (g & 1);
+          wo[(warp * 16 + r) * ostride + d] = ot[db * 2 + jj][e];
+          wo[(warp * 16 + r) * ostride + d + 2] = ot[db * 2 + jj][2 + e];
+        }
+    }
+  }
+  __syncthreads();
+  const bool direct = !CLUSTER && first_split == last_split;
+  const int drow = decode_index[s];
+  constexpr int hq = HD >> 2;
+  for (int idx = tid; idx < rows * hq; idx += NT) {
+    const int r = idx / hq, d = (idx - r * hq) * 4;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, wml[(w * 16 + r) * 2]);
+    float L = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float mw = wml[(w * 16 + r) * 2];
+      if (mw == -INFINITY) continue;
+      const float f = fast_exp2(mw - M);
+      const float4 v = *reinterpret_cast<const float4*>(wo + (w * 16 + r) * ostride + d);
+      L += wml[(w * 16 + r) * 2 + 1] * f;
+      acc.x += v.x * f;
+      acc.y += v.y * f;
+      acc.z += v.z * f;
+      acc.w += v.w * f;
+    }
+    const int head = head0 + r;
+    if (direct) {
+      const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+      bf16* op = out + ((size_t)q0 * nh + head) * HD + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    } else if (CLUSTER) {
+      *reinterpret_cast<float4*>(co + r * ostride + d) = acc;
+      if (d == 0) {
+        cml[r * 2] = M;
+        cml[r * 2 + 1] = L;
+      }
+    } else {
+      const size_t prow = ((size_t)drow * nh + head) * nsplits + split;
+      *reinterpret_cast<float4*>(part_o + prow * HD + d) = acc;
+      if (d == 0) {
+        part_ml[prow * 2] = M;
+        part_ml[prow * 2 + 1] = L;
+      }
+    }
+  }
+  if (direct) return;
+
+  if (CLUSTER) {
+    // the splits of one (request, kv head) are the CTAs of one cluster: every CTA merges a share of the
+    // output columns over all of them through distributed shared memory, in split order
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    for (int idx = tid * csize + crank; idx < rows * hq; idx += NT * csize) {
+      const int r = idx / hq, d = (idx - r * hq) * 4;
+      float ms[8], ls[8];
+      float4 vs4[8];
+      float M = -INFINITY;
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        if (cc < csize) {
+          const float* rml = cluster.map_shared_rank(cml, cc);
+          const float* rco = cluster.map_shared_rank(co, cc);
+          ms[cc] = rml[r * 2];
+          ls[cc] = rml[r * 2 + 1];
+          vs4[cc] = *reinterpret_cast<const float4*>(rco + r * ostride + d);
+          M = fmaxf(M, ms[cc]);
+        }
+      }
+      float L = 0.0f;
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        if (cc < csize && ms[cc] != -INFINITY) {
+          const float f = fast_exp2(ms[cc] - M);
+          L += ls[cc] * f;
+          acc.x += vs4[cc].x * f;
+          acc.y += vs4[cc].y * f;
+          acc.z += vs4[cc].z * f;
+          acc.w += vs4[cc].w * f;
+        }
+      }
+      const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+      bf16* op = out + ((size_t)q0 * nh + head0 + r) * HD + d;
+      *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    }
+    cluster.sync();  // nobody's shared memory goes away while another CTA still reads it
+    return;
+  }
+
+  // Without a cluster: the CTA that finishes last among this group's splits merges them, in split order, so
+  // the result does not depend on which CTA that is. The counter returns to zero.
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* cnt = counters + (size_t)drow * ny_ + by_;
+    const int prev = atomicAdd(cnt, 1);
+    *s_last_p = (prev == last_split - first_split);
+    if (*s_last_p) *cnt = 0;
+  }
+  __syncthreads();
+  if (!*s_last_p) return;
+  __threadfence();
+  const int nv = last_split - first_split + 1;
+  float* sml = wo;  // [rows][nv][2]
+  for (int idx = tid; idx < rows * nv; idx += NT) {
+    const int r = idx / nv, sp = idx - r * nv;
+    const size_t prow = ((size_t)drow * nh + head0 + r) * nsplits + first_split + sp;
+    sml[idx * 2] = __ldcg(part_ml + prow * 2);
+    sml[idx * 2 + 1] = __ldcg(part_ml + prow * 2 + 1);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rows * hq; idx += NT) {
+    const int r = idx / hq, d = (idx - r * hq) * 4;
+    const float* ml = sml + (size_t)r * nv * 2;
+    float M = -INFINITY;
+    for (int sp = 0; sp < nv; ++sp) M = fmaxf(M, ml[sp * 2]);
+    const float* po = part_o + (((size_t)drow * nh + head0 + r) * nsplits + first_split) * HD + d;
+    float L = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int sp0 = 0; sp0 < nv; sp0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (sp0 + u < nv) v[u] = __ldcg(reinterpret_cast<const float4*>(po + (size_t)(sp0 + u) * HD));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (sp0 + u < nv) {
+          const float ms = ml[(sp0 + u) * 2];
+          const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
+          L += ml[(sp0 + u) * 2 + 1] * f;
+          acc.x += v[u].x * f;
+          acc.y += v[u].y * f;
+          acc.z += v[u].z * f;
+          acc.w += v[u].w * f;
+        }
+      }
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    bf16* op = out + ((size_t)q0 * nh + head0 + r) * HD + d;
+    *reinterpret_cast<__nv_bfloat162*>(op) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  }
+}
+
+}  // namespace attn_stream
+
 
 namespace {
 using namespace attn_stream;
@@ -35,7 +537,7 @@ __global__ void __launch_bounds__(NT, 1) attn_decode_stream_kernel(
     float scale_log2, int window, int chunk, int nsplits, FusedRope fr) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_last;
-  attn_stream_unit<HD, CLUSTER, false>([] { pdl_wait(); }, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.y, smem_raw, &s_last, out, part_o,
+  attn_stream_unit<HD, CLUSTER>([] { pdl_wait(); }, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.y, smem_raw, &s_last, out, part_o,
                                        part_ml, q, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                        decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk,
                                        nsplits, fr);
@@ -69,12 +571,6 @@ int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_st
   return rc ? rc : osb_last_error();
 }
 }  // namespace
-
-#ifdef OSB_ATTN_TIMELINE
-OSB_API int osb_attn_stream_timeline(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_stream_timeline, sizeof(long long) * (size_t)n);
-}
-#endif
 
 // The decode part of osb_paged_attn_bf16 (same arguments, same meaning; requests bringing more than one
 // token are skipped) for head sizes 64 and 128 and page sizes that are powers of two; anything else is refused

@@ -254,15 +254,6 @@ struct FusedRope {
   int rot;
 };
 
-#ifdef OSB_ATTN_TIMELINE
-// Development aid (not compiled into the library): clock stamps of the CTAs of request 0, kv head 0.
-__device__ long long g_decode_timeline[16 * 16];
-#define DTL(i) do { if (blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && blockIdx.x < 16) \
-    g_decode_timeline[blockIdx.x * 16 + (i)] = clock64(); } while (0)
-#else
-#define DTL(i) do { } while (0)
-#endif
-
 // ------------------------------------------------------------------------------------------------
 // Decode: one token per request. grid = (splits, kv heads x head tiles, requests).
 template <int HD_MAX, int STAGES, bool CLUSTER>
@@ -279,7 +270,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   bf16* kvs = qs + 16 * stride;                  // STAGES x (K, V) x [TILE_N][stride]; later the warps' outputs
   const int tile_elems = TILE_N * stride;
 
-  DTL(0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, s = blockIdx.z;
   const int g = nh / nkv;
@@ -317,7 +307,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   };
   if (early) first_tiles();
   pdl_wait();
-  DTL(1);
   if (fr.cos_t != nullptr && split == last_split && ht == 0) {
     // the new token's key (rotated) and value go into their page before this CTA reads its tiles
     const int slot = fr.slot_map[q0];
@@ -343,7 +332,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     __syncthreads();
   }
 
-  DTL(2);
   // the group's query rows (plain loads: they must not become a copy group of their own). In the fused
   // rotary form a thread takes the 8 elements at d and their partners at d + rot/2 and rotates them on the
   // way, the cos/sin loads in flight together with the q loads: one round trip instead of two.
@@ -418,7 +406,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     }
     cp_async_wait<STAGES - 1>();
     __syncthreads();
-    if (t < 8) DTL(4 + t);
     const bf16* ks = kvs + st * 2 * tile_elems;
     const bf16* vs = ks + tile_elems;
     if (t == 0) {
@@ -532,7 +519,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
   cp_async_wait<0>();
   __syncthreads();
   pdl_trigger();
-  DTL(12);
 
   // merge the four warps (each saw different keys) in warp order: per-warp results of the valid rows
   // go to shared memory (row stride hd + 8 floats: the 64-bit stores of a half-warp hit distinct banks)
@@ -610,9 +596,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
     // The splits of one (request, kv head) are the CTAs of one cluster: every CTA merges a share of the
     // output columns over all of them through distributed shared memory, in split order.
     cg::cluster_group cluster = cg::this_cluster();
-    DTL(13);
     cluster.sync();
-    DTL(14);
     const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
     for (int idx = tid * csize + crank; idx < rows * hq; idx += NTHREADS * csize) {
       const int r = idx / hq, d = (idx - r * hq) * 4;
@@ -649,7 +633,6 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(
       *reinterpret_cast<__nv_bfloat162*>(op + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     }
     cluster.sync();  // nobody's shared memory goes away while another CTA still reads it
-    DTL(15);
     return;
   }
 
@@ -772,8 +755,6 @@ static inline int page_log2(int page_size) {
   while ((1 << l) < page_size) ++l;
   return l;
 }
-static int g_decode_stages = 0;  // 0: chosen from the grid size; 2 or 3: forced
-
 // out [T, nh*hd] bf16. Requests with one token run through the split-key decode kernel when
 // n_decode > 0 (decode_index[s] = index among them; part_o/part_ml/counters sized by
 // osb_attn_decode_scratch, counters all zero before the first use (the kernel leaves them zero);
@@ -783,11 +764,6 @@ static int g_decode_stages = 0;  // 0: chosen from the grid size; 2 or 3: forced
 // caller then skips the separate rotary/cache-write kernel); allowed only when n_multi == 0.
 // use_cluster: with 2..8 splits, launch the splits of a request as one thread-block cluster and merge
 // them through distributed shared memory (no scratch, no second phase through global memory).
-// Pipeline depth of the decode kernel for head sizes up to 128 (2 or 3 tiles in flight per CTA); 0 lets the
-// launch choose: three stages (two CTAs per SM) unless the grid is larger than two CTAs per SM can hold at
-// once, then two stages (three CTAs per SM).
-OSB_API void osb_attn_set_decode_stages(int stages) { g_decode_stages = (stages == 2 || stages == 3) ? stages : 0; }
-
 OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
                                 const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
                                 const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
@@ -836,7 +812,7 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
       if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 148;
     }
     const long long decode_ctas = (long long)nsplits * nkv * ((nh / nkv + 15) / 16) * n_decode;
-    const bool two_stages = g_decode_stages == 2 || (g_decode_stages == 0 && decode_ctas > 2LL * n_sms);
+    const bool two_stages = decode_ctas > 2LL * n_sms;
     if (hd <= 64)
       rc = launch_decode<64, 3>(o, part_o, part_ml, qq, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                 decode_index, counters, S, nh, nkv, hd, log2ps, num_pages, scale_log2, window, chunk,
@@ -858,11 +834,6 @@ OSB_API int osb_paged_attn_bf16(void* out, const void* q, int q_row_stride, cons
 }
 
 // ------------------------------------------------------------------------------------------------
-#ifdef OSB_ATTN_TIMELINE
-OSB_API int osb_attn_decode_timeline(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_decode_timeline, sizeof(long long) * (size_t)n);
-}
-#endif
 
 // Decode attention for callers that cannot allocate (declared in attn_decode_noalloc.h).
 //

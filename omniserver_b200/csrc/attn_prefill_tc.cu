@@ -30,14 +30,6 @@ constexpr int ATOM_BYTES = 128 * 128;  // 128 rows of 128 bytes
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
-#ifdef OSB_ATTN_TIMELINE
-// Development aid (not compiled into the library): clock stamps of block 0, 16 slots per key tile.
-__device__ long long g_timeline[64 * 16];
-#define TL(t, i) do { if (blockIdx.x == 0 && (t) < 64) g_timeline[(t) * 16 + (i)] = clock64(); } while (0)
-#else
-#define TL(t, i) do { } while (0)
-#endif
-
 template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -134,7 +126,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           *vabort = 1;
         } else {
           mbar_expect_tx(full, (uint32_t)(boxes * NA * box_rows * 128));
-          TL(t, which);  // 0: keys may be loaded, 1: values may be loaded
         }
       }
       __syncwarp();
@@ -169,7 +160,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           ok = false;
           break;
         }
-        TL(t, 2);
         fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -178,7 +168,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           umma_bf16(tmem + S_COL0 + (uint32_t)(st * TILE_N), ad, bd, idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
-        TL(t, 11);
       }
       if (!ok) {
         if (!*vabort) atomicExch(err, 112);
@@ -193,12 +182,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
       for (int t = 0; t < n_tiles && ok; ++t) {
         const int st = t % STAGES;
         const uint32_t ph = (uint32_t)(t / STAGES) & 1u;
-        TL(t, 4);
         if (!mbar_wait(&p_full[st], ph, vabort) || !mbar_wait(&v_full[st], ph, vabort)) {
           ok = false;
           break;
         }
-        TL(t, 3);
         fence_after();
         const uint32_t p_tmem = tmem + S_COL0 + (uint32_t)(st * TILE_N);
 #pragma unroll
@@ -207,7 +194,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           umma_bf16_ts(tmem + O_COL, p_tmem + (uint32_t)(ks * 8), bd, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&pv_done[st]);
-        TL(t, 9);
       }
       if (!ok) {
         if (!*vabort) atomicExch(err, 112);
@@ -231,14 +217,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
         break;
       }
       fence_after();
-      if (threadIdx.x == 64) TL(t, 5);  // S there
       const int key0 = (tile_begin + t) * TILE_N;
       const uint32_t s_addr = tmem + lane_addr + S_COL0 + (uint32_t)(st * TILE_N);
       uint32_t v[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + (uint32_t)(c * 32), v[c]);
       tmem_ld_wait();
-      if (threadIdx.x == 64) TL(t, 6);  // S in registers
       // a tile wholly below the diagonal and inside every row's window needs no mask
       const bool unmasked = key0 + TILE_N - 1 <= p_first && key0 >= lo_last;
       if (!unmasked) {
@@ -322,12 +306,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
           fence_async_smem();
         }
       }
-      if (threadIdx.x == 64) TL(t, 7);  // P computed
       tmem_st_wait();
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[st]);
-      if (threadIdx.x == 64) TL(t, 8);  // P handed over
     }
     // epilogue: O / l
     if (ok) {
@@ -386,11 +368,6 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 }
 }  // namespace
 
-#ifdef OSB_ATTN_TIMELINE
-OSB_API int osb_attn_timeline(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_timeline, sizeof(long long) * (size_t)n);
-}
-#endif
 
 // out [T, nh*hd] bf16; q = the first nh*hd columns of rows of q_row_stride elements; caches
 // [pages, nkv, page_size, hd] bf16. Head sizes 64 and 128, page sizes that are powers of two from 8

@@ -189,176 +189,6 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? (DEEP ? 5 : 8) : 1) g
 }
 
 
-// The same product with the add + RMSNorm that precedes it done by the GEMM itself: x = bf16(norm(res_in +
-// xb) * gamma) is never written. Every CTA needs all of x (a few rows), so every CTA recomputes the
-// norm for its own use from res_in and xb (fp32 statistics, the sum over K in an order fixed by the launch);
-// CTA 0 also writes the new residual stream to res_out, which must not alias res_in (other CTAs still read
-// it). 16 warps split K; a warp holds at most PB blocks of 64 k, all of them in registers, so there is no
-// main loop: weights are requested before the wait for the kernel before, activations after it.
-template <int NT, int PB>
-__global__ void __launch_bounds__(512, 1) gemm_skinny_prenorm_kernel(
-    void* __restrict__ y, int y_is_f32, const bf16* __restrict__ xb, const float* __restrict__ res_in,
-    float* __restrict__ res_out, const void* __restrict__ gamma, int gamma_is_f32, float eps,
-    const bf16* __restrict__ w, const void* __restrict__ bias, int bias_is_f32, int M, int N, int K) {
-  constexpr int WARPS = 16;
-  extern __shared__ float red[];                    // [WARPS][NT*8][16], then the sums of squares [WARPS][NT*8]
-  float* red_ss = red + WARPS * NT * 8 * 16;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, c = lane & 3;
-  int row_a = blockIdx.x * 16 + g, row_b = row_a + 8;
-  if (row_a >= N) row_a = -1;
-  if (row_b >= N) row_b = -1;
-  const bf16* wa = w + (size_t)(row_a < 0 ? 0 : row_a) * K;
-  const bf16* wb = w + (size_t)(row_b < 0 ? 0 : row_b) * K;
-  const int nblocks = (K + 63) >> 6;
-  const int b_begin = (warp * nblocks) / WARPS, b_end = ((warp + 1) * nblocks) / WARPS;
-  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-
-  uint4 wlo[PB][2], whi[PB][2];
-#pragma unroll
-  for (int u = 0; u < PB; ++u)
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int k = (b_begin + u) * 64 + c * 8 + hf * 32;
-      const bool ok = (b_begin + u) < b_end && k < K;
-      wlo[u][hf] = (ok && row_a >= 0) ? ld_stream16(wa + k) : zero4;
-      whi[u][hf] = (ok && row_b >= 0) ? ld_stream16(wb + k) : zero4;
-    }
-  pdl_wait();
-
-  float rr[PB][2][NT][8], gm[PB][2][8], ss[NT];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) ss[j] = 0.0f;
-#pragma unroll
-  for (int u = 0; u < PB; ++u)
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const int k = (b_begin + u) * 64 + c * 8 + hf * 32;
-      const bool ok = (b_begin + u) < b_end && k < K;
-      if (ok) {
-        if (gamma_is_f32) {
-          const float4 g0 = *reinterpret_cast<const float4*>((const float*)gamma + k);
-          const float4 g1 = *reinterpret_cast<const float4*>((const float*)gamma + k + 4);
-          gm[u][hf][0] = g0.x, gm[u][hf][1] = g0.y, gm[u][hf][2] = g0.z, gm[u][hf][3] = g0.w;
-          gm[u][hf][4] = g1.x, gm[u][hf][5] = g1.y, gm[u][hf][6] = g1.z, gm[u][hf][7] = g1.w;
-        } else {
-          const uint4 gv = *reinterpret_cast<const uint4*>((const bf16*)gamma + k);
-          const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(gp[e]);
-            gm[u][hf][2 * e] = f.x, gm[u][hf][2 * e + 1] = f.y;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) gm[u][hf][e] = 0.0f;
-      }
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        const int tok = j * 8 + g;
-        float* r = rr[u][hf][j];
-        if (ok && tok < M) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(xb + (size_t)tok * K + k);
-          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(xp[e]);
-            r[2 * e] = f.x, r[2 * e + 1] = f.y;
-          }
-          if (res_in) {
-            const float4 q0 = *reinterpret_cast<const float4*>(res_in + (size_t)tok * K + k);
-            const float4 q1 = *reinterpret_cast<const float4*>(res_in + (size_t)tok * K + k + 4);
-            r[0] = q0.x + r[0], r[1] = q0.y + r[1], r[2] = q0.z + r[2], r[3] = q0.w + r[3];
-            r[4] = q1.x + r[4], r[5] = q1.y + r[5], r[6] = q1.z + r[6], r[7] = q1.w + r[7];
-          }
-          if (blockIdx.x == 0) {
-            *reinterpret_cast<float4*>(res_out + (size_t)tok * K + k) = make_float4(r[0], r[1], r[2], r[3]);
-            *reinterpret_cast<float4*>(res_out + (size_t)tok * K + k + 4) = make_float4(r[4], r[5], r[6], r[7]);
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ss[j] += r[e] * r[e];
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) r[e] = 0.0f;
-        }
-      }
-    }
-  // sum of squares of a row: the 4 lanes of a token, then the warps in their order
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    float v = ss[j];
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    if (c == 0) red_ss[warp * (NT * 8) + j * 8 + g] = v;
-  }
-  __syncthreads();
-  float rstd[NT];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    float tot = 0.0f;
-#pragma unroll
-    for (int wi = 0; wi < WARPS; ++wi) tot += red_ss[wi * (NT * 8) + j * 8 + g];
-    rstd[j] = 1.0f / sqrtf(tot / (float)K + eps);
-  }
-
-  float acc[NT][4];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-#pragma unroll
-  for (int u = 0; u < PB; ++u)
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      const unsigned a0[4] = {wlo[u][hf].x, whi[u][hf].x, wlo[u][hf].y, whi[u][hf].y};
-      const unsigned a1[4] = {wlo[u][hf].z, whi[u][hf].z, wlo[u][hf].w, whi[u][hf].w};
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        unsigned xv[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float v0 = rr[u][hf][j][2 * e] * rstd[j] * gm[u][hf][2 * e];
-          const float v1 = rr[u][hf][j][2 * e + 1] * rstd[j] * gm[u][hf][2 * e + 1];
-          __nv_bfloat162 b = __floats2bfloat162_rn(v0, v1);
-          xv[e] = *reinterpret_cast<unsigned*>(&b);
-        }
-        mma_bf16_16816(acc[j], a0, xv[0], xv[1]);
-        mma_bf16_16816(acc[j], a1, xv[2], xv[3]);
-      }
-    }
-  pdl_trigger();
-  float* mine = red + (size_t)warp * (NT * 8 * 16);
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int t0 = j * 8 + c * 2;
-    mine[t0 * 16 + g] = acc[j][0];
-    mine[(t0 + 1) * 16 + g] = acc[j][1];
-    mine[t0 * 16 + g + 8] = acc[j][2];
-    mine[(t0 + 1) * 16 + g + 8] = acc[j][3];
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < M * 16; idx += WARPS * 32) {
-    const int tok = idx >> 4, r = idx & 15;
-    const int n = blockIdx.x * 16 + r;
-    if (n >= N) continue;
-    float v = 0.0f;
-#pragma unroll
-    for (int wi = 0; wi < WARPS; ++wi) v += red[(size_t)wi * (NT * 8 * 16) + tok * 16 + r];
-    if (bias) v += bias_is_f32 ? ((const float*)bias)[n] : __bfloat162float(((const bf16*)bias)[n]);
-    if (y_is_f32) ((float*)y)[(size_t)tok * N + n] = v;
-    else ((bf16*)y)[(size_t)tok * N + n] = __float2bfloat16_rn(v);
-  }
-}
-
-template <int NT, int PB>
-int launch_prenorm(void* y, int y_is_f32, const bf16* xb, const float* res_in, float* res_out, const void* gamma,
-                   int gamma_is_f32, float eps, const bf16* w, const void* bias, int bias_is_f32, int M, int N, int K,
-                   cudaStream_t stream) {
-  const size_t smem = (size_t)16 * NT * 8 * 17 * sizeof(float);
-  const int rc = osb_launch(gemm_skinny_prenorm_kernel<NT, PB>, dim3((N + 15) / 16), dim3(512), smem, stream, y, y_is_f32,
-                            xb, res_in, res_out, gamma, gamma_is_f32, eps, w, bias, bias_is_f32, M, N, K);
-  return rc ? rc : osb_last_error();
-}
-
 template <int WARPS, int NT, bool DEEP>
 int launch(void* y, int y_is_f32, const bf16* x, const bf16* w, const void* bias, int bias_is_f32, int M, int N,
            int K, int mode, int I, cudaStream_t stream) {
@@ -416,20 +246,4 @@ OSB_API int osb_gemm_skinny_bf16(void* y, int y_dtype, const void* x, const void
   }
   if (warps == 8) return launch_nt<8, true>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
   return launch_nt<16, true>(nt, y, yf, xx, ww, bias, bf, M, N, K, mode, I, stream);
-}
-
-// y[M,N] = bf16(rmsnorm(res_in + xb) * gamma) W^T (+ bias) with the new residual stream written to res_out
-// (fp32 [M,K]; must not alias res_in; res_in may be null: the stream starts at xb). M <= 16, K a multiple
-// of 8 and at most 2048 (a warp keeps its share of a row in registers): anything else is refused with
-// OSB_ERR_UNSUPPORTED and the caller runs the norm and the product as two kernels.
-OSB_API int osb_gemm_skinny_prenorm_bf16(void* y, int y_dtype, const void* xb, const float* res_in, float* res_out,
-                                         const void* gamma, int gamma_dtype, float eps, const void* w,
-                                         const void* bias, int bias_dtype, int M, int N, int K,
-                                         cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return OSB_OK;
-  if (M > 16 || K <= 0 || (K & 7) || K > 2048 || res_out == nullptr || res_out == res_in) return OSB_ERR_UNSUPPORTED;
-  const int yf = y_dtype == OSB_F32, bf = bias_dtype == OSB_F32, gf = gamma_dtype == OSB_F32;
-  const bf16 *xx = (const bf16*)xb, *ww = (const bf16*)w;
-  if (M <= 8) return launch_prenorm<1, 2>(y, yf, xx, res_in, res_out, gamma, gf, eps, ww, bias, bf, M, N, K, stream);
-  return launch_prenorm<2, 2>(y, yf, xx, res_in, res_out, gamma, gf, eps, ww, bias, bf, M, N, K, stream);
 }

@@ -68,7 +68,9 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ y,
     int y_is_f32, const void* __restrict__ bias, int bias_is_f32, int M, int N, int K, int I, int m_blocks,
-    int num_tiles, int* __restrict__ err) {
+    int num_tiles, int* __restrict__ err, uint32_t wait_limit, uint32_t tx_extra) {
+  // wait_limit: try_wait calls before a wait gives up; tx_extra: bytes that the producer announces beyond what it
+  // copies (0; the test of the give-up path passes 16, so that no stage ever becomes full)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;  // output columns per tile
@@ -114,14 +116,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
         for (int kb = 0; kb < num_kb; ++kb, ++issued) {
           const int s = issued % STAGES;
           const uint32_t ph = (uint32_t)(issued / STAGES) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, vabort)) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, vabort, wait_limit)) {
             if (!*vabort) atomicExch(err, 101);
             *vabort = 1;
             break;
           }
           unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
           unsigned char* b_dst = a_dst + A_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES + tx_extra);
           tma_load_2d(a_dst, &map_a, &full_bar[s], kb * BK, m0);
           if (EPI == EPI_SWIGLU) {
             tma_load_2d(b_dst, &map_b, &full_bar[s], kb * BK, n0);                    // gate rows
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
         for (int i = max(0, issued - STAGES); i < issued; ++i) {
           const int s = i % STAGES;
           const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-          for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(&full_bar[s], ph); ++w) {
+          for (uint32_t w = 0; w < wait_limit && !mbar_try_wait(&full_bar[s], ph); ++w) {
           }
         }
       }
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int buf = local & 1;
         const uint32_t aph = (uint32_t)(local >> 1) & 1u;
-        if (!mbar_wait(&acc_empty[buf], aph ^ 1u, vabort)) {  // the epilogue has drained this accumulator
+        if (!mbar_wait(&acc_empty[buf], aph ^ 1u, vabort, wait_limit)) {  // the epilogue has drained this accumulator
           if (!*vabort) atomicExch(err, 104);
           *vabort = 1;
           ok = false;
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
         for (int kb = 0; kb < num_kb; ++kb, ++consumed) {
           const int s = consumed % STAGES;
           const uint32_t ph = (uint32_t)(consumed / STAGES) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, vabort)) {
+          if (!mbar_wait(&full_bar[s], ph, vabort, wait_limit)) {
             if (!*vabort) atomicExch(err, 102);
             *vabort = 1;
             ok = false;
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
         }
         __syncwarp();
       }
-      bool ok = mbar_wait(&acc_full[buf], aph, vabort);
+      bool ok = mbar_wait(&acc_full[buf], aph, vabort, wait_limit);
       if (!ok && lane == 0) {
         if (!*vabort) atomicExch(err, 103);
         *vabort = 1;
@@ -277,7 +279,7 @@ int sm_count() {
 
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* y, int yf, const void* bias, int bf, int M, int N, int K,
-           int I, int* err, cudaStream_t stream) {
+           int I, int* err, uint32_t wait_limit, uint32_t tx_extra, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
   auto k = gemm_tcgen05_kernel<BN, STAGES, EPI>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -287,7 +289,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* y, int yf, const 
   const int m_blocks = (M + BM - 1) / BM;
   const int num_tiles = m_blocks * ((out_cols + cols_per_tile - 1) / cols_per_tile);
   const int ctas = num_tiles < sm_count() ? num_tiles : sm_count();
-  k<<<ctas, NUM_THREADS, smem, stream>>>(ma, mb, y, yf, bias, bf, M, N, K, I, m_blocks, num_tiles, err);
+  k<<<ctas, NUM_THREADS, smem, stream>>>(ma, mb, y, yf, bias, bf, M, N, K, I, m_blocks, num_tiles, err, wait_limit, tx_extra);
   return osb_last_error();
 }
 
@@ -301,10 +303,14 @@ static inline long long wave_cost(int M, int out_cols, int cols_per_tile, int wi
 
 // mode 0: y[M,N] (+bias), y bf16 or fp32. mode 1 (SwiGLU): w is [2I, K], N = 2I, y [M, I] bf16, no bias.
 // Needs K % 8 == 0 and 16-byte aligned x and w (TMA); refuses other shapes with OSB_ERR_UNSUPPORTED.
-// *err receives 101..103 if a wait inside the kernel ran out (the kernel then returns early).
-OSB_API int osb_gemm_tcgen05_bf16(void* y, int y_dtype, const void* x, const void* w, const void* bias, int bias_dtype,
-                                  int M, int N, int K, int mode, int* err, cudaStream_t stream) {
+// *err receives 101..104 if a wait inside the kernel ran out (the kernel then returns early).
+// wait_limit / tx_extra: 0 / 0 but in the test of the give-up path: so many polls per wait; so many bytes announced
+// to a stage's barrier beyond those copied, which keeps every stage from ever becoming full.
+OSB_API int osb_gemm_tcgen05_bf16_ex(void* y, int y_dtype, const void* x, const void* w, const void* bias, int bias_dtype,
+                                     int M, int N, int K, int mode, int* err, unsigned wait_limit, unsigned tx_extra,
+                                     cudaStream_t stream) {
   if (M <= 0 || N <= 0) return OSB_OK;
+  if (wait_limit == 0) wait_limit = WAIT_LIMIT;
   if (K <= 0 || (K & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return OSB_ERR_UNSUPPORTED;
   const int yf = y_dtype == OSB_F32, bf = bias_dtype == OSB_F32;
   CUtensorMap ma, mb;
@@ -317,11 +323,11 @@ OSB_API int osb_gemm_tcgen05_bf16(void* y, int y_dtype, const void* x, const voi
     if (wave_cost(M, I, 128, 2) <= wave_cost(M, I, 64, 1)) {  // cost in units of 128 B-tile rows
       rc = make_map(&mb, w, N, K, 128);
       if (rc) return rc;
-      return launch<256, 4, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, I, err, stream);
+      return launch<256, 4, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, I, err, wait_limit, tx_extra, stream);
     }
     rc = make_map(&mb, w, N, K, 64);
     if (rc) return rc;
-    return launch<128, 6, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, I, err, stream);
+    return launch<128, 6, EPI_SWIGLU>(ma, mb, y, 0, nullptr, 0, M, N, K, I, err, wait_limit, tx_extra, stream);
   }
   if (mode != 0) return OSB_ERR_BAD_SHAPE;
   // tile width: the one whose full waves over the SMs cost least; wider wins ties (less operand traffic)
@@ -329,14 +335,19 @@ OSB_API int osb_gemm_tcgen05_bf16(void* y, int y_dtype, const void* x, const voi
   if (c256 <= c192 && c256 <= c128) {
     rc = make_map(&mb, w, N, K, 256);
     if (rc) return rc;
-    return launch<256, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
+    return launch<256, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, wait_limit, tx_extra, stream);
   }
   if (c192 <= c128) {
     rc = make_map(&mb, w, N, K, 192);
     if (rc) return rc;
-    return launch<192, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
+    return launch<192, 4, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, wait_limit, tx_extra, stream);
   }
   rc = make_map(&mb, w, N, K, 128);
   if (rc) return rc;
-  return launch<128, 6, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, stream);
+  return launch<128, 6, EPI_PLAIN>(ma, mb, y, yf, bias, bf, M, N, K, 0, err, wait_limit, tx_extra, stream);
+}
+
+OSB_API int osb_gemm_tcgen05_bf16(void* y, int y_dtype, const void* x, const void* w, const void* bias, int bias_dtype,
+                                  int M, int N, int K, int mode, int* err, cudaStream_t stream) {
+  return osb_gemm_tcgen05_bf16_ex(y, y_dtype, x, w, bias, bias_dtype, M, N, K, mode, err, 0u, 0u, stream);
 }

@@ -272,9 +272,12 @@ class LLMEngine:
         outs = self.run_until_complete()
         return [outs.get(i, []) for i in ids]
 
-    def stats(self) -> Dict[str, int]:
+    def stats(self) -> Dict[str, object]:
         c = dict(self.counters)
         c["pages_in_use"] = sum(self.runner.cache.pages_in_use())
         c["running"] = len(self.scheduler.running)
         c["waiting"] = len(self.scheduler.waiting)
+        if self.runner.device.type == "cuda":
+            # launches by kernel entry point since the process began: which kernels the steps have been taking
+            c["kernel_launches"] = dict(ops.kernels().counts)
         return c

@@ -11,6 +11,7 @@ the tokens it is given and returns fp32 logits at the wanted places.
 
 from __future__ import annotations
 
+import collections
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -107,7 +108,11 @@ class ModelRunner:
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self.graph_max_batch = 256
         self.graph_bt_round = 32          # block-table width is rounded up to this many pages
-        self._graphs: Dict[Any, Dict[str, Any]] = {}
+        #: most graphs kept; the one used longest ago goes when another is needed. All graphs allocate from one
+        #: memory pool (they replay one after the other on one stream), so their activations share memory.
+        self.graph_max_count = 32
+        self._graphs: "collections.OrderedDict[Any, Dict[str, Any]]" = collections.OrderedDict()
+        self._graph_pool = None
         model.attach_cache(cache.bindings(), cache.shared_state())
         #: rows of the positions a request may give per token (what the model's position encoding takes)
         self.position_columns = model.position_columns
@@ -433,7 +438,12 @@ class ModelRunner:
             raise
         key = (plan["S"], tuple(plan["bt_widths"]))
         slot = self._graphs.get(key)
-        if slot is None:
+        if slot is not None:
+            self._graphs.move_to_end(key)
+        else:
+            if len(self._graphs) >= max(1, self.graph_max_count):
+                torch.cuda.synchronize()             # the graph that goes may still be running
+                self._graphs.popitem(last=False)
             offs, total = self._layout(plan["segs"])
             with torch.inference_mode(False):
                 # two staging buffers in turn: the host may fill one while the copy out of the other waits
@@ -467,7 +477,9 @@ class ModelRunner:
                 ctx.advance_state = True
                 g = torch.cuda.CUDAGraph()
                 l0 = k.launches
-                with torch.cuda.graph(g):
+                if self._graph_pool is None:
+                    self._graph_pool = torch.cuda.graph_pool_handle()
+                with torch.cuda.graph(g, pool=self._graph_pool):
                     slot["logits"] = self.model.forward(ctx)
                 slot["launches"] = k.launches - l0
                 slot["graph"] = g

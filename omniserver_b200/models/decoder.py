@@ -15,7 +15,6 @@ import torch
 from ..parts import base as pb
 from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, CacheBinding, KVCacheNeed, ParamSpec, Part, StateNeed
 from ..parts.embedding import LMHead, TokenEmbedding
-from .layer_run import find_runs
 from .spec import ModelSpec
 
 
@@ -57,7 +56,6 @@ class DecoderModel:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which owns none")
         self.bindings: List[CacheBinding] = []
         self.shared_state: Dict[str, torch.Tensor] = {}
-        self._runs = None
 
     # ------------------------------------------------------------------ weights
     def parts(self) -> List[Tuple[Part, bool]]:
@@ -129,7 +127,6 @@ class DecoderModel:
             raise ValueError("one cache binding per schedule entry is needed")
         self.bindings = bindings
         self.shared_state = shared_state
-        self._runs = None
 
     # ------------------------------------------------------------------ step
     def forward(self, ctx: Any) -> torch.Tensor:
@@ -137,18 +134,8 @@ class DecoderModel:
         ctx.bind_model(self)
         x = self.embed.forward(ctx)
         residual = None
-        if self._runs is None:   # after the weights are bound and the cache is attached
-            self._runs = find_runs(self.blocks, self.spec.schedule, self.bindings) if x.is_cuda else {}
-        i, n = 0, len(self.spec.schedule)
-        while i < n:
-            run = self._runs.get(i)
-            if run is not None and run.accepts(ctx, x):
-                # consecutive layers that describe themselves alike: one kernel for all of them
-                x, residual = run.forward(ctx, x, residual)
-                i = run.end
-                continue
-            x, residual = self.blocks[self.spec.schedule[i].layer].forward(ctx, x, residual, self.bindings[i])
-            i += 1
+        for i, e in enumerate(self.spec.schedule):
+            x, residual = self.blocks[e.layer].forward(ctx, x, residual, self.bindings[i])
         if getattr(ctx, "advance_state", True):
             for pos in self.positions.values():
                 pos.finish_step(ctx, self.shared_state)

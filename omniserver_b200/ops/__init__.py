@@ -43,6 +43,7 @@ class CudaKernels(PersistentDecodeOps):
         self._err_pending: Dict[int, collections.deque] = {}   # copies of the flags on their way to the host
         self._err_hosts: Dict[int, list] = {}                   # pinned landing places not in use
         self.launches = 0  # kernels of this library launched so far
+        self.counts: collections.Counter = collections.Counter()   # ... by entry point: which path the steps took
         self.skinny_warps = 0  # 0: the skinny GEMM picks its K split from the shape
         #: bf16 products with more rows than SKINNY_MAX_ROWS: the tcgen05/TMEM/TMA kernel (True) or the
         #: vendor library's GEMM (False)
@@ -53,9 +54,6 @@ class CudaKernels(PersistentDecodeOps):
         self.decode_stream = True     # decode attention that streams K and V into MMA registers (head size 64, 128)
         self.stream_target_ctas = 148  # CTAs of that kernel the GPU holds at once (one per SM)
         self.stream_cluster_sizes = (2, 4)   # split counts merged inside a thread-block cluster
-        # few rows: the norm before a projection can run inside the projection's kernel. Off: measured in a full
-        # decode step it is slower than the two kernels (every CTA re-reads the rows of the residual stream)
-        self.fuse_prenorm = False
         # Rows from which a plain projection runs in this repository's tcgen05 kernels. Measured, the vendor
         # library is 15-40 % faster on plain products at every row count (it spreads shapes with few tiles over
         # all SMs), so they go to the library; the fused SwiGLU product, which the library cannot do in one
@@ -67,15 +65,14 @@ class CudaKernels(PersistentDecodeOps):
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
         self._pinned_stream: Optional[ctypes.c_void_p] = None
+        # decode steps of up to 16 rows: the weight-streaming kernels (csrc/decode_stream.cu) for the feed-forward
+        # half, for a projection with the norm in front of it, and for a plain projection
         self.fuse_ffn_decode = True
         self.fuse_norm_linear_decode = True
         self.stream_linear_decode = True
-        # the attention half and whole runs of layers as persistent kernels: built and tested; in a full decode step
-        # they measured 3 % and 5 % slower than the separate kernels (five grid barriers per layer), so they are off
-        self.fuse_attn_decode = False
-        self.fuse_decode_layers = False
         self._fused: dict = {}
         self._retired: list = []
+        self._prof: Optional[list] = None    # while profiling: (kernel name, event behind its launch)
         self.tcgen05_pair_min_rows_swiglu = 2048
 
     # ------------------------------------------------------------------ plumbing
@@ -104,9 +101,30 @@ class CudaKernels(PersistentDecodeOps):
 
     def _ok(self, rc: int, what: str) -> None:
         self.launches += 1
+        self.counts[what] += 1
         if rc != 0:
             why = _STATUS.get(rc, f"CUDA error {rc}")
             raise KernelError(f"{what}: {why}")
+        if self._prof is not None:
+            self._mark(what)
+
+    # ------------------------------------------------------------------ per-kernel times (measurement only)
+    def _mark(self, what: str) -> None:
+        if self._prof is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._prof.append((what, ev))
+
+    def start_profile(self) -> None:
+        """From here on an event is recorded behind every launch (kernel by kernel, no graphs)."""
+        self._prof = []
+        self._mark("start")
+
+    def stop_profile(self) -> list:
+        """[(kernel name, ms since the event before it)] of the launches since ``start_profile``; waits for them."""
+        prof, self._prof = self._prof or [], None
+        torch.cuda.synchronize()
+        return [(what, prof[i - 1][1].elapsed_time(ev)) for i, (what, ev) in enumerate(prof) if i > 0]
 
     def check_device_errors(self) -> None:
         """Raise if a kernel recorded a bad index since the last check (synchronises)."""
@@ -227,15 +245,10 @@ class CudaKernels(PersistentDecodeOps):
         M, K = x.shape
         N = w.shape[0]
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-            if (self.stream_linear_decode and out_dtype == torch.bfloat16 and 0 < M <= self.STREAM_LINEAR_MAX_ROWS
-                    and N <= self.STREAM_LINEAR_MAX_N and (bias is None or bias.dtype == torch.bfloat16)
-                    and bool(self.lib.osb_norm_linear_decode_supported(K))):
-                # a few rows and a matrix that one wave of CTAs covers: the weight-streaming kernel without its norm
-                y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-                rc = self.lib.osb_norm_linear_decode(_p(y), _p(None), _p(x), _p(None), _p(None), ctypes.c_float(0.0), _p(w),
-                                                     _p(bias), _p(self.err_flag(x.device)), M, N, K, self._stream())
-                self._ok(rc, "linear_decode")
-                return y
+            if (self.stream_linear_decode and out_dtype == torch.bfloat16 and N <= self.STREAM_LINEAR_MAX_N
+                    and self.can_stream_linear(x, w, bias)):
+                # a few rows: the weight-streaming kernel without a norm
+                return self.stream_linear(x, w, bias)
             return self._linear_bf16(x, w, bias, out_dtype)
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         rc = self.lib.osb_gemm_simt(_p(y), _dt(y), _p(x), _dt(x), _p(w), _dt(w), _p(bias),
@@ -281,22 +294,26 @@ class CudaKernels(PersistentDecodeOps):
             # Library GEMM on the tensor cores (fp32 accumulation inside).
             if out_dtype == torch.bfloat16:
                 if bias is not None and bias.dtype == torch.bfloat16:
-                    return torch.addmm(bias, x, w.t())
-                y = torch.mm(x, w.t())
+                    y = torch.addmm(bias, x, w.t())
+                else:
+                    y = torch.mm(x, w.t())
+                    if bias is not None:
+                        y += bias.to(torch.bfloat16)
+            else:
+                y = torch.mm(x, w.t(), out_dtype=torch.float32)
                 if bias is not None:
-                    y += bias.to(torch.bfloat16)
-                return y
-            y = torch.mm(x, w.t(), out_dtype=torch.float32)
-            if bias is not None:
-                y += bias.float()
+                    y += bias.float()
+            self._mark("library_gemm")
             return y
         return self.gemm_simt(x, w, bias, out_dtype)
 
     def gemm_tcgen05(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                     swiglu: bool = False, pairs: Optional[bool] = None) -> torch.Tensor:
+                     swiglu: bool = False, pairs: Optional[bool] = None, wait_limit: int = 0, tx_extra: int = 0
+                     ) -> torch.Tensor:
         """bf16 product on tcgen05 tensor cores with TMA-fed operands and the accumulator in TMEM.
         ``swiglu``: w is [2I, K] (gate rows first) and the result is silu(x Wg^T) * (x Wu^T), [M, I].
-        ``pairs``: two CTAs per 256-row tile (cta_group::2); None: from ``tcgen05_pair_min_rows``."""
+        ``pairs``: two CTAs per 256-row tile (cta_group::2); None: from ``tcgen05_pair_min_rows``.
+        ``wait_limit`` / ``tx_extra``: only for the test that makes a wait inside the one-CTA kernel run out."""
         _cuda_contig("x", x, torch.bfloat16)
         _cuda_contig("w", w, torch.bfloat16)
         M, K = x.shape
@@ -305,44 +322,18 @@ class CudaKernels(PersistentDecodeOps):
         y = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
         if pairs is None:
             pairs = M >= (self.tcgen05_pair_min_rows_swiglu if swiglu else self.tcgen05_pair_min_rows)
+        if wait_limit or tx_extra:
+            _check(not pairs, "gemm_tcgen05: the wait test runs the one-CTA kernel")
+            rc = self.lib.osb_gemm_tcgen05_bf16_ex(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
+                                                   M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)),
+                                                   int(wait_limit), int(tx_extra), self._stream())
+            self._ok(rc, "gemm_tcgen05_bf16")
+            return y
         fn = self.lib.osb_gemm_tcgen05_2cta_bf16 if pairs else self.lib.osb_gemm_tcgen05_bf16
         rc = fn(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
                 M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)), self._stream())
         self._ok(rc, "gemm_tcgen05_2cta_bf16" if pairs else "gemm_tcgen05_bf16")
         return y
-
-    PRENORM_MAX_ROWS, PRENORM_MAX_K = 16, 2048
-
-    def can_linear_prenorm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
-        """Whether ``linear_prenorm`` takes these operands (else: ``add_rmsnorm`` then ``linear``)."""
-        return (self.fuse_prenorm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2
-                and 0 < x.shape[0] <= self.PRENORM_MAX_ROWS and x.shape[1] % 8 == 0
-                and x.shape[1] <= self.PRENORM_MAX_K)
-
-    def linear_prenorm(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
-                       w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
-                       ) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(norm(residual + x) * norm_weight) @ w^T (+ bias) in one kernel for a few rows; returns (y, the
-        new fp32 residual stream, a new tensor: ``residual`` itself is left as it was)."""
-        _cuda_contig("x", x, torch.bfloat16)
-        _cuda_contig("w", w, torch.bfloat16)
-        _cuda_contig("norm_weight", norm_weight)
-        M, Kd = x.shape
-        N = w.shape[0]
-        _check(self.can_linear_prenorm(x, w) and w.shape[1] == Kd and norm_weight.shape == (Kd,),
-               "linear_prenorm: x [M<=16, K<=2048] bf16, w [N,K] bf16, norm_weight [K]")
-        if residual is not None:
-            _cuda_contig("residual", residual, torch.float32)
-            _check(residual.shape == x.shape, "linear_prenorm: residual [M,K]")
-        if bias is not None:
-            _cuda_contig("bias", bias)
-        res_out = torch.empty((M, Kd), dtype=torch.float32, device=x.device)
-        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        rc = self.lib.osb_gemm_skinny_prenorm_bf16(
-            _p(y), _dt(y), _p(x), _p(residual), _p(res_out), _p(norm_weight), _dt(norm_weight), ctypes.c_float(eps),
-            _p(w), _p(bias), _dt(bias) if bias is not None else 0, M, N, Kd, self._stream())
-        self._ok(rc, "gemm_skinny_prenorm")
-        return y, res_out
 
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].

@@ -2,6 +2,7 @@
 
     python -m omniserver_b200.ops.microbench [--what gemm|gemm_prefill|attn_decode|attn_prefill|ffn_fused|norm|all]
         [--batch 1,8,64] [--ctx 2048] [--hidden 1536 --heads 12 --kv-heads 2 --head-dim 128 --inter 8960 --vocab 151936]
+        [--peak-gbs 6544]
 
 Every timed call runs on its own copy of the weights or cache pages (enough copies to exceed the
 L2), and the calls are replayed from a CUDA graph so that host launch time is not measured.
@@ -11,8 +12,6 @@ Times are CUDA-event times per call; GB/s counts the bytes the kernel has to rea
 from __future__ import annotations
 
 import argparse
-import json
-import os
 from typing import Callable, List
 
 import torch
@@ -40,15 +39,6 @@ def graph_time_us(fn: Callable[[int], None], n_rot: int, iters: int = 5) -> floa
     return e0.elapsed_time(e1) * 1e3 / (iters * n_rot)
 
 
-def peak_gbs() -> float:
-    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
-    try:
-        with open(p) as f:
-            return float(json.load(f)["hbm_gbs"])
-    except Exception:
-        return 6650.0
-
-
 def bench_gemm(args, K, dev, peak) -> None:
     H, I, V = args.hidden, args.inter, args.vocab
     qkv = (args.heads + 2 * args.kv_heads) * args.head_dim
@@ -71,8 +61,12 @@ def bench_gemm(args, K, dev, peak) -> None:
                 else:
                     us = graph_time_us(lambda i: K.gemm_skinny(x, ws[i], None, out_dt), n_rot)
                 gbs = N * Kd * 2 / us / 1e3
-                cols.append(f"warps={warps}: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+                cols.append(f"skinny warps={warps}: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
             K.skinny_warps = 0
+            if name != "head" and K.can_stream_linear(x, ws[0], None):
+                us = graph_time_us(lambda i: K.stream_linear(x, ws[i], None, gated=bool(mode)), n_rot)
+                gbs = N * Kd * 2 / us / 1e3
+                cols.append(f"streaming: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
             if not mode:
                 us = graph_time_us(lambda i: torch.mm(x, ws[i].t()), n_rot)
                 cols.append(f"library: {us:7.1f} us {N * Kd * 2 / us / 1e3:6.0f} GB/s")
@@ -168,8 +162,8 @@ def bench_ffn_fused(args, K, dev, peak) -> None:
         x = torch.randn(B, H, device=dev, dtype=torch.bfloat16)
         res = torch.randn(B, H, device=dev)
         cols = []
-        if K.can_ffn_decode_fused(x, gm, wgu[0], wd[0]):
-            us = graph_time_us(lambda i: K.ffn_decode_fused(x, res, gm, 1e-6, wgu[i], wd[i]), n_rot)
+        if K.can_stream_ffn(x, gm, wgu[0], wd[0]):
+            us = graph_time_us(lambda i: K.stream_ffn(x, res, gm, 1e-6, wgu[i], wd[i]), n_rot)
             gbs = 3 * I * H * 2 / us / 1e3
             cols.append(f"persistent: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
 
@@ -210,7 +204,7 @@ def main() -> None:
     ap.add_argument("--warps", default="0", help="K splits of the skinny GEMM to try (0 = its own choice)")
     ap.add_argument("--no-stream", action="store_true", help="decode attention: the shared-memory kernel instead of the streaming one")
     ap.add_argument("--no-clusters", action="store_true", help="decode attention: merge splits through global memory")
-    ap.add_argument("--stages", type=int, default=0, help="pipeline depth of the decode attention kernel (2 or 3; 0: chosen by the launch)")
+    ap.add_argument("--peak-gbs", type=float, default=6650.0, help="the copy bandwidth the fractions are taken of")
     ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
     args = ap.parse_args()
     args.batch = [int(b) for b in args.batch.split(",")]
@@ -220,10 +214,9 @@ def main() -> None:
     args.target_ctas = [int(b) for b in args.target_ctas.split(",")]
     dev = torch.device("cuda:0")
     K = ops.kernels()
-    K.lib.osb_attn_set_decode_stages(args.stages)
     K.decode_clusters = not args.no_clusters
     K.decode_stream = not args.no_stream
-    peak = peak_gbs()
+    peak = args.peak_gbs
     with torch.inference_mode():
         if args.what in ("all", "gemm"):
             bench_gemm(args, K, dev, peak)

@@ -199,11 +199,6 @@ class Mixer(Part):
     def forward(self, ctx: "Any", x: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
         """x [T, hidden] -> [T, hidden]; reads and writes its cache through ``binding``."""
 
-    def decode_descriptor(self) -> Optional[Dict[str, Any]]:
-        """What a kernel that runs several whole layers of a decode step at once has to know about this mixer
-        (its kind, tensors and constants), or None: then the layer is run part by part."""
-        return None
-
     def forward_prenorm(self, ctx: "Any", x: torch.Tensor, residual: Optional[torch.Tensor], norm: Norm,
                         binding: CacheBinding) -> Tuple[torch.Tensor, torch.Tensor]:
         """forward(norm(residual + x)) and the new residual stream. A mixer whose first projection can
@@ -216,10 +211,6 @@ class FeedForward(Part):
     @abc.abstractmethod
     def forward(self, ctx: "Any", x: torch.Tensor) -> torch.Tensor:
         """x [T, hidden] -> [T, hidden], token by token."""
-
-    def decode_descriptor(self) -> Optional[Dict[str, Any]]:
-        """As ``Mixer.decode_descriptor``, for the feed-forward."""
-        return None
 
     def forward_prenorm(self, ctx: "Any", x: torch.Tensor, residual: Optional[torch.Tensor], norm: Norm
                         ) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -241,10 +232,6 @@ class Block(abc.ABC):
     def forward(self, ctx: "Any", x: torch.Tensor, residual: Optional[torch.Tensor],
                 binding: CacheBinding) -> Tuple[torch.Tensor, torch.Tensor]:
         """One layer on the step's tokens; returns (branch output, residual stream)."""
-
-    def decode_descriptor(self) -> Optional[Dict[str, Any]]:
-        """As ``Mixer.decode_descriptor``, for the whole layer: its arrangement and its parts' descriptors."""
-        return None
 
 
 # --------------------------------------------------------------------------- registries

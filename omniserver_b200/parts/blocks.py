@@ -28,13 +28,5 @@ class PreNormBlock(Block):
         m, residual = self.ffn.forward_prenorm(ctx, a, residual, self.ffn_norm)
         return m, residual
 
-    def decode_descriptor(self):
-        n1, n2 = self.mixer_norm.rms_operands(), self.ffn_norm.rms_operands()
-        m, f = self.mixer.decode_descriptor(), self.ffn.decode_descriptor()
-        if n1 is None or n2 is None or m is None or f is None:
-            return None
-        return {"block": "prenorm_rms", "mixer": m, "ffn": f, "norm_attn": n1[0], "eps_attn": n1[1],
-                "norm_ffn": n2[0], "eps_ffn": n2[1]}
-
 
 register_block("prenorm", PreNormBlock)

@@ -31,17 +31,13 @@ class SwiGLU(FeedForward):
         m = ops.kernels().gate_up_silu(x, self.gate_up.weight, ctx.act_dtype)
         return self.down(m, ctx.act_dtype)
 
-    def decode_descriptor(self):
-        return {"kind": "swiglu", "w_gate_up": self.gate_up.weight, "w_down": self.down.weight,
-                "intermediate_size": self.intermediate_size}
-
     def forward_prenorm(self, ctx: Any, x: torch.Tensor, residual, norm):
         # a few rows (a decode step): norm, both projections and the activation as one kernel, if the
         # norm is one that the kernel computes
         k = ops.kernels()
         rms = norm.rms_operands()
-        if rms is not None and k.can_ffn_decode_fused(x, rms[0], self.gate_up.weight, self.down.weight):
-            return k.ffn_decode_fused(x, residual, rms[0], rms[1], self.gate_up.weight, self.down.weight)
+        if rms is not None and k.can_stream_ffn(x, rms[0], self.gate_up.weight, self.down.weight):
+            return k.stream_ffn(x, residual, rms[0], rms[1], self.gate_up.weight, self.down.weight)
         return super().forward_prenorm(ctx, x, residual, norm)
 
 

@@ -46,13 +46,6 @@ class GQAAttention(Mixer):
     def forward(self, ctx: Any, x: torch.Tensor, binding: CacheBinding) -> torch.Tensor:
         return self._attend(ctx, self.qkv(x, ctx.act_dtype), binding)
 
-    def decode_descriptor(self):
-        if self.position is None or self.out.bias is not None:
-            return None
-        return {"kind": "gqa_rope", "w_qkv": self.qkv.weight, "b_qkv": self.qkv.bias, "w_o": self.out.weight,
-                "nh": self.nh, "nkv": self.nkv, "hd": self.hd, "scale": self.scale, "window": self.window,
-                "position": self.position}
-
     def _rotary(self, ctx: Any):
         """(the step's tables of this mixer's encoding, the same as rotary operands or None)."""
         if self.position is None:
@@ -61,21 +54,7 @@ class GQAAttention(Mixer):
         return tables, self.position.rotary(tables)
 
     def forward_prenorm(self, ctx: Any, x: torch.Tensor, residual, norm, binding: CacheBinding):
-        # a decode step of a few single-token requests: norm, projections, rotary encoding, cache write and
-        # attention as one persistent kernel, if the norm is one that the kernel computes
-        k = ops.kernels()
-        rms = norm.rms_operands()
-        _, rot = self._rotary(ctx)
-        if (rms is not None and rot is not None and binding.writes and ctx.decode_index is not None
-                and self.out.bias is None
-                and k.can_attn_decode_fused(x, rms[0], self.qkv.weight, self.qkv.bias, self.out.weight, binding.k_cache,
-                                            self.nh, self.nkv, self.hd, ctx.n_decode, ctx.n_multi, rot.rot_dim)):
-            g = binding.group
-            return k.attn_decode_fused(x, residual, rms[0], rms[1], self.qkv.weight, self.qkv.bias, self.out.weight,
-                                       binding.k_cache, binding.v_cache, ctx.block_tables[g], ctx.cu_q, ctx.seq_lens,
-                                       ctx.decode_index, self.nh, self.nkv, self.hd, self.scale, self.window,
-                                       ctx.max_kv_len, (rot.cos, rot.sin, ctx.slot_maps[g], rot.rot_dim),
-                                       ctx.scratch)
+        # a few rows (a decode step): the norm inside the kernel of the q/k/v projection, if the norm has such a kernel
         fused = norm.fused_linear(x, residual, self.qkv, ctx.act_dtype)
         if fused is None:
             return super().forward_prenorm(ctx, x, residual, norm, binding)

@@ -35,11 +35,10 @@ class RMSNorm(Norm):
 
     def fused_linear(self, x, residual, linear, out_dtype):
         k = ops.kernels()
-        if out_dtype == torch.bfloat16 and k.can_norm_linear_decode(x, self.weight, linear.weight, linear.bias):
-            return k.norm_linear_decode(x, residual, self.weight, self.eps, linear.weight, linear.bias)
-        if not k.can_linear_prenorm(x, linear.weight):
-            return None
-        return k.linear_prenorm(x, residual, self.weight, self.eps, linear.weight, linear.bias, out_dtype)
+        if (out_dtype == torch.bfloat16 and k.fuse_norm_linear_decode
+                and k.can_stream_linear(x, linear.weight, linear.bias, self.weight)):
+            return k.stream_linear(x, linear.weight, linear.bias, norm=(residual, self.weight, self.eps))
+        return None
 
 
 register_norm("rmsnorm", RMSNorm)

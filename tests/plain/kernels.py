@@ -18,19 +18,12 @@ class PlainKernels:
     SKINNY_MAX_ROWS = 0
     launches = 0
 
-    def can_decode_layers_fused(self, *args, **kw):
+    fuse_norm_linear_decode = False
+
+    def can_stream_linear(self, x, w, bias, norm_weight=None):
         return False
 
-    def can_attn_decode_fused(self, *args, **kw):
-        return False
-
-    def can_norm_linear_decode(self, x, norm_weight, w, bias):
-        return False
-
-    def can_ffn_decode_fused(self, x, norm_weight, w_gate_up, w_down):
-        return False
-
-    def can_linear_prenorm(self, x, w):
+    def can_stream_ffn(self, x, norm_weight, w_gate_up, w_down):
         return False
 
     @contextlib.contextmanager

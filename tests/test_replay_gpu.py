@@ -80,6 +80,29 @@ def test_replay_matches_plain(dtype, name, family, tmp_path):
         check(got[rid], want, dtype, f"{name}/{family}/{rid}")
 
 
+@pytest.mark.parametrize("family", list(FAMILIES))
+def test_replay_through_the_serving_kernels_of_decode_steps(family, tmp_path):
+    """The tiny configuration whose sizes the weight-streaming kernels and the streaming decode attention take: the
+    replay families in bfloat16 run decode steps (and mixed steps of up to 16 rows) through those kernels inside
+    the engine, with pages that are used again; the kernels' use is checked by their launch counts."""
+    from omniserver_b200 import ops
+    d = make_model_dir(tmp_path, "tiny_d", "bfloat16")
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V)
+    steps = FAMILIES[family](reqs)
+    runner = runner_for(d, "bfloat16", rc.max_live_tokens(steps))
+    counts = ops.kernels().counts
+    before = dict(counts)
+    got = rc.collect(steps, replay_in_process(runner, steps))
+    if family in ("tail", "mixed"):
+        for what in ("stream_ffn", "stream_linear", "attn_decode_stream"):
+            assert counts.get(what, 0) > before.get(what, 0), f"{what} did not run in the {family} family"
+    for rid, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        assert torch.isfinite(got[rid]).all()
+        check(got[rid], want, "bfloat16", f"tiny_d/{family}/{rid}")
+
+
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
 def test_fp32_logits_do_not_depend_on_the_cut(name, tmp_path):
     """In 32-bit every kernel sums in an order fixed by the element, so whole, token by token,
@@ -161,6 +184,37 @@ def test_decode_graphs_across_buckets_and_batch_sizes(dtype, tmp_path):
         rows = sorted(got[r])
         assert len(rows) >= 16
         check(torch.stack([got[r][p] for p in rows]), want[rows], dtype, f"graphs/{r}")
+
+
+def test_the_number_of_decode_graphs_is_bounded(tmp_path):
+    """With room for two graphs, a batch that keeps changing its size makes the runner drop the graph used longest
+    ago and build it again later; the logits stay those of the plain model."""
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_a", "float32")
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V, (30, 30, 30, 30), seed=14)
+    runner = runner_for(d, "float32", 512)
+    runner.graph_max_count = 2
+    got = {r: {} for r in reqs}
+    with torch.inference_mode():
+        for r, toks in reqs.items():
+            runner.start_request(r)
+            runner.step([StepEntry(r, toks[:10], want=[])])
+        pos = {r: 10 for r in reqs}
+        names = list(reqs)
+        for step in range(20):
+            live = names[:1 + step % 4]              # batch sizes 1, 2, 3, 4, 1, ...
+            lg = runner.step([StepEntry(r, [reqs[r][pos[r]]], want=[0]) for r in live]).float().cpu()
+            for i, r in enumerate(live):
+                got[r][pos[r]] = lg[i]
+                pos[r] += 1
+            assert len(runner._graphs) <= 2
+        for r in reqs:
+            runner.end_request(r)
+    for r, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        rows = sorted(got[r])
+        check(torch.stack([got[r][p] for p in rows]), want[rows], "float32", f"bounded graphs/{r}")
 
 
 def test_positions_and_embeddings_given_with_the_prompt(tmp_path):

@@ -35,4 +35,16 @@ TINY_C = {
 }
 TINY_C_INIT = {"seed": 5, "std": 0.05, "norm_noise": 0.05}
 
-ALL = {"tiny_a": (TINY_A, TINY_A_INIT), "tiny_b": (TINY_B, TINY_B_INIT), "tiny_c": (TINY_C, TINY_C_INIT)}
+# Sizes that the decode step's weight-streaming kernels take (width and intermediate size multiples of 128) and the
+# streaming decode attention (head size 64): the fast kernels of serving inside the engine, at a size a CPU can check.
+TINY_D = {
+    "architectures": [ARCH], "model_type": "qwen2_vl",
+    "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 384, "vocab_size": 640, "rms_norm_eps": 1e-6,
+    "rope_theta": 10000.0, "rope_scaling": {"type": "mrope", "mrope_section": [8, 12, 12]},
+    "tie_word_embeddings": False, "hidden_act": "silu", "use_sliding_window": False,
+}
+TINY_D_INIT = {"seed": 9, "std": 0.03, "norm_noise": 0.1}
+
+ALL = {"tiny_a": (TINY_A, TINY_A_INIT), "tiny_b": (TINY_B, TINY_B_INIT), "tiny_c": (TINY_C, TINY_C_INIT),
+       "tiny_d": (TINY_D, TINY_D_INIT)}
