@@ -32,6 +32,8 @@ constexpr int NW = 8;              // warps per CTA
 constexpr int NT = NW * 32;
 constexpr int BLK = 16;            // keys per block
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr uint32_t MERGE_WAIT_LIMIT = 1u << 20;   // polls of a group's counter before the merging CTA gives up
+enum : int { ERR_MERGE_WAIT = 141 };
 
 struct FusedRope {
   const float* cos_t;
@@ -59,12 +61,12 @@ struct KVRegs {
 // (programmatic dependent launch); nothing of this step's q, k, v is touched before it.
 template <int HD, bool CLUSTER, class WaitFn>
 __device__ __forceinline__ void attn_stream_unit(
-    WaitFn&& wait_for_q, int split_, int by_, int s_, int ny_, unsigned char* smem_raw, int* s_last_p,
+    WaitFn&& wait_for_q, int split_, int by_, int s_, int ny_, unsigned char* smem_raw,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
     const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int log2ps, int num_pages,
-    float scale_log2, int window, int chunk, int nsplits, FusedRope fr) {
+    float scale_log2, int window, int chunk, int nsplits, FusedRope fr, int* __restrict__ err) {
   constexpr int NDB = HD / 32;     // 32-dim blocks
   constexpr int stride = HD + 8;   // q rows in shared memory, bf16
   constexpr int ostride = HD + 8;  // merge rows, fp32
@@ -379,8 +381,12 @@ __device__ __forceinline__ void attn_stream_unit(
   }
   __syncthreads();
   const bool direct = !CLUSTER && first_split == last_split;
+  const bool merger = !CLUSTER && split == last_split;   // without a cluster: the CTA of the last split merges
   const int drow = decode_index[s];
   constexpr int hq = HD >> 2;
+  static_assert(8 * hq <= NT, "a thread has at most one (head, four dims) of the CTA's result");
+  float my_m = -INFINITY, my_l = 0.0f;   // the merging CTA keeps its own partial result in registers
+  float4 my_acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (int idx = tid; idx < rows * hq; idx += NT) {
     const int r = idx / hq, d = (idx - r * hq) * 4;
     float M = -INFINITY;
@@ -412,6 +418,10 @@ __device__ __forceinline__ void attn_stream_unit(
         cml[r * 2] = M;
         cml[r * 2 + 1] = L;
       }
+    } else if (merger) {
+      my_m = M;
+      my_l = L;
+      my_acc = acc;
     } else {
       const size_t prow = ((size_t)drow * nh + head) * nsplits + split;
       *reinterpret_cast<float4*>(part_o + prow * HD + d) = acc;
@@ -467,47 +477,62 @@ __device__ __forceinline__ void attn_stream_unit(
     return;
   }
 
-  // Without a cluster: the CTA that finishes last among this group's splits merges them, in split order, so
-  // the result does not depend on which CTA that is. The counter returns to zero.
-  __threadfence();
-  __syncthreads();
+  // Without a cluster: the CTA of the last split (the highest block index of its group, so the others were handed
+  // to SMs before it) merges. The others put their partial results into global memory, add one to the group's
+  // counter without waiting for the answer, and are done. The merging CTA keeps its own partial result in
+  // registers, waits (bounded) until the counter says that all others have arrived, puts the counter back to zero,
+  // and folds the others' results into its own in split order, fetching (max, sum) and outputs of up to eight
+  // splits in one round trip. The launcher only takes this path when all CTAs of the grid fit on the GPU at once.
+  int* cnt = counters + (size_t)drow * ny_ + by_;
+  if (!merger) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) atomicAdd(cnt, 1);   // the result is not used: nobody waits for it
+    return;
+  }
+  const int others = last_split - first_split;
   if (tid == 0) {
-    int* cnt = counters + (size_t)drow * ny_ + by_;
-    const int prev = atomicAdd(cnt, 1);
-    *s_last_p = (prev == last_split - first_split);
-    if (*s_last_p) *cnt = 0;
+    bool ok = false;
+    for (uint32_t i = 0; i < MERGE_WAIT_LIMIT && !ok; ++i) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+      ok = v >= others;
+    }
+    if (!ok) atomicExch(err, ERR_MERGE_WAIT);
+    *cnt = 0;
   }
   __syncthreads();
-  if (!*s_last_p) return;
-  __threadfence();
-  const int nv = last_split - first_split + 1;
-  float* sml = wo;  // [rows][nv][2]
-  for (int idx = tid; idx < rows * nv; idx += NT) {
-    const int r = idx / nv, sp = idx - r * nv;
-    const size_t prow = ((size_t)drow * nh + head0 + r) * nsplits + first_split + sp;
-    sml[idx * 2] = __ldcg(part_ml + prow * 2);
-    sml[idx * 2 + 1] = __ldcg(part_ml + prow * 2 + 1);
-  }
-  __syncthreads();
-  for (int idx = tid; idx < rows * hq; idx += NT) {
-    const int r = idx / hq, d = (idx - r * hq) * 4;
-    const float* ml = sml + (size_t)r * nv * 2;
-    float M = -INFINITY;
-    for (int sp = 0; sp < nv; ++sp) M = fmaxf(M, ml[sp * 2]);
-    const float* po = part_o + (((size_t)drow * nh + head0 + r) * nsplits + first_split) * HD + d;
-    float L = 0.0f;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int sp0 = 0; sp0 < nv; sp0 += 8) {
+  if (tid < rows * hq) {
+    const int r = tid / hq, d = (tid - r * hq) * 4;
+    const size_t prow0 = ((size_t)drow * nh + head0 + r) * nsplits + first_split;
+    float M = my_m, L = my_l;
+    float4 acc = my_acc;
+    for (int sp0 = 0; sp0 < others; sp0 += 8) {
+      float2 ml[8];
       float4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (sp0 + u < nv) v[u] = __ldcg(reinterpret_cast<const float4*>(po + (size_t)(sp0 + u) * HD));
+        if (sp0 + u < others) {
+          ml[u] = __ldcg(reinterpret_cast<const float2*>(part_ml + (prow0 + sp0 + u) * 2));
+          v[u] = __ldcg(reinterpret_cast<const float4*>(part_o + (prow0 + sp0 + u) * HD + d));
+        }
+      float Mc = M;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (sp0 + u < others) Mc = fmaxf(Mc, ml[u].x);
+      if (Mc == -INFINITY) continue;
+      const float keep = M == -INFINITY ? 0.0f : fast_exp2(M - Mc);
+      L *= keep;
+      acc.x *= keep;
+      acc.y *= keep;
+      acc.z *= keep;
+      acc.w *= keep;
+      M = Mc;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        if (sp0 + u < nv) {
-          const float ms = ml[(sp0 + u) * 2];
-          const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - M);
-          L += ml[(sp0 + u) * 2 + 1] * f;
+        if (sp0 + u < others && ml[u].x != -INFINITY) {
+          const float f = fast_exp2(ml[u].x - M);
+          L += ml[u].y * f;
           acc.x += v[u].x * f;
           acc.y += v[u].y * f;
           acc.z += v[u].z * f;
@@ -534,20 +559,19 @@ __global__ void __launch_bounds__(NT, 1) attn_decode_stream_kernel(
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
     const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int log2ps, int num_pages,
-    float scale_log2, int window, int chunk, int nsplits, FusedRope fr) {
+    float scale_log2, int window, int chunk, int nsplits, FusedRope fr, int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ int s_last;
-  attn_stream_unit<HD, CLUSTER>([] { pdl_wait(); }, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.y, smem_raw, &s_last, out, part_o,
+  attn_stream_unit<HD, CLUSTER>([] { pdl_wait(); }, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.y, smem_raw, out, part_o,
                                        part_ml, q, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                        decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk,
-                                       nsplits, fr);
+                                       nsplits, fr, err);
 }
 
 template <int HD>
 int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_stride, const bf16* kc, const bf16* vc,
            const int* bt, int bt_stride, const int* cu_q, const int* seq_lens, const int* decode_index, int* counters,
            int S, int nh, int nkv, int log2ps, int num_pages, float scale_log2, int window, int chunk, int nsplits,
-           cudaStream_t stream, FusedRope fr, bool use_cluster) {
+           cudaStream_t stream, FusedRope fr, bool use_cluster, int* err) {
   // q rows, the warps' (max, sum) and outputs, the CTA's own; the last CTA's table of (max, sum) of all splits
   size_t smem = (size_t)16 * (HD + 8) * sizeof(bf16) + (size_t)(NW + 1) * 16 * 2 * sizeof(float) +
                 (size_t)(NW + 1) * 16 * (HD + 8) * sizeof(float);
@@ -560,13 +584,13 @@ int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_st
     if (e != cudaSuccess) return (int)e;
     rc = osb_launch_cluster(k, grid, dim3(NT), smem, stream, nsplits, out, part_o, part_ml, q, q_row_stride, kc, vc, bt,
                             bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2,
-                            window, chunk, nsplits, fr);
+                            window, chunk, nsplits, fr, err);
   } else {
     auto k = attn_decode_stream_kernel<HD, false>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     rc = osb_launch(k, grid, dim3(NT), smem, stream, out, part_o, part_ml, q, q_row_stride, kc, vc, bt, bt_stride, cu_q,
-                    seq_lens, decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk, nsplits, fr);
+                    seq_lens, decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk, nsplits, fr, err);
   }
   return rc ? rc : osb_last_error();
 }
@@ -575,13 +599,15 @@ int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_st
 // The decode part of osb_paged_attn_bf16 (same arguments, same meaning; requests bringing more than one
 // token are skipped) for head sizes 64 and 128 and page sizes that are powers of two; anything else is refused
 // with OSB_ERR_UNSUPPORTED. chunk is a multiple of 64; with nsplits > 1 and no cluster, part_o / part_ml /
-// counters as for osb_paged_attn_bf16 (the splits table of the merging CTA needs rows * nsplits <= 8 * 16 * (hd + 8) / 2).
+// counters as for osb_paged_attn_bf16; the CTA of a group's last split then waits (bounded; error 141 in *err) for the
+// group's other splits, so the grid (nsplits x kv heads x head tiles x S) must fit on the GPU at once: a larger one is
+// refused with OSB_ERR_TOO_LARGE (n_decode: how many of the S requests bring one token; 0: all of them).
 OSB_API int osb_attn_decode_stream(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
                                    const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
                                    const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
                                    float scale, int window, float* part_o, float* part_ml, int* counters, int chunk,
                                    int nsplits, const float* rope_cos, const float* rope_sin, const int* rope_slot_map,
-                                   int rope_rot, int use_cluster, cudaStream_t stream) {
+                                   int rope_rot, int use_cluster, int n_decode, int* err, cudaStream_t stream) {
   if (S <= 0) return OSB_OK;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return OSB_ERR_UNSUPPORTED;
   if (page_size < 1 || (page_size & (page_size - 1))) return OSB_ERR_UNSUPPORTED;
@@ -589,7 +615,19 @@ OSB_API int osb_attn_decode_stream(void* out, const void* q, int q_row_stride, c
     return OSB_ERR_UNSUPPORTED;
   if (chunk <= 0 || chunk % 64 != 0 || nsplits <= 0 || nsplits > 128) return OSB_ERR_BAD_SHAPE;
   if (use_cluster && (nsplits < 2 || nsplits > 8)) use_cluster = 0;
-  if (nsplits > 1 && !use_cluster && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OSB_ERR_BAD_SHAPE;
+  if (nsplits > 1 && !use_cluster) {
+    if (part_o == nullptr || part_ml == nullptr || counters == nullptr || err == nullptr) return OSB_ERR_BAD_SHAPE;
+    // the CTA that merges a group's splits waits for the others: all CTAs must be on the GPU at the same time
+    static int n_sms = 0;
+    if (n_sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0) n_sms = 1;
+    }
+    // (n_decode: the requests of the step that bring one token; the CTAs of the others end at once)
+    if (n_decode <= 0 || n_decode > S) n_decode = S;
+    if ((long long)nsplits * nkv * ((nh / nkv + 7) / 8) * n_decode > n_sms) return OSB_ERR_TOO_LARGE;
+  }
   FusedRope fr{rope_cos, rope_sin, rope_slot_map, rope_rot};
   if (rope_cos != nullptr) {
     if (nh / nkv > 8 || rope_sin == nullptr || rope_slot_map == nullptr || rope_rot <= 0 || rope_rot > hd || (rope_rot & 1))
@@ -601,8 +639,8 @@ OSB_API int osb_attn_decode_stream(void* out, const void* q, int q_row_stride, c
   if (hd == 64)
     return launch<64>((bf16*)out, part_o, part_ml, (const bf16*)q, q_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
                       block_table, bt_stride, cu_q, seq_lens, decode_index, counters, S, nh, nkv, log2ps, num_pages,
-                      scale_log2, window, chunk, nsplits, stream, fr, use_cluster != 0);
+                      scale_log2, window, chunk, nsplits, stream, fr, use_cluster != 0, err);
   return launch<128>((bf16*)out, part_o, part_ml, (const bf16*)q, q_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
                      block_table, bt_stride, cu_q, seq_lens, decode_index, counters, S, nh, nkv, log2ps, num_pages,
-                     scale_log2, window, chunk, nsplits, stream, fr, use_cluster != 0);
+                     scale_log2, window, chunk, nsplits, stream, fr, use_cluster != 0, err);
 }
