@@ -60,9 +60,6 @@ class CudaKernels(PersistentDecodeOps):
         # kernel, is 35-40 % faster here at many rows and still ahead of library + activation kernel at 64 rows
         # (15.6 vs 16.2 us; at 24 rows the library pair wins, 14.0 vs 19.1 us).
         self.tcgen05_min_rows = 1 << 30
-        # 17 to 128 rows (decode steps of many requests): the tcgen05 kernel that cuts K over the CTAs of a cluster
-        self.use_splitk = True
-        self.SPLITK_MAX_ROWS = 128
         self.tcgen05_min_rows_swiglu = 64
         # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
@@ -293,9 +290,6 @@ class CudaKernels(PersistentDecodeOps):
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows and K % 8 == 0 and x.data_ptr() % 16 == 0
                 and w.data_ptr() % 16 == 0):
             return self.gemm_tcgen05(x, w, bias, out_dtype)
-        if (self.use_splitk and M <= self.SPLITK_MAX_ROWS and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-                and bool(self.lib.osb_gemm_splitk_supported(M, N, K))):
-            return self.gemm_splitk(x, w, bias, out_dtype)
         if K % 8 == 0 and N % 8 == 0:
             # Library GEMM on the tensor cores (fp32 accumulation inside).
             if out_dtype == torch.bfloat16:
@@ -339,24 +333,6 @@ class CudaKernels(PersistentDecodeOps):
         rc = fn(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
                 M, N, K, 1 if swiglu else 0, _p(self.err_flag(x.device)), self._stream())
         self._ok(rc, "gemm_tcgen05_2cta_bf16" if pairs else "gemm_tcgen05_bf16")
-        return y
-
-    def gemm_splitk(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype
-                    ) -> torch.Tensor:
-        """bf16 product for up to 128 rows on tcgen05 tensor cores with K cut over the CTAs of a thread-block cluster
-        and the partial tiles summed through distributed shared memory (projections with few tiles of W)."""
-        _cuda_contig("x", x, torch.bfloat16)
-        _cuda_contig("w", w, torch.bfloat16)
-        M, K = x.shape
-        N = w.shape[0]
-        _check(w.shape[1] == K and bool(self.lib.osb_gemm_splitk_supported(M, N, K)),
-               "gemm_splitk: x [M<=128, K], w [N, K], K % 8 == 0, no more 64-row tiles of w than SMs")
-        if bias is not None:
-            _cuda_contig("bias", bias)
-        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        rc = self.lib.osb_gemm_splitk_bf16(_p(y), _dt(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0,
-                                           M, N, K, _p(self.err_flag(x.device)), self._stream())
-        self._ok(rc, "gemm_splitk_bf16")
         return y
 
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

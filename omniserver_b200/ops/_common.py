@@ -37,9 +37,6 @@ _DEVICE_ERR = {
     111: "tcgen05 attention: the TMA producer waited too long for a free key/value stage",
     112: "tcgen05 attention: the MMA issuer waited too long for operands",
     113: "tcgen05 attention: the softmax warps waited too long for scores or the output",
-    151: "split-K tcgen05 GEMM: the TMA producer waited too long for a free stage",
-    152: "split-K tcgen05 GEMM: the MMA issuer waited too long for operands",
-    153: "split-K tcgen05 GEMM: the epilogue waited too long for the accumulator",
     141: "decode attention: the CTA that merges a request's splits waited too long for the others",
     131: "weight-streaming decode kernel: the consumer warps waited too long for a weight tile",
     132: "weight-streaming decode kernel: the weight stream waited too long for a free tile",

@@ -324,31 +324,6 @@ def test_a_wait_of_all_ctas_for_one_another_runs_out_and_reports():
     assert torch.equal(again, good)
 
 
-@pytest.mark.parametrize("M,N,K_", [(17, 2048, 1536), (64, 1536, 1536), (64, 1536, 8960), (128, 4608, 3584), (33, 3584, 18944),
-                                    (24, 100, 72), (19, 10240, 8192), (100, 1000, 200), (1, 264, 2048)])
-def test_gemm_splitk(M, N, K_):
-    """The tcgen05 product for up to 128 rows whose K range is cut over the CTAs of a cluster, with the partial tiles
-    summed through distributed shared memory: the projections of the 2B, 7B and 72B sizes at decode row counts, and
-    ragged shapes (N no multiple of the tile, K no multiple of 64, one row); bias of either type, both output types;
-    twice in a row gives the same bits (the sum's order does not depend on timing)."""
-    x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(N, K_, dtype=torch.bfloat16, seed=1, scale=K_ ** -0.5)
-    b = rnd(N, dtype=torch.bfloat16, seed=2)
-    k = K()
-    assert bool(k.lib.osb_gemm_splitk_supported(M, N, K_))
-    for bias in (None, b, b.float()):
-        for out_dtype in (torch.bfloat16, torch.float32):
-            bd = bias.to(DEV) if bias is not None else None
-            got = k.gemm_splitk(x.to(DEV), w.to(DEV), bd, out_dtype)
-            again = k.gemm_splitk(x.to(DEV), w.to(DEV), bd, out_dtype)
-            assert torch.equal(got, again)
-            want = REF.linear(x.double(), w.double(), bias.double() if bias is not None else None, torch.float64)
-            t = dict(rtol=1e-4, atol=2.5e-8 * K_ * float(want.abs().max()) + 1e-5) if out_dtype == torch.float32 \
-                else tol(torch.bfloat16)
-            assert torch.allclose(got.double().cpu(), want, **t)
-    k.check_device_errors()
-    assert not bool(k.lib.osb_gemm_splitk_supported(129, N, K_)) and not bool(k.lib.osb_gemm_splitk_supported(M, 151936, K_))
-
-
 def test_a_wait_inside_the_tcgen05_gemm_runs_out_and_reports():
     """Every mbarrier wait of the tcgen05 kernels is bounded. Here the TMA producer announces 16 bytes more to every
     stage's barrier than it copies, so no stage ever becomes full, and the waits give up after 4,096 polls: the MMA
