@@ -684,6 +684,20 @@ def test_prefill_attention_tcgen05(nh, nkv, hd, ps, window):
     _assert_attn_close(other, want, case, nh, nkv, hd, window, "mma.sync")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (14, 2, 64, 32, 150), (16, 4, 128, 64, None)])
+def test_prefill_attention_tcgen05_many_units_per_cta(nh, nkv, hd, ps, window):
+    """More units of work (128 rows of a request and head) than SMs, several times over: a CTA takes one
+    after another (a long one, then short ones, empty ones between them) with its barriers, tensor memory and
+    K/V stages running on; requests of very different lengths, with and without earlier context."""
+    q_lens = [600, 129, 1, 384, 77, 512, 2, 640, 300]
+    kv_lens = [600, 1200, 333, 384, 900, 513, 130, 1500, 301]
+    case = _poison_unused(_paged_case(q_lens, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=23), ps)
+    assert -(-max(q_lens) // 128) * nh * len(q_lens) > 3 * 148
+    got, want = _run_attn(case, nh, nkv, hd, window, torch.bfloat16)
+    assert torch.isfinite(got).all()
+    _assert_attn_close(got, want, case, nh, nkv, hd, window, "tcgen05, several units per CTA")
+
+
 @pytest.mark.parametrize("window", [None, 130])
 def test_prefill_attention_tcgen05_finds_one_key_that_matters(window):
     """One dominating key at the edges of the 128-key tiles, of pages, of the window and at the query
