@@ -50,7 +50,7 @@ MODEL_2B = {
 FULL_LAYERS = 28
 CONTEXT = 2048
 NEW_TOKENS = 256
-PAGE_SIZE = 16       # tokens per cache page (--page-size)
+PAGE_SIZE = 32       # tokens per cache page (--page-size); the engine's default
 SEED = 2
 
 

@@ -22,6 +22,8 @@ import sys
 import time
 from typing import List
 
+from .config.engine_config import DEFAULT_PAGE_SIZE
+
 
 def _prompts(args) -> List[List[int]]:
     out: List[List[int]] = []
@@ -155,7 +157,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--max-prefill-per-step", type=int, default=1)
     g.add_argument("--max-prefill-tokens", type=int, default=8192)
     g.add_argument("--max-seq-len", type=int, default=4096)
-    g.add_argument("--page-size", type=int, default=16)
+    g.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE)
     g.add_argument("--max-cache-tokens", type=int, default=32768)
     g.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel")
     g.add_argument("--device", default="cuda:0")
@@ -187,7 +189,7 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--prompt-hi", type=int, default=4096)
     b.add_argument("--chunk", type=int, default=2048, help="most prompt tokens per step of 'mixed'")
     b.add_argument("--max-new-tokens", type=int, default=256)
-    b.add_argument("--page-size", type=int, default=16)
+    b.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE)
     b.add_argument("--no-cuda-graph", action="store_true")
     b.add_argument("--profile", action="store_true", help="time per class of kernels inside real steps")
     b.add_argument("--peaks", default=None, help="a MEASURED_PEAKS.json (hbm_gbs, bf16_tflops) for the fractions")
@@ -199,7 +201,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True)
     p.add_argument("--max-tokens", type=int, required=True)
-    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE)
     p.set_defaults(fn=cmd_replay)
     return ap
 

@@ -100,6 +100,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_kernel(
   if (warp == 1) {  // TMEM: two accumulators of BN fp32 columns x 128 lanes
     tmem_alloc(&tmem_base_slot, (uint32_t)TMEM_COLS);
   }
+  // the set-up above may run while the kernel before this one in the stream finishes; x (and whatever shares y's
+  // memory) belongs to that kernel until here
+  pdl_wait();
   fence_before();
   __syncthreads();
   fence_after();
@@ -289,8 +292,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* y, int yf, const 
   const int m_blocks = (M + BM - 1) / BM;
   const int num_tiles = m_blocks * ((out_cols + cols_per_tile - 1) / cols_per_tile);
   const int ctas = num_tiles < sm_count() ? num_tiles : sm_count();
-  k<<<ctas, NUM_THREADS, smem, stream>>>(ma, mb, y, yf, bias, bf, M, N, K, I, m_blocks, num_tiles, err, wait_limit, tx_extra);
-  return osb_last_error();
+  const int rc = osb_launch(k, dim3(ctas), dim3(NUM_THREADS), smem, stream, ma, mb, y, yf, bias, bf, M, N, K, I, m_blocks,
+                            num_tiles, err, wait_limit, tx_extra);
+  return rc ? rc : osb_last_error();
 }
 
 // Time of a shape in units of "one 128-column tile on one SM": full waves over the SMs.

@@ -147,6 +147,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_tcgen05_2cta_kernel(
     mbar_init_fence();
   }
   if (warp == 1) tmem_alloc_pair(&tmem_base_slot, TMEM_COLS);
+  // The kernel is launched with programmatic stream serialization: it may begin while the kernel before it in the
+  // stream is still writing x. Only the set-up above runs before that kernel has completed.
+  pdl_wait();
   fence_before();
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them from the other CTA

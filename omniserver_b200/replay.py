@@ -27,7 +27,7 @@ import numpy as np
 import torch
 
 from . import ops
-from .config import EngineConfig
+from .config import DEFAULT_PAGE_SIZE, EngineConfig
 from .engine.llm_engine import build_runner
 from .engine.step import ModelRunner, StepEntry
 
@@ -95,7 +95,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder the logits files are written to")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each request rounded up to 64)")
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE)
     ap.add_argument("--max-requests", type=int, default=64)
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
