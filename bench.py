@@ -12,7 +12,8 @@ decode step of the whole batch.  It prints one JSON line:
   median of --trials such runs;
 * ``e2e``: the same through the Python entry point (LLMEngine.step): scheduler, host token ids in
   (pinned staging buffer, one host-to-device copy per step) and sampled ids out;
-* ``prefill``: one 2,048-token prompt through the step function; ``frac`` = flops / time / bf16 peak;
+* ``prefill``: one 2,048-token prompt through the step function; ``frac`` = flops / time / bf16 peak, the time from
+  the call to the logits with the device idle before (``back_to_back_ms``: per step when four follow one another);
 * ``roofline``: bytes a decode step has to read (every weight once, the live requests' keys and
   values) / its time, against the measured copy bandwidth;
 * ``points``: decode at batch 1 and 64 (tokens/s, ms per step, fraction of the roofline), and for the 7B and
@@ -208,7 +209,7 @@ def run_ours(args):
                 r = b72.decode(B, 8, 3, trials=1)
                 points.update({f"72b_decode_b{B}": round(r["tokens_per_s"], 1), f"72b_decode_b{B}_ms": round(r["ms_per_step"], 3),
                                f"72b_decode_b{B}_frac": round(r["frac"], 4)})
-            p72 = b72.prefill(CONTEXT, trials=3, warmup=1)
+            p72 = b72.prefill(CONTEXT, trials=3, warmup=1, back_to_back=1)
             points.update({"72b_prefill_tok_s": p72["value"], "72b_prefill_ms": p72["ms"], "72b_prefill_frac": p72["frac"]})
             b72.close()
         except Exception as e:

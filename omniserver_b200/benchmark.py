@@ -131,7 +131,7 @@ def prefill_flops(cfg: Dict[str, Any], layers: int, T: int, start: int = 0, logi
 KERNEL_CLASS = (
     ("attn", "attention"), ("paged_attn", "attention"), ("stream_", "gemm"), ("gemm", "gemm"), ("library_gemm", "gemm"),
     ("silu_mul", "gemm"), ("add_rmsnorm", "norm"), ("rope", "rope"), ("advance_cursor", "rope"), ("embed", "embedding"),
-    ("scatter_rows", "embedding"), ("argmax", "sampling"), ("sample", "sampling"),
+    ("scatter_rows", "embedding"), ("argmax", "sampling"), ("sample", "sampling"), ("plan", "host"),
 )
 
 
@@ -180,10 +180,14 @@ class Bench:
         return self.torch.randint(0, self.cfg["vocab_size"], (n,), generator=self.gen).tolist()
 
     # ------------------------------------------------------------------ prefill: one prompt through the step function
-    def prefill(self, tokens: int = 2048, trials: int = 5, warmup: int = 3) -> Dict[str, Any]:
+    def prefill(self, tokens: int = 2048, trials: int = 5, warmup: int = 3, back_to_back: int = 4) -> Dict[str, Any]:
+        """One prompt of ``tokens`` tokens through the step function. ``ms`` is the time from the call to the logits,
+        the device idle before it (so the host's planning of the step counts: what a first token waits for).
+        ``back_to_back_ms`` is the time per step when ``back_to_back`` such steps of different requests are launched
+        one behind the other, as a loaded engine runs them: the host plans a step while the one before computes."""
         from .engine.step import StepEntry
         torch, runner = self.torch, self.runner
-        times = []
+        times, b2b = [], []
         with torch.inference_mode():
             for i in range(warmup + trials):
                 toks = self.new_prompt(tokens)
@@ -196,12 +200,28 @@ class Bench:
                 runner.end_request(f"p{i}")
                 if i >= warmup:
                     times.append(e0.elapsed_time(e1))
+            for i in range(trials if back_to_back > 1 else 0):
+                prompts = [self.new_prompt(tokens) for _ in range(back_to_back)]
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for j, toks in enumerate(prompts):
+                    runner.start_request(f"b{i}_{j}")
+                    runner.step([StepEntry(f"b{i}_{j}", toks, want=[tokens - 1])])
+                    runner.end_request(f"b{i}_{j}")     # its pages go to the next prompt; the stream keeps the order
+                e1.record()
+                torch.cuda.synchronize()
+                b2b.append(e0.elapsed_time(e1) / back_to_back)
         ms = statistics.median(times)
         fl = prefill_flops(self.cfg, self.layers, tokens)
-        return {"value": round(tokens / (ms / 1e3), 1), "tokens": tokens, "ms": round(ms, 3),
-                "frac": round(fl["total"] / (ms / 1e3) / (self.tf_peak * 1e12), 4),
-                "tflops": round(fl["total"] / (ms / 1e3) / 1e12, 1), "peak_tflops": self.tf_peak, "of": self.peak_src,
-                "trials": len(times)}
+        out = {"value": round(tokens / (ms / 1e3), 1), "tokens": tokens, "ms": round(ms, 3),
+               "frac": round(fl["total"] / (ms / 1e3) / (self.tf_peak * 1e12), 4),
+               "tflops": round(fl["total"] / (ms / 1e3) / 1e12, 1), "peak_tflops": self.tf_peak, "of": self.peak_src,
+               "trials": len(times)}
+        if b2b:
+            m2 = statistics.median(b2b)
+            out.update({"back_to_back_ms": round(m2, 3), "back_to_back_steps": back_to_back,
+                        "back_to_back_frac": round(fl["total"] / (m2 / 1e3) / (self.tf_peak * 1e12), 4)})
+        return out
 
     # ------------------------------------------------------------------ decode through the step function
     def decode(self, B: int, steps: int, warmup: int, trials: int = 3, clocks: bool = False) -> Dict[str, Any]:

@@ -377,6 +377,7 @@ class ModelRunner:
         try:
             ctx = self.build_context(entries)
             self.logit_slots = ctx.logit_slots
+            ops.profile_mark("plan")     # what came before is the host laying out the step
             with ops.kernels().pinned_stream():
                 logits = self.model.forward(ctx)
         except Exception:

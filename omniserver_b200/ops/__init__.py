@@ -636,4 +636,12 @@ def kernels():
     return _KERNELS
 
 
-__all__ = ["kernels", "CudaKernels", "KernelError", "KernelLibraryError", "library"]
+def profile_mark(what: str) -> None:
+    """While a profile is being taken (``CudaKernels.start_profile``), what ran since the event before is counted
+    under ``what``; otherwise nothing happens."""
+    k = _KERNELS
+    if k is not None and getattr(k, "_prof", None) is not None:
+        k._mark(what)
+
+
+__all__ = ["kernels", "CudaKernels", "KernelError", "KernelLibraryError", "library", "profile_mark"]
