@@ -347,6 +347,9 @@ class CudaKernels(PersistentDecodeOps):
                "gate_up_silu: x [M,K], w [2I,K]")
         M, K = x.shape
         N = w.shape[0]
+        if self.stream_linear_decode and out_dtype == torch.bfloat16 and self.can_stream_linear(x, w, None):
+            # a few rows: the weight-streaming kernel (as fast as the skinny one at 8 rows, ahead of it from 9)
+            return self.stream_linear(x, w, None, gated=True)
         if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= self.SKINNY_MAX_ROWS and K % 8 == 0
                 and out_dtype in (torch.bfloat16, torch.float32)):
             y = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)

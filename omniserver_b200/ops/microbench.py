@@ -67,6 +67,20 @@ def bench_gemm(args, K, dev, peak) -> None:
                 us = graph_time_us(lambda i: K.stream_linear(x, ws[i], None, gated=bool(mode)), n_rot)
                 gbs = N * Kd * 2 / us / 1e3
                 cols.append(f"streaming: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+            if name == "qkv" and K.can_stream_linear(x, ws[0], None):
+                # with the add + norm in front of it: inside the kernel, or as a kernel of its own
+                res = torch.randn(M, Kd, device=dev)
+                gm = torch.ones(Kd, device=dev, dtype=torch.bfloat16)
+
+                def apart(i):
+                    h, _ = K.add_rmsnorm(x, res, gm, 1e-6, torch.bfloat16)
+                    K.stream_linear(h, ws[i], None)
+                us2 = graph_time_us(apart, n_rot)
+                txt = f"norm + streaming: {us2:7.1f} us"
+                if K.can_stream_linear(x, ws[0], None, gm):
+                    us1 = graph_time_us(lambda i: K.stream_linear(x, ws[i], None, norm=(res, gm, 1e-6)), n_rot)
+                    txt = f"norm inside: {us1:7.1f} us | " + txt
+                cols.append(txt)
             if not mode:
                 us = graph_time_us(lambda i: torch.mm(x, ws[i].t()), n_rot)
                 cols.append(f"library: {us:7.1f} us {N * Kd * 2 / us / 1e3:6.0f} GB/s")
@@ -167,12 +181,27 @@ def bench_ffn_fused(args, K, dev, peak) -> None:
             gbs = 3 * I * H * 2 / us / 1e3
             cols.append(f"persistent: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
 
+        if K.can_stream_linear(x, wgu[0], None, gm):
+            def two(i):
+                h, _ = K.stream_linear(x, wgu[i], None, norm=(res, gm, 1e-6), gated=True)
+                K.linear(h, wd[i], None, torch.bfloat16)
+            us = graph_time_us(two, n_rot)
+            gbs = 3 * I * H * 2 / us / 1e3
+            cols.append(f"norm inside gate/up, down: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+
         def separate(i):
             h, _ = K.add_rmsnorm(x, res, gm, 1e-6, torch.bfloat16)
             K.linear(K.gate_up_silu(h, wgu[i], torch.bfloat16), wd[i], None, torch.bfloat16)
         us = graph_time_us(separate, n_rot)
         gbs = 3 * I * H * 2 / us / 1e3
         cols.append(f"three kernels: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
+
+        def separate_lib(i):
+            h, _ = K.add_rmsnorm(x, res, gm, 1e-6, torch.bfloat16)
+            torch.mm(K.gate_up_silu(h, wgu[i], torch.bfloat16), wd[i].t())
+        us = graph_time_us(separate_lib, n_rot)
+        gbs = 3 * I * H * 2 / us / 1e3
+        cols.append(f"with the library's down: {us:6.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
         print(f"ffn half B={B:3d} H={H} I={I} | " + " | ".join(cols), flush=True)
 
 

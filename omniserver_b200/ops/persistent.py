@@ -75,12 +75,35 @@ class PersistentDecodeOps:
         self._ok(rc, "stream_linear")
         return (y, res_out) if norm is not None else y
 
+    #: rows up to this length are normalised inside ``stream_linear``; longer ones by the norm kernel in front of it
+    STREAM_NORM_INSIDE_WIDTH = 2048
+
+    def prefer_norm_inside(self, x: torch.Tensor) -> bool:
+        """Whether add + norm are better done inside ``stream_linear`` than by the norm kernel in front of it.
+        Measured on a B200 with the q/k/v projection behind the norm (us, 1 / 8 / 16 rows): width 1,536: 3.9 / 4.2 /
+        6.8 inside against 5.2 / 4.6 / 7.6 apart; width 3,584: 13.6 / 15.1 / 25.1 against 12.2 / 13.2 / 15.7; width
+        8,192: 46 / 49 / - against 35 / 36 / 37. Rows of up to 2,048 elements are normalised out of registers in one
+        pass by every CTA; longer ones take two passes and leave less shared memory for the weight tiles."""
+        return x.shape[1] <= self.STREAM_NORM_INSIDE_WIDTH
+
     def can_stream_ffn(self, x: torch.Tensor, norm_weight: torch.Tensor, w_gate_up: torch.Tensor,
                        w_down: torch.Tensor) -> bool:
         """Whether ``stream_ffn`` takes these operands (else: norm, ``gate_up_silu``, ``linear``)."""
         return (self.fuse_ffn_decode and x.dim() == 2 and 0 < x.shape[0] <= self.STREAM_MAX_ROWS
                 and x.dtype == norm_weight.dtype == w_gate_up.dtype == w_down.dtype == torch.bfloat16
                 and bool(self.lib.osb_stream_ffn_supported(x.shape[0], x.shape[1], w_down.shape[1])))
+
+    #: ``stream_ffn`` is preferred over the separate kernels up to these sizes
+    STREAM_FFN_PREFER_ROWS = 8
+    STREAM_FFN_PREFER_WIDTH = 4096
+
+    def prefer_stream_ffn(self, x: torch.Tensor) -> bool:
+        """Whether the one-kernel feed-forward half is the faster form for these rows. Measured on a B200 against
+        add + norm, gate/up with the activation, down as three streaming kernels (us, 1 / 8 / 16 rows): width 1,536:
+        17.6 / 18.5 / 25.4 against 20.2 / 19.7 / 21.8; width 3,584: 70 / 73 / 94 against 78 / 78 / 82; width 8,192:
+        296 / 299 / - against 230 / 235 / 239. The one kernel keeps the normalised rows in shared memory beside its
+        weight tiles: with 16 rows (two column tiles) or rows of 8,192 elements too little is left for the tiles."""
+        return x.shape[0] <= self.STREAM_FFN_PREFER_ROWS and x.shape[1] <= self.STREAM_FFN_PREFER_WIDTH
 
     def stream_ffn(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                    w_gate_up: torch.Tensor, w_down: torch.Tensor, wait_limit: int = 0, bar_extra: int = 0

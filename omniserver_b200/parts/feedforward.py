@@ -33,10 +33,11 @@ class SwiGLU(FeedForward):
 
     def forward_prenorm(self, ctx: Any, x: torch.Tensor, residual, norm):
         # a few rows (a decode step): norm, both projections and the activation as one kernel, if the
-        # norm is one that the kernel computes
+        # norm is one that the kernel computes and the rows are few and short enough for that form to be the faster
         k = ops.kernels()
         rms = norm.rms_operands()
-        if rms is not None and k.can_stream_ffn(x, rms[0], self.gate_up.weight, self.down.weight):
+        if (rms is not None and k.can_stream_ffn(x, rms[0], self.gate_up.weight, self.down.weight)
+                and k.prefer_stream_ffn(x)):
             return k.stream_ffn(x, residual, rms[0], rms[1], self.gate_up.weight, self.down.weight)
         return super().forward_prenorm(ctx, x, residual, norm)
 

@@ -36,7 +36,7 @@ class RMSNorm(Norm):
     def fused_linear(self, x, residual, linear, out_dtype):
         k = ops.kernels()
         if (out_dtype == torch.bfloat16 and k.fuse_norm_linear_decode
-                and k.can_stream_linear(x, linear.weight, linear.bias, self.weight)):
+                and k.can_stream_linear(x, linear.weight, linear.bias, self.weight) and k.prefer_norm_inside(x)):
             return k.stream_linear(x, linear.weight, linear.bias, norm=(residual, self.weight, self.eps))
         return None
 

@@ -508,6 +508,25 @@ def test_paged_attention_mixed_batch(dtype, nh, nkv, hd, ps, window):
     assert torch.allclose(got, want, **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd", list(range(16, 257, 16)))
+def test_paged_attention_every_head_size(dtype, hd):
+    """Head sizes in steps of 16 up to 256, prompt portions beside decode tokens with long contexts: each size is
+    either computed right by whichever kernel takes it, or refused with an error that says so."""
+    nh, nkv, ps = 6, 2, 16
+    q_lens, kv_lens = [150, 1, 2, 1, 130], [150, 700, 260, 129, 400]
+    case = _paged_case(q_lens, kv_lens, nh, nkv, hd, ps, dtype, seed=hd)
+    try:
+        got, want = _run_attn(case, nh, nkv, hd, None, dtype)
+    except Exception as e:      # a refusal names the size
+        assert "head" in str(e).lower() or "unsupported" in str(e).lower(), e
+        return
+    if dtype == torch.bfloat16:   # the bound that follows from rounding P and the output to bf16 (one or two of
+        _assert_attn_close(got, want, case, nh, nkv, hd, None, f"head size {hd}")   # 10^5 values pass the flat one by a hair)
+    else:
+        assert torch.allclose(got, want, **tol(dtype))
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(12, 2, 128, 16), (28, 4, 128, 16), (6, 3, 48, 8), (4, 4, 64, 64), (40, 2, 32, 16),
                                           (8, 1, 256, 16), (16, 2, 128, 16), (7, 1, 128, 32), (8, 2, 64, 4), (12, 2, 128, 8),
                                           (6, 6, 64, 2), (24, 2, 128, 16)])
