@@ -32,6 +32,7 @@ class CudaKernels(PersistentDecodeOps):
     #: rows up to which the bf16 weight-streaming GEMM is used instead of the tiled tensor-core GEMM
     #: (measured on B200: it wins up to 16 rows, the library GEMM from 32 rows on)
     SKINNY_MAX_ROWS = 16
+    SKINNY_TWO_TILE_MAX_ELEMS = 1 << 25   # 9 to 16 rows: matrices from 64 MB on go to the library
     #: splits of a request's keys that one thread-block cluster of the decode attention merges
     CLUSTER_MAX_SPLITS = 8
 
@@ -285,7 +286,9 @@ class CudaKernels(PersistentDecodeOps):
                      ) -> torch.Tensor:
         M, K = x.shape
         N = w.shape[0]
-        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0:
+        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and (M <= 8 or N * K < self.SKINNY_TWO_TILE_MAX_ELEMS or N % 8 != 0):
+            # (with 9 to 16 rows the kernel's two-column-tile form streams a large matrix, the head over the
+            # vocabulary, at 0.71 to 0.74 of the copy rate where the library reaches 0.93)
             return self.gemm_skinny(x, w, bias, out_dtype)
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows and K % 8 == 0 and x.data_ptr() % 16 == 0
                 and w.data_ptr() % 16 == 0):
