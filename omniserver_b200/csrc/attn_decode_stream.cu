@@ -157,38 +157,82 @@ __device__ __forceinline__ void attn_stream_unit(
     prefetch_block(warp + NW, pg1);
     prefetch_block(warp + 2 * NW, pg2);
   }
+  // Before the wait: what the host or an earlier kernel of the step wrote (the slot of the new token, the rotary
+  // tables). After it: this step's q, k, v, every load issued before any is used (a thread has at most one item of
+  // each kind), so that the whole preparation costs one round trip to the L2 and not one per piece.
+  constexpr int cpr = HD >> 3;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  const bool do_kv = fr.cos_t != nullptr && split == last_split;
+  const int half = fr.rot >> 1, hc = half >> 3;
+  const bool rotate_here = fr.cos_t != nullptr && (half & 7) == 0;   // q rotated on its way into shared memory
+  const int per_row = rotate_here ? hc + (cpr - 2 * hc) : cpr;       // this thread's piece of the q tile: (row, piece)
+  const int qi_r = tid / per_row, qi_c = tid - qi_r * per_row;
+  const bool q_item = tid < 8 * per_row, q_live = q_item && qi_r < rows, q_rot = rotate_here && q_live && qi_c < hc;
+  float4 qc0 = make_float4(0.f, 0.f, 0.f, 0.f), qc1 = qc0, qs0 = qc0, qs1 = qc0;
+  float k_cs = 0.0f, k_sn = 0.0f;
+  int slot = -1;
+  if (q_rot) {
+    const float* cs = fr.cos_t + (size_t)q0 * half + qi_c * 8;
+    const float* sn = fr.sin_t + (size_t)q0 * half + qi_c * 8;
+    qc0 = *reinterpret_cast<const float4*>(cs);
+    qc1 = *reinterpret_cast<const float4*>(cs + 4);
+    qs0 = *reinterpret_cast<const float4*>(sn);
+    qs1 = *reinterpret_cast<const float4*>(sn + 4);
+  }
+  if (do_kv) {
+    slot = fr.slot_map[q0];
+    if (tid < half) {
+      k_cs = fr.cos_t[(size_t)q0 * half + tid];
+      k_sn = fr.sin_t[(size_t)q0 * half + tid];
+    }
+  }
   wait_for_q();   // until here nothing of this step's q, k, v was touched
-  if (fr.cos_t != nullptr && split == last_split) {
-    const int slot = fr.slot_map[q0];
+  const bf16* qsrc = q + (size_t)q0 * q_row_stride + (size_t)(head0 + (q_item ? qi_r : 0)) * HD;
+  uint4 qa = zero4, qb = zero4;
+  if (q_live) {
+    if (q_rot) {
+      qa = *reinterpret_cast<const uint4*>(qsrc + qi_c * 8);
+      qb = *reinterpret_cast<const uint4*>(qsrc + half + qi_c * 8);
+    } else {
+      qa = *reinterpret_cast<const uint4*>(qsrc + (rotate_here ? 2 * hc + (qi_c - hc) : qi_c) * 8);
+    }
+  }
+  bf16 kx1 = __float2bfloat16_rn(0.0f), kx2 = kx1, kpl = kx1, vv = kx1;
+  if (do_kv) {
+    const bf16* ksrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + kvh) * HD;
+    const bf16* vsrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + nkv + kvh) * HD;
+    if (tid < half) {
+      kx1 = ksrc[tid];
+      kx2 = ksrc[tid + half];
+    }
+    if (fr.rot + tid < HD) kpl = ksrc[fr.rot + tid];
+    if (tid < HD) vv = vsrc[tid];
+  }
+  if (do_kv) {
+    // the new token's key (rotated) and value: into shared memory for this CTA's own block, and, by one CTA of the
+    // kv head, into the cache page
     const int page = slot >> log2ps, off = slot & ps_mask;
-    const bool store = ht == 0 && page >= 0 && page < num_pages;   // one CTA of the kv head stores
+    const bool store = ht == 0 && page >= 0 && page < num_pages;
     const size_t dst = store ? ((((size_t)page * nkv + kvh) << log2ps) + off) * HD : 0;
     bf16* kd = const_cast<bf16*>(kc) + dst;
     bf16* vd = const_cast<bf16*>(vc) + dst;
-    const bf16* ksrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + kvh) * HD;
-    const bf16* vsrc = q + (size_t)q0 * q_row_stride + (size_t)(nh + nkv + kvh) * HD;
-    const int half = fr.rot >> 1;
-    const float* cs = fr.cos_t + (size_t)q0 * half;
-    const float* sn = fr.sin_t + (size_t)q0 * half;
-    for (int d = tid; d < half; d += NT) {
-      const float x1 = __bfloat162float(ksrc[d]), x2 = __bfloat162float(ksrc[d + half]);
-      const bf16 a = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]), b = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
-      ks[d] = a;
-      ks[d + half] = b;
+    if (tid < half) {
+      const float x1 = __bfloat162float(kx1), x2 = __bfloat162float(kx2);
+      const bf16 ra = __float2bfloat16_rn(x1 * k_cs - x2 * k_sn), rb = __float2bfloat16_rn(x2 * k_cs + x1 * k_sn);
+      ks[tid] = ra;
+      ks[tid + half] = rb;
       if (store) {
-        kd[d] = a;
-        kd[d + half] = b;
+        kd[tid] = ra;
+        kd[tid + half] = rb;
       }
     }
-    for (int d = fr.rot + tid; d < HD; d += NT) {
-      const bf16 a = ksrc[d];
-      ks[d] = a;
-      if (store) kd[d] = a;
+    if (fr.rot + tid < HD) {
+      ks[fr.rot + tid] = kpl;
+      if (store) kd[fr.rot + tid] = kpl;
     }
-    for (int d = tid; d < HD; d += NT) {
-      const bf16 a = vsrc[d];
-      vs[d] = a;
-      if (store) vd[d] = a;
+    if (tid < HD) {
+      vs[tid] = vv;
+      if (store) vd[tid] = vv;
     }
   }
   if (!early) {
@@ -198,64 +242,41 @@ __device__ __forceinline__ void attn_stream_unit(
   }
 
   // the group's query rows into shared memory, rotated on the way in the fused rotary form
-  {
-    constexpr int cpr = HD >> 3;
-    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    const bool rotate_here = fr.cos_t != nullptr && ((fr.rot >> 1) & 7) == 0;
-    if (rotate_here) {
-      const int half = fr.rot >> 1, hc = half >> 3;
-      const int per_row = hc + (cpr - 2 * hc);
-      const float* cs = fr.cos_t + (size_t)q0 * half;
-      const float* sn = fr.sin_t + (size_t)q0 * half;
-      for (int i = tid; i < 8 * per_row; i += NT) {
-        const int r = i / per_row, cc0 = i - r * per_row;
-        bf16* dst = qs + r * stride;
-        const bf16* src = q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * HD;
-        if (cc0 >= hc) {
-          const int cc = 2 * hc + (cc0 - hc);
-          *reinterpret_cast<uint4*>(dst + cc * 8) = r < rows ? *reinterpret_cast<const uint4*>(src + cc * 8) : zero4;
-          continue;
-        }
-        uint4 a = zero4, b = zero4;
-        if (r < rows) {
-          a = *reinterpret_cast<const uint4*>(src + cc0 * 8);
-          b = *reinterpret_cast<const uint4*>(src + half + cc0 * 8);
-          const float4 c0 = *reinterpret_cast<const float4*>(cs + cc0 * 8), c1 = *reinterpret_cast<const float4*>(cs + cc0 * 8 + 4);
-          const float4 s0 = *reinterpret_cast<const float4*>(sn + cc0 * 8), s1 = *reinterpret_cast<const float4*>(sn + cc0 * 8 + 4);
-          const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-          const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-          __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&a);
-          __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&b);
+  if (q_item) {
+    bf16* dstq = qs + qi_r * stride;
+    if (q_rot) {
+      const float cv[8] = {qc0.x, qc0.y, qc0.z, qc0.w, qc1.x, qc1.y, qc1.z, qc1.w};
+      const float sv[8] = {qs0.x, qs0.y, qs0.z, qs0.w, qs1.x, qs1.y, qs1.z, qs1.w};
+      __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&qa);
+      __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&qb);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 x1 = __bfloat1622float2(pa[e]), x2 = __bfloat1622float2(pb[e]);
-            pa[e] = __floats2bfloat162_rn(x1.x * cv[2 * e] - x2.x * sv[2 * e], x1.y * cv[2 * e + 1] - x2.y * sv[2 * e + 1]);
-            pb[e] = __floats2bfloat162_rn(x2.x * cv[2 * e] + x1.x * sv[2 * e], x2.y * cv[2 * e + 1] + x1.y * sv[2 * e + 1]);
-          }
-        }
-        *reinterpret_cast<uint4*>(dst + cc0 * 8) = a;
-        *reinterpret_cast<uint4*>(dst + half + cc0 * 8) = b;
+      for (int e = 0; e < 4; ++e) {
+        const float2 x1 = __bfloat1622float2(pa[e]), x2 = __bfloat1622float2(pb[e]);
+        pa[e] = __floats2bfloat162_rn(x1.x * cv[2 * e] - x2.x * sv[2 * e], x1.y * cv[2 * e + 1] - x2.y * sv[2 * e + 1]);
+        pb[e] = __floats2bfloat162_rn(x2.x * cv[2 * e] + x1.x * sv[2 * e], x2.y * cv[2 * e + 1] + x1.y * sv[2 * e + 1]);
       }
+      *reinterpret_cast<uint4*>(dstq + qi_c * 8) = qa;
+      *reinterpret_cast<uint4*>(dstq + half + qi_c * 8) = qb;
+    } else if (rotate_here && qi_c >= hc) {
+      *reinterpret_cast<uint4*>(dstq + (2 * hc + (qi_c - hc)) * 8) = qa;   // zeros in rows beyond the group's heads
+    } else if (rotate_here) {
+      // a row beyond the group's heads in the rotated span: zeros in both halves
+      *reinterpret_cast<uint4*>(dstq + qi_c * 8) = zero4;
+      *reinterpret_cast<uint4*>(dstq + half + qi_c * 8) = zero4;
     } else {
-      for (int i = tid; i < 8 * cpr; i += NT) {
-        const int r = i / cpr, cc = i - r * cpr;
-        uint4 v = zero4;
-        if (r < rows) v = *reinterpret_cast<const uint4*>(q + (size_t)q0 * q_row_stride + (size_t)(head0 + r) * HD + cc * 8);
-        *reinterpret_cast<uint4*>(qs + r * stride + cc * 8) = v;
-      }
-      if (fr.cos_t != nullptr) {  // a rotated span that is no multiple of 16: rotate in place
-        __syncthreads();
-        const int half = fr.rot >> 1;
-        const float* cs = fr.cos_t + (size_t)q0 * half;
-        const float* sn = fr.sin_t + (size_t)q0 * half;
-        for (int i = tid; i < rows * half; i += NT) {
-          const int r = i / half, d = i - r * half;
-          bf16* row = qs + r * stride;
-          const float x1 = __bfloat162float(row[d]), x2 = __bfloat162float(row[d + half]);
-          row[d] = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]);
-          row[d + half] = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
-        }
-      }
+      *reinterpret_cast<uint4*>(dstq + qi_c * 8) = qa;
+    }
+  }
+  if (fr.cos_t != nullptr && !rotate_here) {  // a rotated span that is no multiple of 16: rotate in place
+    __syncthreads();
+    const float* cs = fr.cos_t + (size_t)q0 * half;
+    const float* sn = fr.sin_t + (size_t)q0 * half;
+    for (int i = tid; i < rows * half; i += NT) {
+      const int r = i / half, d = i - r * half;
+      bf16* row = qs + r * stride;
+      const float x1 = __bfloat162float(row[d]), x2 = __bfloat162float(row[d + half]);
+      row[d] = __float2bfloat16_rn(x1 * cs[d] - x2 * sn[d]);
+      row[d + half] = __float2bfloat16_rn(x2 * cs[d] + x1 * sn[d]);
     }
   }
   __syncthreads();
