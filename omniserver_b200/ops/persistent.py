@@ -95,13 +95,13 @@ class PersistentDecodeOps:
 
     #: ``stream_ffn`` is preferred over the separate kernels up to these sizes
     STREAM_FFN_PREFER_ROWS = 8
-    STREAM_FFN_PREFER_WIDTH = 4096
+    STREAM_FFN_PREFER_WIDTH = 3584
 
     def prefer_stream_ffn(self, x: torch.Tensor) -> bool:
         """Whether the one-kernel feed-forward half is the faster form for these rows. Measured on a B200 against
         add + norm, gate/up with the activation, down as three streaming kernels (us, 1 / 8 / 16 rows): width 1,536:
-        17.6 / 18.5 / 25.4 against 20.2 / 19.7 / 21.8; width 3,584: 70 / 73 / 94 against 78 / 78 / 82; width 8,192:
-        296 / 299 / - against 230 / 235 / 239. The one kernel keeps the normalised rows in shared memory beside its
+        17.6 / 18.5 / 25.4 against 20.2 / 19.7 / 21.8; width 3,584: 70 / 73 / 94 against 78 / 78 / 82; width 4,096 (and
+        14,336 between): - / 69.5 / - against - / 65.2 / -; width 8,192: 296 / 299 / - against 230 / 235 / 239. The one kernel keeps the normalised rows in shared memory beside its
         weight tiles: with 16 rows (two column tiles) or rows of 8,192 elements too little is left for the tiles."""
         return x.shape[0] <= self.STREAM_FFN_PREFER_ROWS and x.shape[1] <= self.STREAM_FFN_PREFER_WIDTH
 
