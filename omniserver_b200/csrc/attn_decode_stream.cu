@@ -579,10 +579,13 @@ __global__ void __launch_bounds__(NT, 1) attn_decode_stream_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     int q_row_stride, const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
-    const int* __restrict__ decode_index, int* __restrict__ counters, int nh, int nkv, int log2ps, int num_pages,
-    float scale_log2, int window, int chunk, int nsplits, FusedRope fr, int* __restrict__ err) {
+    const int* __restrict__ decode_index, const int* __restrict__ order, int* __restrict__ counters, int nh, int nkv,
+    int log2ps, int num_pages, float scale_log2, int window, int chunk, int nsplits, FusedRope fr, int* __restrict__ err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  attn_stream_unit<HD, CLUSTER>([] { pdl_wait(); }, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.y, smem_raw, out, part_o,
+  // CTAs are handed to the SMs in the order of their indices: `order` (the requests by falling length) lets the long
+  // ones start first, so that, when there are more CTAs than SMs, the short ones fill the gaps at the end
+  const int s = order != nullptr ? order[blockIdx.z] : (int)blockIdx.z;
+  attn_stream_unit<HD, CLUSTER>([] { pdl_wait(); }, blockIdx.x, blockIdx.y, s, gridDim.y, smem_raw, out, part_o,
                                        part_ml, q, q_row_stride, kc, vc, block_table, bt_stride, cu_q, seq_lens,
                                        decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk,
                                        nsplits, fr, err);
@@ -590,8 +593,8 @@ __global__ void __launch_bounds__(NT, 1) attn_decode_stream_kernel(
 
 template <int HD>
 int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_stride, const bf16* kc, const bf16* vc,
-           const int* bt, int bt_stride, const int* cu_q, const int* seq_lens, const int* decode_index, int* counters,
-           int S, int nh, int nkv, int log2ps, int num_pages, float scale_log2, int window, int chunk, int nsplits,
+           const int* bt, int bt_stride, const int* cu_q, const int* seq_lens, const int* decode_index, const int* order,
+           int* counters, int S, int nh, int nkv, int log2ps, int num_pages, float scale_log2, int window, int chunk, int nsplits,
            cudaStream_t stream, FusedRope fr, bool use_cluster, int* err) {
   // q rows, the warps' (max, sum) and outputs, the CTA's own; the last CTA's table of (max, sum) of all splits
   size_t smem = (size_t)16 * (HD + 8) * sizeof(bf16) + (size_t)(NW + 1) * 16 * 2 * sizeof(float) +
@@ -604,14 +607,15 @@ int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_st
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     rc = osb_launch_cluster(k, grid, dim3(NT), smem, stream, nsplits, out, part_o, part_ml, q, q_row_stride, kc, vc, bt,
-                            bt_stride, cu_q, seq_lens, decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2,
+                            bt_stride, cu_q, seq_lens, decode_index, order, counters, nh, nkv, log2ps, num_pages, scale_log2,
                             window, chunk, nsplits, fr, err);
   } else {
     auto k = attn_decode_stream_kernel<HD, false>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     rc = osb_launch(k, grid, dim3(NT), smem, stream, out, part_o, part_ml, q, q_row_stride, kc, vc, bt, bt_stride, cu_q,
-                    seq_lens, decode_index, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk, nsplits, fr, err);
+                    seq_lens, decode_index, order, counters, nh, nkv, log2ps, num_pages, scale_log2, window, chunk, nsplits, fr,
+                    err);
   }
   return rc ? rc : osb_last_error();
 }
@@ -623,9 +627,11 @@ int launch(bf16* out, float* part_o, float* part_ml, const bf16* q, int q_row_st
 // counters as for osb_paged_attn_bf16; the CTA of a group's last split then waits (bounded; error 141 in *err) for the
 // group's other splits, so the grid (nsplits x kv heads x head tiles x S) must fit on the GPU at once: a larger one is
 // refused with OSB_ERR_TOO_LARGE (n_decode: how many of the S requests bring one token; 0: all of them).
+// order: null, or a permutation of 0..S-1: the requests in the order in which their CTAs are to start.
 OSB_API int osb_attn_decode_stream(void* out, const void* q, int q_row_stride, const void* k_cache, const void* v_cache,
                                    const int* block_table, int bt_stride, const int* cu_q, const int* seq_lens,
-                                   const int* decode_index, int S, int nh, int nkv, int hd, int page_size, int num_pages,
+                                   const int* decode_index, const int* order, int S, int nh, int nkv, int hd, int page_size,
+                                   int num_pages,
                                    float scale, int window, float* part_o, float* part_ml, int* counters, int chunk,
                                    int nsplits, const float* rope_cos, const float* rope_sin, const int* rope_slot_map,
                                    int rope_rot, int use_cluster, int n_decode, int* err, cudaStream_t stream) {
@@ -659,9 +665,9 @@ OSB_API int osb_attn_decode_stream(void* out, const void* q, int q_row_stride, c
   const float scale_log2 = scale * LOG2E;
   if (hd == 64)
     return launch<64>((bf16*)out, part_o, part_ml, (const bf16*)q, q_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
-                      block_table, bt_stride, cu_q, seq_lens, decode_index, counters, S, nh, nkv, log2ps, num_pages,
+                      block_table, bt_stride, cu_q, seq_lens, decode_index, order, counters, S, nh, nkv, log2ps, num_pages,
                       scale_log2, window, chunk, nsplits, stream, fr, use_cluster != 0, err);
   return launch<128>((bf16*)out, part_o, part_ml, (const bf16*)q, q_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
-                     block_table, bt_stride, cu_q, seq_lens, decode_index, counters, S, nh, nkv, log2ps, num_pages,
+                     block_table, bt_stride, cu_q, seq_lens, decode_index, order, counters, S, nh, nkv, log2ps, num_pages,
                      scale_log2, window, chunk, nsplits, stream, fr, use_cluster != 0, err);
 }

@@ -68,6 +68,7 @@ class StepContext:
         self.page_size = 0
         self.logit_slots: Optional[torch.Tensor] = None    # [wanted rows]: the request slot of each logits row
         self.decode_index: Optional[torch.Tensor] = None   # [S]: index among requests bringing one token, else -1
+        self.attn_order: Optional[torch.Tensor] = None     # [S]: the requests by falling length (attention starts long ones first)
         self.n_decode = self.n_multi = 0
         self.scratch: Dict[str, torch.Tensor] = {}         # per-step scratch buffers shared by the layers
         self.advance_state = True                          # False: a dry run that must not move cursors
@@ -249,6 +250,7 @@ class ModelRunner:
             ("pos_mode", pos_mode), ("logit_rows", np.asarray(logit_rows, dtype=np.int32)),
             ("override_rows", np.asarray(ov_rows, dtype=np.int32)), ("decode_index", decode_index),
             ("token_src", tok_src), ("logit_slots", np.asarray(logit_slots, dtype=np.int32)),
+            ("attn_order", np.argsort(-np.asarray(kv_lens), kind="stable").astype(np.int32)),
         ]
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
@@ -301,6 +303,7 @@ class ModelRunner:
             ("positions", np.zeros(self.position_columns * S, dtype=np.int32)), ("pos_mode", np.ones(S, dtype=np.int32)),
             ("logit_rows", ar[:S]), ("override_rows", np.zeros(0, dtype=np.int32)), ("decode_index", ar[:S]),
             ("token_src", np.where(from_dev, slots, -1).astype(np.int32)), ("logit_slots", slots),
+            ("attn_order", np.argsort(-cursors, kind="stable").astype(np.int32)),
         ]
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
@@ -341,6 +344,7 @@ class ModelRunner:
         ctx.max_q_len, ctx.max_kv_len = max(plan["q_lens"]), max(plan["kv_lens"])
         ctx.page_size = self.cache.page_size
         ctx.decode_index = seg("decode_index")
+        ctx.attn_order = seg("attn_order")      # the requests by falling length: long ones start first
         if self.last_token is not None:
             ctx.token_src, ctx.last_token = seg("token_src"), self.last_token
         ctx.logit_slots = seg("logit_slots")

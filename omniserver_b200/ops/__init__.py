@@ -424,7 +424,8 @@ class CudaKernels(PersistentDecodeOps):
                         max_q_len: int, max_kv_len: int, out_dtype: torch.dtype,
                         decode_index: Optional[torch.Tensor] = None, n_decode: int = 0, n_multi: int = 0,
                         exact: bool = False, scratch: Optional[dict] = None,
-                        rope: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None) -> torch.Tensor:
+                        rope: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None,
+                        order: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache.
 
         bfloat16 operands run on the tensor cores (one kernel for requests bringing several tokens,
@@ -435,6 +436,10 @@ class CudaKernels(PersistentDecodeOps):
         ``rope`` = (cos, sin, slot_map, rot_dim): only for steps of single-token requests for which
         ``can_fuse_rope_decode`` holds; the decode kernel then rotates q and k itself and stores the new
         key and value, and the caller must not have called ``rope_kv_write``.
+
+        ``order`` [S] int32: the requests by falling length. The decode kernel starts their CTAs in that order, so
+        that with more CTAs than SMs the short ones fill the gaps at the end (64 requests of 256 to 4,352 keys on 4
+        kv heads: 79 us in the order given, 53 us longest first; 47 us would be the copy rate).
         """
         _cuda_contig("qkv", qkv)
         _cuda_contig("k_cache", k_cache)
@@ -443,6 +448,9 @@ class CudaKernels(PersistentDecodeOps):
             _cuda_contig(n, t, torch.int32)
         T = qkv.shape[0]
         S = seq_lens.shape[0]
+        if order is not None:
+            _cuda_contig("order", order, torch.int32)
+            _check(order.shape == (S,), "paged_attention: order [S]")
         _check(qkv.shape[1] >= nh * hd, "paged_attention: q columns missing")
         _check(k_cache.dim() == 4 and k_cache.shape[1] == nkv and k_cache.shape[3] == hd
                and v_cache.shape == k_cache.shape, "paged_attention: caches [pages, nkv, page_size, hd]")
@@ -495,7 +503,7 @@ class CudaKernels(PersistentDecodeOps):
                     counters = self._scratch(scratch, "attn_counters", n_decode * nkv, qkv.device, zero_int=True)
                 rc = self.lib.osb_attn_decode_stream(
                     _p(out), _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
-                    _p(cu_q), _p(seq_lens), _p(decode_index), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
+                    _p(cu_q), _p(seq_lens), _p(decode_index), _p(order), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
                     ctypes.c_float(scale), win, _p(part_o), _p(part_ml), _p(counters), chunk, nsplits,
                     _p(rope[0] if rope else None), _p(rope[1] if rope else None), _p(rope[2] if rope else None),
                     int(rope[3]) if rope else 0, 1 if (use_cluster and nsplits > 1) else 0, n_decode, _p(self.err_flag(qkv.device)),

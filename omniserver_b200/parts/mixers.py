@@ -81,7 +81,8 @@ class GQAAttention(Mixer):
                               ctx.tok_seq, self.nh, self.nkv, self.hd, self.scale, self.window,
                               ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype, decode_index=ctx.decode_index,
                               n_decode=ctx.n_decode, n_multi=ctx.n_multi, scratch=ctx.scratch,
-                              rope=(rot.cos, rot.sin, ctx.slot_maps[g], rot_dim) if fuse else None)
+                              rope=(rot.cos, rot.sin, ctx.slot_maps[g], rot_dim) if fuse else None,
+                              order=ctx.attn_order)
         return self.out(a, ctx.act_dtype)
 
 

@@ -541,6 +541,26 @@ def test_decode_attention_long_contexts_split_keys(nh, nkv, hd, ps, window):
     assert torch.allclose(got, want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("nh,nkv,batch", [(12, 2, 40), (28, 4, 64), (12, 2, 7)])
+def test_decode_attention_in_a_given_order_of_requests(nh, nkv, batch):
+    """The order in which the requests' CTAs start (longest first, as the engine asks for; any permutation) changes
+    nothing of the result: bitwise the same output as without it, more CTAs than SMs or fewer."""
+    hd, ps = 128, 16
+    g = torch.Generator().manual_seed(batch)
+    kv_lens = [int(x) for x in torch.randint(1, 1200, (batch,), generator=g)]
+    case = _paged_case([1] * batch, kv_lens, nh, nkv, hd, ps, torch.bfloat16, seed=batch + 1)
+    qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = [t.to(DEV) for t in case]
+    ts = torch.arange(batch, device=DEV, dtype=torch.int32)
+    outs = []
+    for order in (None, torch.argsort(-seq_lens.cpu(), stable=True).to(torch.int32), torch.randperm(batch, generator=g).to(torch.int32)):
+        outs.append(K().paged_attention(qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens),
+                                        torch.bfloat16, decode_index=ts, n_decode=batch, n_multi=0, scratch={},
+                                        order=None if order is None else order.to(DEV)).cpu())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    want = REF.paged_attention(*case, nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens), torch.float32)
+    assert torch.allclose(outs[1].float(), want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("batch", [1, 3, 20, 40, 150])
 @pytest.mark.parametrize("stream", [True, False])
 def test_decode_attention_split_and_merge_paths(batch, stream):
