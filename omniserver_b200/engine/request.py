@@ -74,9 +74,11 @@ class Request:
     embed_values: Optional[torch.Tensor] = None
 
 
-@dataclass
+@dataclass(eq=False)
 class Sequence:
-    """Mutable per-request state inside the engine (omniserve/request.py:50-115)."""
+    """Mutable per-request state inside the engine (omniserve/request.py:50-115). A sequence is equal to itself
+    only: the scheduler looks sequences up in its lists every step, and a field-by-field comparison (prompts of
+    thousands of tokens) of 64 running requests cost a millisecond a step."""
 
     request: Request
     prompt_token_ids: List[int] = field(default_factory=list)

@@ -140,8 +140,8 @@ class Scheduler:
         # 1) decodes first, oldest request first; a decode without a page preempts the request
         #    admitted last (which may be itself)
         for seq in sorted([s for s in self.running if s.is_decoding], key=lambda s: s.admit_order):
-            if seq.status != Status.RUNNING or seq not in self.running:
-                continue  # preempted by an older decode
+            if seq.status != Status.RUNNING:
+                continue  # preempted by an older decode (a request that left ``running`` is no longer RUNNING)
             while not fits(seq, 1):
                 victim = max(self.running, key=lambda s: s.admit_order)
                 if victim is seq and len(self.running) == 1:
@@ -153,7 +153,7 @@ class Scheduler:
                 refresh_free()
                 if victim is seq:
                     break
-            if seq.status == Status.RUNNING and seq in self.running:
+            if seq.status == Status.RUNNING:
                 grant(seq, 1)
 
         # 2) prompts in flight, oldest first: as much as the budget and the free pages allow

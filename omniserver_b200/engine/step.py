@@ -69,6 +69,7 @@ class StepContext:
         self.logit_slots: Optional[torch.Tensor] = None    # [wanted rows]: the request slot of each logits row
         self.decode_index: Optional[torch.Tensor] = None   # [S]: index among requests bringing one token, else -1
         self.attn_order: Optional[torch.Tensor] = None     # [S]: the requests by falling length (attention starts long ones first)
+        self.kv_uneven = False                             # the single-token requests' lengths differ much
         self.n_decode = self.n_multi = 0
         self.scratch: Dict[str, torch.Tensor] = {}         # per-step scratch buffers shared by the layers
         self.advance_state = True                          # False: a dry run that must not move cursors
@@ -257,7 +258,8 @@ class ModelRunner:
             segs.append((f"sm{g}", sms[g]))
         return dict(S=S, T=T, segs=segs, q_lens=q_lens, kv_lens=kv_lens, bt_widths=[b.shape[1] for b in bts],
                     n_logit_rows=len(logit_rows), ov_vals=ov_vals, n_decode=int(single.sum()),
-                    explicit_positions=bool((pos_mode == 0).any()))
+                    explicit_positions=bool((pos_mode == 0).any()),
+                    uneven=self._uneven(np.asarray(kv_lens)[single]))
 
     def _plan_decode(self, entries: Sequence[StepEntry], bt_round: int) -> Dict[str, Any]:
         """``_plan`` for a step in which every request brings one token and wants its logits: the same
@@ -310,7 +312,13 @@ class ModelRunner:
             segs.append((f"sm{g}", sms[g].astype(np.int32)))
         kv_lens = (cursors + 1).tolist()
         return dict(S=S, T=S, segs=segs, q_lens=[1] * S, kv_lens=kv_lens, bt_widths=[b.shape[1] for b in bts],
-                    n_logit_rows=S, ov_vals=[], n_decode=S, explicit_positions=False)
+                    n_logit_rows=S, ov_vals=[], n_decode=S, explicit_positions=False, uneven=self._uneven(cursors + 1))
+
+    @staticmethod
+    def _uneven(lens: np.ndarray) -> bool:
+        """Whether the lengths of the requests that bring one token differ much: the longest 1.5 times the mean or
+        more (the attention kernel may then cut the keys into more parts)."""
+        return bool(lens.size >= 2 and lens.max() >= 1.5 * lens.mean())
 
     @staticmethod
     def _layout(segs: List[Tuple[str, np.ndarray]]) -> Tuple[Dict[str, Tuple[int, int]], int]:
@@ -345,6 +353,7 @@ class ModelRunner:
         ctx.page_size = self.cache.page_size
         ctx.decode_index = seg("decode_index")
         ctx.attn_order = seg("attn_order")      # the requests by falling length: long ones start first
+        ctx.kv_uneven = plan["uneven"]
         if self.last_token is not None:
             ctx.token_src, ctx.last_token = seg("token_src"), self.last_token
         ctx.logit_slots = seg("logit_slots")
@@ -429,7 +438,7 @@ class ModelRunner:
     def _graph_step(self, entries: Sequence[StepEntry], copy_logits: bool = True) -> torch.Tensor:
         """A decode step replayed from a CUDA graph: the launch-bound inner loop of generation.
 
-        One graph per (batch size, block-table width bucket). The step's metadata goes into a
+        One graph per (batch size, block-table width bucket, lengths uneven or not). The step's metadata goes into a
         buffer at a fixed address (one host-to-device copy); everything the kernels need that
         changes from step to step is read from that buffer or from the state slots.
         """
@@ -441,7 +450,7 @@ class ModelRunner:
         except Exception:
             self._rollback(entries)
             raise
-        key = (plan["S"], tuple(plan["bt_widths"]))
+        key = (plan["S"], tuple(plan["bt_widths"]), plan["uneven"])   # (the attention's splits depend on the last)
         slot = self._graphs.get(key)
         if slot is not None:
             self._graphs.move_to_end(key)

@@ -425,7 +425,7 @@ class CudaKernels(PersistentDecodeOps):
                         decode_index: Optional[torch.Tensor] = None, n_decode: int = 0, n_multi: int = 0,
                         exact: bool = False, scratch: Optional[dict] = None,
                         rope: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None,
-                        order: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        order: Optional[torch.Tensor] = None, uneven: bool = False) -> torch.Tensor:
         """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache.
 
         bfloat16 operands run on the tensor cores (one kernel for requests bringing several tokens,
@@ -440,6 +440,8 @@ class CudaKernels(PersistentDecodeOps):
         ``order`` [S] int32: the requests by falling length. The decode kernel starts their CTAs in that order, so
         that with more CTAs than SMs the short ones fill the gaps at the end (64 requests of 256 to 4,352 keys on 4
         kv heads: 79 us in the order given, 53 us longest first; 47 us would be the copy rate).
+        ``uneven``: the single-token requests' lengths differ much (the longest is 1.5 times the mean or more): the
+        keys may then be cut into more splits than fill the SMs once (see ``decode_splits``).
         """
         _cuda_contig("qkv", qkv)
         _cuda_contig("k_cache", k_cache)
@@ -487,7 +489,7 @@ class CudaKernels(PersistentDecodeOps):
                 # until that many SMs of one GPC are free at once, which for 3 or 8 cost more than it saved
                 # (measured in full decode steps at batch 8 and 24)
                 chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, self.stream_target_ctas,
-                                                    max_splits=self.stream_max_splits)
+                                                    max_splits=self.stream_max_splits, uneven=uneven)
                 use_cluster = 1 if self.decode_clusters and nsplits in self.stream_cluster_sizes else 0
                 if nsplits > 1 and not use_cluster and nsplits * n_decode * nkv > self.stream_target_ctas:
                     # the CTA that merges waits for the others: the grid must fit on the GPU at once
@@ -563,17 +565,32 @@ class CudaKernels(PersistentDecodeOps):
 
     @staticmethod
     def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 296,
-                      max_splits: int = 128):
+                      max_splits: int = 128, uneven: bool = False):
         """(chunk, nsplits) of the split-key decode kernel. ``target_ctas`` is the number of CTAs the
         GPU holds at once (148 SMs x 2); the keys are cut so that the grid fills them but does not
-        spill into a second wave. Splits end at multiples of ``chunk`` keys (a multiple of 64)."""
+        spill into a second wave. Splits end at multiples of ``chunk`` keys (a multiple of 64).
+
+        ``uneven``: the requests' lengths differ much. With one CTA per (request, kv head) the longest request then
+        sets the time; twice the splits are taken if this estimate says so: a CTA costs its keys plus a fixed part
+        worth about 600 keys, the step takes the longer of the longest CTA and of all CTAs' costs over the SMs, the
+        mean length taken as half the longest (64 requests of 256 to 4,352 keys on 2 kv heads: 48 us with one split,
+        34 us with two, 50 us with four; equal lengths of 2,048: 29 us with one, 35 us with two)."""
         per_split = max(1, n_decode * nkv * ((group + 15) // 16))
         want = max(1, target_ctas // per_split)
         chunk = -(-max(1, max_kv_len) // want)
         chunk = max(128, -(-chunk // 64) * 64)
         while -(-max_kv_len // chunk) > max_splits:   # the kernel merges at most 128 splits (8 in a cluster)
             chunk += 64
-        return chunk, max(1, -(-max_kv_len // chunk))
+        nsplits = max(1, -(-max_kv_len // chunk))
+        if uneven and 2 * nsplits <= max_splits and max_kv_len >= 256 * nsplits:
+            fixed, sms = 600.0, max(1, min(target_ctas, 148))
+
+            def cost(s: int) -> float:
+                return max(max_kv_len / s + fixed, per_split * s * (0.5 * max_kv_len / s + fixed) / sms)
+            if cost(2 * nsplits) < 0.9 * cost(nsplits):
+                chunk2 = max(128, -(-(-(-max_kv_len // (2 * nsplits))) // 64) * 64)
+                return chunk2, max(1, -(-max_kv_len // chunk2))
+        return chunk, nsplits
 
     @staticmethod
     def _scratch(pool: Optional[dict], name: str, numel: int, device, zero_int: bool = False) -> torch.Tensor:

@@ -273,3 +273,19 @@ def test_preemption_of_a_request_with_given_positions_and_embeddings(overlap, tm
     assert outs[b] == want_img and outs[a] == want_txt
     eng.runner.cache.check_invariants()
     assert all(p == 0 for p in eng.runner.cache.pages_in_use())
+
+
+def test_decode_splits_take_uneven_lengths_into_account():
+    """One CTA per (request, kv head) when they fill the SMs and the lengths are alike; twice the splits when the
+    longest request would otherwise set the time; never when the CTAs already come in several waves."""
+    from omniserver_b200.ops import CudaKernels
+    split = CudaKernels.decode_splits
+    assert split(64, 2, 6, 2048, 148, max_splits=16)[1] == 1
+    assert split(64, 2, 6, 2048, 148, max_splits=16, uneven=True)[1] == 2
+    assert split(64, 2, 6, 512, 148, max_splits=16, uneven=True)[1] == 1        # short requests: the fixed part dominates
+    assert split(64, 2, 6, 4352, 148, max_splits=16)[1] == 1
+    chunk, n = split(64, 2, 6, 4352, 148, max_splits=16, uneven=True)
+    assert n == 2 and chunk % 64 == 0 and chunk * n >= 4352
+    assert split(64, 4, 7, 4352, 148, max_splits=16, uneven=True)[1] == 1       # 256 CTAs: two waves already
+    assert split(8, 2, 6, 2048, 148, max_splits=16)[1] == 8
+    assert split(8, 2, 6, 2048, 148, max_splits=16, uneven=True)[1] == 8

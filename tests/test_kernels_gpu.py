@@ -559,6 +559,12 @@ def test_decode_attention_in_a_given_order_of_requests(nh, nkv, batch):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     want = REF.paged_attention(*case, nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens), torch.float32)
     assert torch.allclose(outs[1].float(), want, **tol(torch.bfloat16))
+    # told that the lengths are uneven the kernel may cut the keys into more parts: the same result up to rounding
+    more = K().paged_attention(qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, hd ** -0.5, None, 1, max(kv_lens),
+                               torch.bfloat16, decode_index=ts, n_decode=batch, n_multi=0, scratch={},
+                               order=torch.argsort(-seq_lens.cpu(), stable=True).to(torch.int32).to(DEV), uneven=True).cpu()
+    assert torch.allclose(more.float(), want, **tol(torch.bfloat16))
+    K().check_device_errors()
 
 
 @pytest.mark.parametrize("batch", [1, 3, 20, 40, 150])
