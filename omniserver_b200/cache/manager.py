@@ -102,7 +102,8 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, entry_needs, shared_state_needs: Sequence[StateNeed], page_size: int, num_pages: int,
-                 max_requests: int, dtype: torch.dtype, device, allocate: bool = True, poison_freed: bool = False):
+                 max_requests: int, dtype: torch.dtype, device, allocate: bool = True, poison_freed: bool = False,
+                 spare_slots: int = 0):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = int(page_size)
@@ -142,7 +143,7 @@ class CacheManager:
                 names[s.name] = full
             self._entry_state_names.append(names)
         self._shared_names = [s.name for s in shared_state_needs]
-        self.state = StateSlots(max_requests, fields, device, allocate=allocate)
+        self.state = StateSlots(max_requests, fields, device, allocate=allocate, spare=spare_slots)
         if allocate:
             for g in self.groups:
                 g.storage = torch.zeros((len(g.entries), 2, self.num_pages, g.need.num_kv_heads, self.page_size,
@@ -172,10 +173,11 @@ class CacheManager:
         return {n: self.state.tensors[n] for n in self._shared_names if n in self.state.tensors}
 
     # ------------------------------------------------------------------ request life
-    def begin(self, request_id: str) -> RequestCache:
+    def begin(self, request_id: str, spare: bool = False) -> RequestCache:
+        """``spare``: the slot comes out of the spare ones (a row that is no request)."""
         if request_id in self.requests:
             raise ValueError(f"request {request_id!r} is already live")
-        slot = self.state.alloc()
+        slot = self.state.alloc(spare=spare)
         rc = RequestCache(request_id, slot, tables=[PageTable() for _ in self.groups],
                           first_live=[0 for _ in self.groups])
         self.requests[request_id] = rc

@@ -69,8 +69,9 @@ def build_runner(model_dir: Optional[str] = None, engine_config: Optional[Engine
     else:
         fill_random(model, seed, dtype, device, std=init_std, norm_noise=norm_noise, on_device=random_on_device)
     num_pages = (ec.max_cache_tokens + ec.page_size - 1) // ec.page_size
+    spare = ModelRunner.GRAPH_FILLERS if (ec.cuda_graphs and device.type == "cuda") else 0
     cache = CacheManager(model.entry_needs(), model.shared_state_needs(), ec.page_size, num_pages, ec.max_requests,
-                         dtype, device, allocate=allocate)
+                         dtype, device, allocate=allocate, spare_slots=spare)
     runner = ModelRunner(model, cache, dtype, device, check_device_errors=ec.check_device_errors,
                          use_graphs=ec.cuda_graphs)
     runner.model_config = cfg

@@ -113,6 +113,13 @@ class ModelRunner:
         #: most graphs kept; the one used longest ago goes when another is needed. All graphs allocate from one
         #: memory pool (they replay one after the other on one stream), so their activations share memory.
         self.graph_max_count = 32
+        #: a graph is built when its shape comes by for this many-th time; before that the step is launched kernel
+        #: by kernel (1: build at once)
+        self.graph_min_uses = 1
+        self._graph_seen: Dict[Any, int] = {}
+        #: rows that pad a decode step to the next batch size for which graphs are kept (``_graph_bucket``): requests
+        #: of one token at position 0 on spare state slots, whose page goes back after every step
+        self._filler_ids: List[str] = []
         self._graphs: "collections.OrderedDict[Any, Dict[str, Any]]" = collections.OrderedDict()
         self._graph_pool = None
         model.attach_cache(cache.bindings(), cache.shared_state())
@@ -142,6 +149,10 @@ class ModelRunner:
 
     def end_request(self, request_id: str) -> None:
         self.cache.finish(request_id)
+        if self._filler_ids and len(self.cache.requests) == len(self._filler_ids):
+            for rid in self._filler_ids:       # the last request has gone: so do the rows that padded its steps
+                self.cache.finish(rid)
+            self._filler_ids = []
 
     def reset_request(self, request_id: str, prompt_positions: Optional[np.ndarray] = None,
                       num_prompt_tokens: int = 0) -> None:
@@ -261,7 +272,7 @@ class ModelRunner:
                     explicit_positions=bool((pos_mode == 0).any()),
                     uneven=self._uneven(np.asarray(kv_lens)[single]))
 
-    def _plan_decode(self, entries: Sequence[StepEntry], bt_round: int) -> Dict[str, Any]:
+    def _plan_decode(self, entries: Sequence[StepEntry], bt_round: int, n_real: Optional[int] = None) -> Dict[str, Any]:
         """``_plan`` for a step in which every request brings one token and wants its logits: the same
         result, built with array operations instead of a loop over entries."""
         cache = self.cache
@@ -312,7 +323,8 @@ class ModelRunner:
             segs.append((f"sm{g}", sms[g].astype(np.int32)))
         kv_lens = (cursors + 1).tolist()
         return dict(S=S, T=S, segs=segs, q_lens=[1] * S, kv_lens=kv_lens, bt_widths=[b.shape[1] for b in bts],
-                    n_logit_rows=S, ov_vals=[], n_decode=S, explicit_positions=False, uneven=self._uneven(cursors + 1))
+                    n_logit_rows=S, ov_vals=[], n_decode=S, explicit_positions=False,
+                    uneven=self._uneven((cursors + 1)[:n_real]))      # (rows behind n_real only pad the step)
 
     @staticmethod
     def _uneven(lens: np.ndarray) -> bool:
@@ -363,7 +375,9 @@ class ModelRunner:
         return ctx
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        plan = self._plan(entries)
+        return self._context_of_plan(self._plan(entries))
+
+    def _context_of_plan(self, plan: Dict[str, Any]) -> StepContext:
         offs, total = self._layout(plan["segs"])
         # one staging buffer, one host-to-device copy
         host = torch.empty(total, dtype=torch.int32, pin_memory=self.device.type == "cuda")
@@ -398,6 +412,25 @@ class ModelRunner:
             raise
         self._after_step(entries)
         return logits
+
+    def _planned_step(self, entries: Sequence[StepEntry], plan: Dict[str, Any], fill: Sequence[StepEntry] = ()
+                      ) -> torch.Tensor:
+        """Runs a step whose plan exists (its pages are taken) kernel by kernel. ``fill``: the rows behind those of
+        ``entries`` that only pad the step."""
+        n_real = len(entries)
+        try:
+            ctx = self._context_of_plan(plan)
+            self.logit_slots = ctx.logit_slots[:n_real]
+            ops.profile_mark("plan")
+            with ops.kernels().pinned_stream():
+                logits = self.model.forward(ctx)
+        except Exception:
+            self._rollback(list(entries) + list(fill))
+            raise
+        self._after_step(entries)
+        for e in fill:
+            self.cache.rollback(e.request_id)
+        return logits[:n_real] if fill else logits
 
     def _rollback(self, entries: Sequence[StepEntry]) -> None:
         """A step that failed gives back what it reserved: its requests hold the pages of their cursors again."""
@@ -435,6 +468,39 @@ class ModelRunner:
                 return False
         return True
 
+    #: spare state slots for the rows that pad a decode step (the largest gap between two graph batch sizes)
+    GRAPH_FILLERS = 127
+
+    @staticmethod
+    def _graph_bucket(n: int) -> int:
+        """The batch size of the graph that a decode step of ``n`` requests replays: the next power of two. While
+        the requests of a run end one after the other every batch size comes by once or twice, and building a graph
+        costs as much as five to ten steps; padded, 33 to 63 requests replay the graph of 64 (a decode step of up to
+        64 rows is bound by the weights it streams: the rows that pad it cost next to nothing, their attention is
+        one key long)."""
+        b = 1
+        while b < n:
+            b *= 2
+        return b
+
+    def _fillers(self, entries: Sequence[StepEntry]) -> List[StepEntry]:
+        """Entries that pad ``entries`` to the batch size of a graph, or none (no spare slots, or no page left)."""
+        n = min(self._graph_bucket(len(entries)), self.graph_max_batch) - len(entries)
+        if n <= 0:
+            return []
+        from ..cache.state_slots import OutOfSlots
+        while len(self._filler_ids) < n:
+            rid = "\x00filler%d" % len(self._filler_ids)
+            try:
+                self.cache.begin(rid, spare=True)
+            except OutOfSlots:
+                return []
+            self._filler_ids.append(rid)
+        fill = [StepEntry(r, [0], want=[0]) for r in self._filler_ids[:n]]
+        if not self.cache.can_reserve([(e.request_id, 1) for e in list(entries) + fill]):
+            return []
+        return fill
+
     def _graph_step(self, entries: Sequence[StepEntry], copy_logits: bool = True) -> torch.Tensor:
         """A decode step replayed from a CUDA graph: the launch-bound inner loop of generation.
 
@@ -445,13 +511,26 @@ class ModelRunner:
         k = ops.kernels()
         round_to = self.graph_bt_round
         self._before_step()
+        n_real = len(entries)
+        fill = self._fillers(entries)
+        real, entries = entries, list(entries) + fill      # ``entries``: what runs; ``real``: what the caller sees
         try:
-            plan = self._plan_decode(entries, bt_round=round_to)
+            plan = self._plan_decode(entries, bt_round=round_to, n_real=n_real)
         except Exception:
             self._rollback(entries)
             raise
         key = (plan["S"], tuple(plan["bt_widths"]), plan["uneven"])   # (the attention's splits depend on the last)
         slot = self._graphs.get(key)
+        if slot is None and self.graph_min_uses > 1:
+            # Building a graph costs about as much as ten steps (a warm-up forward, a wait for the device, the
+            # capture): a shape that comes by once or twice, as the batch sizes do while the last requests of a
+            # run end one after the other, is launched kernel by kernel instead.
+            if len(self._graph_seen) > 4096:
+                self._graph_seen.clear()
+            seen = self._graph_seen.get(key, 0) + 1
+            self._graph_seen[key] = seen
+            if seen < self.graph_min_uses:
+                return self._planned_step(real, plan, fill)
         if slot is not None:
             self._graphs.move_to_end(key)
         else:
@@ -503,7 +582,10 @@ class ModelRunner:
         except Exception:
             self._rollback(entries)
             raise
-        self._after_step(entries)
+        self._after_step(real)
+        for e in fill:
+            self.cache.rollback(e.request_id)       # the filler's page goes back; it stays at position 0
         o, n = slot["offs"]["logit_slots"]
-        self.logit_slots = slot["dev"][o:o + n]
-        return slot["logits"].clone() if copy_logits else slot["logits"]
+        self.logit_slots = slot["dev"][o:o + n_real]
+        logits = slot["logits"][:n_real]
+        return logits.clone() if copy_logits else logits

@@ -145,6 +145,7 @@ def test_decode_graphs_across_buckets_and_batch_sizes(dtype, tmp_path):
     reqs = requests_for(cfg.V, (530, 60, 45, 38), seed=12)
     runner = runner_for(d, dtype, 1024)
     assert runner.use_graphs
+    runner.graph_min_uses = 1              # every shape gets its graph at once
     pos = {"r0": 500, "r1": 40, "r2": 0, "r3": 0}
     got = {r: {} for r in reqs}
     live = []
@@ -186,6 +187,83 @@ def test_decode_graphs_across_buckets_and_batch_sizes(dtype, tmp_path):
         check(torch.stack([got[r][p] for p in rows]), want[rows], dtype, f"graphs/{r}")
 
 
+def test_a_decode_graph_may_wait_until_its_shape_comes_back(tmp_path):
+    """With ``graph_min_uses`` = 3 a shape of decode step (batch size, table width) is launched kernel by kernel the
+    first two times and replayed from a graph from the third on; shapes that come by once or twice never get one.
+    The logits are the plain model's either way."""
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_b", "bfloat16")
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V, (40, 33, 29, 31), seed=31)
+    runner = runner_for(d, "bfloat16", 512)
+    assert runner.use_graphs and runner.graph_min_uses == 1
+    runner.graph_min_uses = 3
+    got = {r: {} for r in reqs}
+    n_graphs = []
+    with torch.inference_mode():
+        for r, toks in reqs.items():
+            runner.start_request(r)
+            runner.step([StepEntry(r, toks[:20], want=[])])
+        pos = {r: 20 for r in reqs}
+        names = list(reqs)
+        for live in ([names[:4]] * 5 + [names[:2]] * 2 + [names[:1]] * 4):
+            lg = runner.step([StepEntry(r, [reqs[r][pos[r]]], want=[0]) for r in live]).float().cpu()
+            for i, r in enumerate(live):
+                got[r][pos[r]] = lg[i]
+                pos[r] += 1
+            n_graphs.append(len(runner._graphs))
+        for r in reqs:
+            runner.end_request(r)
+    assert n_graphs == [0, 0, 1, 1, 1, 1, 1, 1, 1, 2, 2], n_graphs     # batch 4 at its third step, batch 2 never, batch 1 at its third
+    for r, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        rows = sorted(got[r])
+        check(torch.stack([got[r][p] for p in rows]), want[rows], "bfloat16", f"late graphs/{r}")
+
+
+def test_decode_steps_are_padded_to_the_batch_sizes_of_graphs(tmp_path):
+    """Eleven, nine, five and then four decoding requests: the steps of eleven and of nine replay the graph of sixteen
+    rows, that of five the graph of eight, padded with rows that are no requests (spare state slots, a page that
+    goes back after every step); four need none. Every request's logits are the plain model's, the fillers hold
+    nothing between steps and take no request's slot."""
+    from omniserver_b200 import EngineConfig, build_runner
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_b", "bfloat16")
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V, tuple(30 + (i % 4) for i in range(11)), seed=41)
+    runner = build_runner(model_dir=d, engine_config=EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=1024,
+                                                               max_requests=12))
+    runner.cache.poison_freed = True
+    runner.graph_min_uses = 1
+    got = {r: {} for r in reqs}
+    names = list(reqs)
+    with torch.inference_mode():
+        for r, toks in reqs.items():
+            runner.start_request(r)
+            runner.step([StepEntry(r, toks[:12], want=[])])
+        pos = {r: 12 for r in reqs}
+        free_slots = runner.cache.state.num_free
+        for live in ([names] * 4 + [names[:9]] * 4 + [names[:5]] * 3 + [names[:4]] * 2):
+            lg = runner.step([StepEntry(r, [reqs[r][pos[r]]], want=[0]) for r in live]).float().cpu()
+            assert lg.shape[0] == len(live) and runner.logit_slots.shape[0] == len(live)
+            for i, r in enumerate(live):
+                got[r][pos[r]] = lg[i]
+                pos[r] += 1
+            runner.cache.check_invariants()
+            assert runner.cache.state.num_free == free_slots
+            for f in runner._filler_ids:
+                rc = runner.cache.requests[f]
+                assert rc.cursor == 0 and rc.reserved == 0 and all(len(t) == 0 for t in rc.tables)
+        assert {k[0] for k in runner._graphs} == {16, 8, 4} and len(runner._filler_ids) == 7
+        for r in reqs:
+            runner.end_request(r)
+    assert all(p == 0 for p in runner.cache.pages_in_use())
+    for r, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        rows = sorted(got[r])
+        check(torch.stack([got[r][p] for p in rows]), want[rows], "bfloat16", f"padded/{r}")
+
+
 def test_the_number_of_decode_graphs_is_bounded(tmp_path):
     """With room for two graphs, a batch that keeps changing its size makes the runner drop the graph used longest
     ago and build it again later; the logits stay those of the plain model."""
@@ -195,6 +273,7 @@ def test_the_number_of_decode_graphs_is_bounded(tmp_path):
     reqs = requests_for(cfg.V, (30, 30, 30, 30), seed=14)
     runner = runner_for(d, "float32", 512)
     runner.graph_max_count = 2
+    runner.graph_min_uses = 1
     got = {r: {} for r in reqs}
     with torch.inference_mode():
         for r, toks in reqs.items():
