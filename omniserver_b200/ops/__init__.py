@@ -503,6 +503,8 @@ class CudaKernels(PersistentDecodeOps):
                     part_o = self._scratch(scratch, "attn_part_o", n_decode * nh * nsplits * hd, qkv.device)
                     part_ml = self._scratch(scratch, "attn_part_ml", n_decode * nh * nsplits * 2, qkv.device)
                     counters = self._scratch(scratch, "attn_counters", n_decode * nkv, qkv.device, zero_int=True)
+                if order is not None and nsplits * n_decode * nkv * ((nh // nkv + 7) // 8) <= self.stream_target_ctas:
+                    order = None      # all CTAs start at once: no order to choose (and one round trip less in the kernel)
                 rc = self.lib.osb_attn_decode_stream(
                     _p(out), _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
                     _p(cu_q), _p(seq_lens), _p(decode_index), _p(order), S, nh, nkv, hd, k_cache.shape[2], k_cache.shape[0],
