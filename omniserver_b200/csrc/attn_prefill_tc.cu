@@ -53,13 +53,25 @@ __device__ __forceinline__ int item_index(int pass) {
   return pass * G + ((pass & 1) ? G - 1 - x : x);
 }
 
+// `units` (or null): the (request, 128-row tile) pairs that have work, those with the most keys first; item idx is then
+// head idx % nh of unit idx / nh. Without it every (tile, request, head) of the batch is an item and most may be empty.
 __device__ __forceinline__ bool item_of(int idx, Item& it, const int* __restrict__ block_table, int bt_stride,
                                         const int* __restrict__ cu_q, const int* __restrict__ seq_lens, int nh, int nkv,
-                                        int window, int skip_single, int m_tiles, int per_tile) {
-  const int m_tile = m_tiles - 1 - idx / per_tile;
-  const int hs = idx % per_tile;
-  const int s = hs / nh;
-  it.h = hs - s * nh;
+                                        int window, int skip_single, int m_tiles, int per_tile,
+                                        const int2* __restrict__ units) {
+  int m_tile, s;
+  if (units != nullptr) {
+    const int u = idx / nh;
+    it.h = idx - u * nh;
+    const int2 un = units[u];
+    s = un.x;
+    m_tile = un.y;
+  } else {
+    m_tile = m_tiles - 1 - idx / per_tile;
+    const int hs = idx % per_tile;
+    s = hs / nh;
+    it.h = hs - s * nh;
+  }
   it.q0 = cu_q[s];
   const int q_len = cu_q[s + 1] - it.q0;
   it.m0 = m_tile * BLOCK_M;
@@ -96,7 +108,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_lens, int nh, int nkv, int log2ps,
-    float scale_log2, int window, int skip_single, int m_tiles, int n_items, int* __restrict__ err) {
+    float scale_log2, int window, int skip_single, int m_tiles, int n_items, const int2* __restrict__ units,
+    int* __restrict__ err) {
   constexpr int NA = HD / 64;                 // 64-element atoms along the head dimension
   constexpr int Q_BYTES = NA * ATOM_BYTES;    // [atom][128 rows][128 B]
   constexpr int KV_BYTES = NA * ATOM_BYTES;   // one K or V tile: [atom][128 keys][128 B]
@@ -164,7 +177,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
     for (;;) {
       const int idx = item_index(pass++);
       if (idx >= n_items) return false;
-      if (item_of(idx, it, block_table, bt_stride, cu_q, seq_lens, nh, nkv, window, skip_single, m_tiles, per_tile)) return true;
+      if (item_of(idx, it, block_table, bt_stride, cu_q, seq_lens, nh, nkv, window, skip_single, m_tiles, per_tile, units))
+        return true;
     }
   };
 
@@ -511,7 +525,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attn_prefill_tc_kernel(
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, bf16* out, const int* bt, int bt_stride,
            const int* cu_q, const int* seq_lens, int S, int nh, int nkv, int log2ps, float scale_log2, int window,
-           int max_q_len, int skip_single, int* err, cudaStream_t stream) {
+           int max_q_len, int skip_single, const int2* units, int n_units, int* err, cudaStream_t stream) {
   // at least 120 KB so that one CTA is resident per SM: each takes all 512 tensor-memory columns
   constexpr size_t need = (size_t)(HD / 64) * ATOM_BYTES * (1 + 2 * STAGES) + 1024;
   constexpr size_t smem = need > 120 * 1024 ? need : 120 * 1024;
@@ -519,7 +533,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int m_tiles = (max_q_len + BLOCK_M - 1) / BLOCK_M;
-  const int n_items = m_tiles * nh * S;
+  const int n_items = units != nullptr ? n_units * nh : m_tiles * nh * S;
+  if (n_items <= 0) return OSB_OK;
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -530,7 +545,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   // one CTA per SM at most (each takes all tensor memory and most of the shared memory), several items each if need be
   const dim3 grid((unsigned)(n_items < num_sms ? n_items : num_sms));
   return osb_launch(k, grid, dim3(NUM_THREADS), smem, stream, mq, mk, mv, out, bt, bt_stride, cu_q, seq_lens, nh, nkv,
-                    log2ps, scale_log2, window, skip_single, m_tiles, n_items, err);
+                    log2ps, scale_log2, window, skip_single, m_tiles, n_items, units, err);
 }
 }  // namespace
 
@@ -538,12 +553,14 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // out [T, nh*hd] bf16; q = the first nh*hd columns of rows of q_row_stride elements; caches
 // [pages, nkv, page_size, hd] bf16. Head sizes 64 and 128, page sizes that are powers of two from 8
 // up; anything else is refused with OSB_ERR_UNSUPPORTED (the caller then uses the mma.sync kernel).
-// Requests bringing one token are skipped when skip_single is set.
+// Requests bringing one token are skipped when skip_single is set. units (or null) [n_units][2] int32: the (request,
+// 128-row tile of its portion) pairs to compute, in the order in which they are to start; the caller lists every pair
+// that has rows (a pair that has none is skipped).
 OSB_API int osb_attn_prefill_tc(void* out, const void* q, int q_row_stride, int T, const void* k_cache,
                                 const void* v_cache, const int* block_table, int bt_stride, const int* cu_q,
                                 const int* seq_lens, int S, int nh, int nkv, int hd, int page_size, int num_pages,
-                                float scale, int window, int max_q_len, int skip_single, int* err,
-                                cudaStream_t stream) {
+                                float scale, int window, int max_q_len, int skip_single, const int* units, int n_units,
+                                int* err, cudaStream_t stream) {
   if (S <= 0 || T <= 0) return OSB_OK;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || !(scale > 0.0f)) return OSB_ERR_UNSUPPORTED;
   if (page_size < 8 || (page_size & (page_size - 1))) return OSB_ERR_UNSUPPORTED;
@@ -572,7 +589,7 @@ OSB_API int osb_attn_prefill_tc(void* out, const void* q, int q_row_stride, int 
   const float scale_log2 = scale * LOG2E;
   if (hd == 64)
     return launch<64>(mq, mk, mv, (bf16*)out, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, log2ps, scale_log2,
-                      window, max_q_len, skip_single, err, stream);
+                      window, max_q_len, skip_single, reinterpret_cast<const int2*>(units), n_units, err, stream);
   return launch<128>(mq, mk, mv, (bf16*)out, block_table, bt_stride, cu_q, seq_lens, S, nh, nkv, log2ps, scale_log2,
-                     window, max_q_len, skip_single, err, stream);
+                     window, max_q_len, skip_single, reinterpret_cast<const int2*>(units), n_units, err, stream);
 }

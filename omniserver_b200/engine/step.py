@@ -70,6 +70,7 @@ class StepContext:
         self.decode_index: Optional[torch.Tensor] = None   # [S]: index among requests bringing one token, else -1
         self.attn_order: Optional[torch.Tensor] = None     # [S]: the requests by falling length (attention starts long ones first)
         self.kv_uneven = False                             # the single-token requests' lengths differ much
+        self.prefill_units: Optional[torch.Tensor] = None  # [n, 2]: (request, 128-row tile) with work, most keys first
         self.n_decode = self.n_multi = 0
         self.scratch: Dict[str, torch.Tensor] = {}         # per-step scratch buffers shared by the layers
         self.advance_state = True                          # False: a dry run that must not move cursors
@@ -263,6 +264,7 @@ class ModelRunner:
             ("override_rows", np.asarray(ov_rows, dtype=np.int32)), ("decode_index", decode_index),
             ("token_src", tok_src), ("logit_slots", np.asarray(logit_slots, dtype=np.int32)),
             ("attn_order", np.argsort(-np.asarray(kv_lens), kind="stable").astype(np.int32)),
+            ("prefill_units", ops.CudaKernels.prefill_units(q_lens, kv_lens).reshape(-1)),
         ]
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
@@ -317,6 +319,7 @@ class ModelRunner:
             ("logit_rows", ar[:S]), ("override_rows", np.zeros(0, dtype=np.int32)), ("decode_index", ar[:S]),
             ("token_src", np.where(from_dev, slots, -1).astype(np.int32)), ("logit_slots", slots),
             ("attn_order", np.argsort(-cursors, kind="stable").astype(np.int32)),
+            ("prefill_units", np.zeros(0, dtype=np.int32)),
         ]
         for g in range(G):
             segs.append((f"bt{g}", bts[g].reshape(-1)))
@@ -366,6 +369,7 @@ class ModelRunner:
         ctx.decode_index = seg("decode_index")
         ctx.attn_order = seg("attn_order")      # the requests by falling length: long ones start first
         ctx.kv_uneven = plan["uneven"]
+        ctx.prefill_units = seg("prefill_units").view(-1, 2)   # (request, row tile) of the requests bringing several tokens
         if self.last_token is not None:
             ctx.token_src, ctx.last_token = seg("token_src"), self.last_token
         ctx.logit_slots = seg("logit_slots")

@@ -17,6 +17,7 @@ import contextlib
 import ctypes
 from typing import Dict, Optional, Tuple
 
+import numpy as np
 import torch
 
 from . import library
@@ -425,7 +426,8 @@ class CudaKernels(PersistentDecodeOps):
                         decode_index: Optional[torch.Tensor] = None, n_decode: int = 0, n_multi: int = 0,
                         exact: bool = False, scratch: Optional[dict] = None,
                         rope: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None,
-                        order: Optional[torch.Tensor] = None, uneven: bool = False) -> torch.Tensor:
+                        order: Optional[torch.Tensor] = None, uneven: bool = False,
+                        units: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention of the step's queries (the first nh*hd columns of ``qkv``) over the paged cache.
 
         bfloat16 operands run on the tensor cores (one kernel for requests bringing several tokens,
@@ -440,6 +442,10 @@ class CudaKernels(PersistentDecodeOps):
         ``order`` [S] int32: the requests by falling length. The decode kernel starts their CTAs in that order, so
         that with more CTAs than SMs the short ones fill the gaps at the end (64 requests of 256 to 4,352 keys on 4
         kv heads: 79 us in the order given, 53 us longest first; 47 us would be the copy rate).
+        ``units`` [n, 2] int32 (``prefill_units``): the (request, 128-row tile) pairs of the requests that bring
+        several tokens, most keys first; the tcgen05 kernel then works through exactly these (beside 60 decoding
+        requests a 2,048-token portion otherwise cost 3.95 instead of 1.60 ms over 28 layers: every CTA looked at
+        every (tile, request, head) of the batch).
         ``uneven``: the single-token requests' lengths differ much (the longest is 1.5 times the mean or more): the
         keys may then be cut into more splits than fill the SMs once (see ``decode_splits``).
         """
@@ -450,6 +456,9 @@ class CudaKernels(PersistentDecodeOps):
             _cuda_contig(n, t, torch.int32)
         T = qkv.shape[0]
         S = seq_lens.shape[0]
+        if units is not None:
+            _cuda_contig("units", units, torch.int32)
+            _check(units.dim() == 2 and units.shape[1] == 2, "paged_attention: units [n, 2]")
         if order is not None:
             _cuda_contig("order", order, torch.int32)
             _check(order.shape == (S,), "paged_attention: order [S]")
@@ -474,7 +483,7 @@ class CudaKernels(PersistentDecodeOps):
                     _p(out), _p(qkv), qkv.shape[1], T, _p(k_cache), _p(v_cache), _p(block_table),
                     block_table.shape[1], _p(cu_q), _p(seq_lens), S, nh, nkv, hd, k_cache.shape[2],
                     k_cache.shape[0], ctypes.c_float(scale), win, max_q_len, 1 if n_decode > 0 else 0,
-                    _p(self.err_flag(qkv.device)), self._stream())
+                    _p(units), 0 if units is None else units.shape[0], _p(self.err_flag(qkv.device)), self._stream())
                 self._ok(rc, "attn_prefill_tc")
                 if n_decode == 0:
                     return out
@@ -564,6 +573,24 @@ class CudaKernels(PersistentDecodeOps):
         return (not exact and n_multi == 0 and n_decode > 0 and qkv.dtype == torch.bfloat16
                 and k_cache.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256 and nh // nkv <= 16
                 and ps >= 2 and (ps & (ps - 1)) == 0)
+
+    PREFILL_ROW_TILE = 128     # query rows of one unit of work of the tcgen05 prefill attention
+
+    @staticmethod
+    def prefill_units(q_lens, kv_lens) -> np.ndarray:
+        """[n, 2] int32 (request, row tile) for every 128-row tile of the requests that bring more than one token,
+        ordered by the number of keys the tile's last row sees, most first (host-side plan of a step)."""
+        tile = CudaKernels.PREFILL_ROW_TILE
+        ql, kv = np.asarray(q_lens, dtype=np.int64), np.asarray(kv_lens, dtype=np.int64)
+        req = np.nonzero(ql > 1)[0]
+        if req.size == 0:
+            return np.zeros((0, 2), dtype=np.int32)
+        n_tiles = -(-ql[req] // tile)
+        s = np.repeat(req, n_tiles)
+        m = np.concatenate([np.arange(n) for n in n_tiles])
+        keys = kv[s] - ql[s] + np.minimum((m + 1) * tile, ql[s])
+        order = np.argsort(-keys, kind="stable")
+        return np.stack([s[order], m[order]], axis=1).astype(np.int32)
 
     @staticmethod
     def decode_splits(n_decode: int, nkv: int, group: int, max_kv_len: int, target_ctas: int = 296,

@@ -82,7 +82,7 @@ class GQAAttention(Mixer):
                               ctx.max_q_len, ctx.max_kv_len, ctx.act_dtype, decode_index=ctx.decode_index,
                               n_decode=ctx.n_decode, n_multi=ctx.n_multi, scratch=ctx.scratch,
                               rope=(rot.cos, rot.sin, ctx.slot_maps[g], rot_dim) if fuse else None,
-                              order=ctx.attn_order, uneven=ctx.kv_uneven)
+                              order=ctx.attn_order, uneven=ctx.kv_uneven, units=ctx.prefill_units)
         return self.out(a, ctx.act_dtype)
 
 

@@ -118,7 +118,7 @@ class PlainKernels:
     # -- attention
     def paged_attention(self, qkv, k_cache, v_cache, block_table, cu_q, seq_lens, tok_seq, nh, nkv, hd, scale,
                         window, max_q_len, max_kv_len, out_dtype, decode_index=None, n_decode=0, n_multi=0, exact=False,
-                        scratch=None, rope=None, order=None, uneven=False):
+                        scratch=None, rope=None, order=None, uneven=False, units=None):
         T = qkv.shape[0]
         ps = k_cache.shape[2]
         g = nh // nkv

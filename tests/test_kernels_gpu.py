@@ -481,7 +481,7 @@ def _paged_case(q_lens, kv_lens, nh, nkv, hd, ps, dtype, seed=0, pages_extra=3):
     return qkv, kc, vc, bt, cu_q, seq_lens, tok_seq
 
 
-def _run_attn(case, nh, nkv, hd, window, dtype, exact=False):
+def _run_attn(case, nh, nkv, hd, window, dtype, exact=False, units=None):
     qkv, kc, vc, bt, cu_q, seq_lens, tok_seq = case
     scale = hd ** -0.5
     mq, mk = int((cu_q[1:] - cu_q[:-1]).max()), int(seq_lens.max())
@@ -491,7 +491,7 @@ def _run_attn(case, nh, nkv, hd, window, dtype, exact=False):
     got = K().paged_attention(qkv.to(DEV), kc.to(DEV), vc.to(DEV), bt.to(DEV), cu_q.to(DEV), seq_lens.to(DEV),
                               tok_seq.to(DEV), nh, nkv, hd, scale, window, mq, mk, dtype,
                               decode_index=decode_index.to(DEV), n_decode=int(single.sum()),
-                              n_multi=int((~single).sum()), exact=exact)
+                              n_multi=int((~single).sum()), exact=exact, units=None if units is None else units.to(DEV))
     want = REF.paged_attention(qkv, kc, vc, bt, cu_q, seq_lens, tok_seq, nh, nkv, hd, scale, window, mq, mk,
                                torch.float32)
     K().check_device_errors()
@@ -741,6 +741,12 @@ def test_prefill_attention_tcgen05_many_units_per_cta(nh, nkv, hd, ps, window):
     got, want = _run_attn(case, nh, nkv, hd, window, torch.bfloat16)
     assert torch.isfinite(got).all()
     _assert_attn_close(got, want, case, nh, nkv, hd, window, "tcgen05, several units per CTA")
+    # given the list of (request, row tile) pairs that have work, as the engine's plan gives it: the same output
+    from omniserver_b200.ops import CudaKernels
+    units = torch.from_numpy(CudaKernels.prefill_units(q_lens, kv_lens))
+    assert units.shape[0] == sum(-(-q // 128) for q in q_lens if q > 1)
+    listed, _ = _run_attn(case, nh, nkv, hd, window, torch.bfloat16, units=units)
+    assert torch.equal(listed, got)
 
 
 @pytest.mark.parametrize("window", [None, 130])
