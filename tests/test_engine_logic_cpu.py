@@ -289,3 +289,38 @@ def test_decode_splits_take_uneven_lengths_into_account():
     assert split(64, 4, 7, 4352, 148, max_splits=16, uneven=True)[1] == 1       # 256 CTAs: two waves already
     assert split(8, 2, 6, 2048, 148, max_splits=16)[1] == 8
     assert split(8, 2, 6, 2048, 148, max_splits=16, uneven=True)[1] == 8
+
+
+def test_prefill_units_list_every_row_tile_with_work_most_keys_first():
+    from omniserver_b200.ops import CudaKernels
+    u = CudaKernels.prefill_units([300, 1, 130, 1, 2], [300, 900, 700, 5, 259])
+    # request 0: 3 tiles seeing 128, 256, 300 keys; request 2: 2 tiles seeing 698, 700; request 4: one tile seeing 259
+    assert u.tolist() == [[2, 1], [2, 0], [0, 2], [4, 0], [0, 1], [0, 0]]
+    assert CudaKernels.prefill_units([1, 1], [10, 20]).shape == (0, 2)
+
+
+def test_decode_steps_share_graphs_of_power_of_two_batch_sizes():
+    from omniserver_b200.engine.step import ModelRunner
+    assert [ModelRunner._graph_bucket(n) for n in (1, 2, 3, 5, 8, 9, 17, 33, 63, 64, 65, 200)] == \
+        [1, 2, 4, 8, 8, 16, 32, 64, 64, 64, 128, 256]
+    assert ModelRunner.GRAPH_FILLERS >= 127
+
+
+def test_spare_state_slots_are_not_counted_and_never_handed_to_requests():
+    from omniserver_b200.cache.state_slots import OutOfSlots, StateSlots
+    s = StateSlots(2, {}, "cpu", allocate=False, spare=2)
+    assert s.num_free == 2
+    a, b = s.alloc(), s.alloc()
+    assert {a, b} == {0, 1} and s.num_free == 0
+    with pytest.raises(OutOfSlots):
+        s.alloc()
+    x, y = s.alloc(spare=True), s.alloc(spare=True)
+    assert {x, y} == {2, 3} and s.num_free == 0
+    with pytest.raises(OutOfSlots):
+        s.alloc(spare=True)
+    s.free(x)
+    assert s.num_free == 0 and s.alloc(spare=True) == x
+    s.free(a)
+    assert s.num_free == 1
+    with pytest.raises(ValueError):
+        s.free(a)
