@@ -225,8 +225,8 @@ def run_ours(args):
 
 def _reference_root():
     """Where the unmodified reference package lies: the copy under baseline/_ref (it travels with the
-    repository's snapshot), else a checkout named by OMNISERVE_REFERENCE, else /root/reference."""
-    for p in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("OMNISERVE_REFERENCE", ""), "/root/reference"):
+    repository's snapshot), else a checkout named by OMNISERVE_REFERENCE."""
+    for p in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("OMNISERVE_REFERENCE", "")):
         if p and os.path.isdir(os.path.join(p, "omniserve")):
             return p
     return None
