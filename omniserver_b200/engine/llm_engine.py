@@ -8,6 +8,7 @@ here the scheduler's entries always run as one batch.
 
 from __future__ import annotations
 
+import itertools
 import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence as Seq
@@ -148,8 +149,8 @@ class LLMEngine:
         With ``overlap`` the host does not wait for the step it has just launched: sampled tokens stay
         on the device for the next step's embedding lookup (``StepEntry.from_device``) and are read one
         call later, so that scheduling and launching step t+1 overlaps the device's work on step t.
-        That is done only while every running request decodes, nothing waits for admission and no
-        preemption can happen; otherwise the step in flight is read before the next is scheduled.
+        That is done whenever no preemption can happen in the next step (pages to spare for all it may
+        take); otherwise the step in flight is read before the next is scheduled.
         A request that ends on a stop token is found out one step late; the token computed for it
         meanwhile is dropped."""
         deltas: List[StepDelta] = []
@@ -176,15 +177,24 @@ class LLMEngine:
         return deltas
 
     def _steady_decode(self) -> bool:
-        """Whether the next step can be scheduled before the tokens of the step in flight are known."""
+        """Whether the next step can be scheduled before the tokens of the step in flight are known: whenever no
+        request can be preempted in it (a preempted request is computed again from its tokens, and its newest one
+        is still on the device). The step then takes the tokens it lacks from the device (``from_device``), be it a
+        decode step or one that also brings portions of prompts and admits requests."""
         sch = self.scheduler
-        if sch.waiting:
-            return False
+        cfg = sch.config
         live = [s for s in sch.running if s.status == Status.RUNNING]
-        if not all(s.is_decoding for s in live):
-            return False
+        ps = self.runner.cache.page_size
+        # the most pages the next step can take: one per decoding request; for the prompts in flight and those that
+        # may be admitted, the tokens the budget lets through and a page more each (a portion may start inside a page)
+        admit = min(len(sch.waiting), cfg.max_prefill_per_step, max(0, cfg.max_running - len(live)))
+        prompts = [s for s in live if not s.is_decoding] + list(itertools.islice(sch.waiting, admit))
+        tokens = min(cfg.max_prefill_tokens, sum(s.remaining for s in prompts))
+        need = (len(live) + admit - len(prompts)) + -(-tokens // ps) + len(prompts)
         free = self.runner.cache.free_pages()
-        return not free or min(free) >= len(live)     # nobody can run out of pages: no preemption
+        if free and min(free) < need:
+            return False
+        return admit == 0 or self.runner.cache.state.num_free >= admit
 
     def _launch(self, out: SchedulerOutput) -> "_InFlight":
         entries = []
