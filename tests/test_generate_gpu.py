@@ -195,3 +195,61 @@ def test_overlapped_and_step_by_step_engines_agree(dtype, tmp_path):
     assert outs[True] == want
     if dtype == "float32":
         assert outs[False][0] == pm.generate(cfg, w, prompts[0], 40)
+
+
+@pytest.mark.parametrize("seed,pool", [(s, p) for s in range(1, 7) for p in (96, 160, 4096)][::2] + [(2, 96)])
+def test_random_traffic_matches_plain(seed, pool, tmp_path):
+    """Requests of random lengths that arrive while others run, some ending on a stop token, some aborted, in a
+    pool that forces preemptions (or none), batch sizes that need padding to the graphs' sizes, steps launched
+    before the ones before are read: every request's greedy tokens are the plain model's; nothing is left in the
+    cache."""
+    import random
+    from omniserver_b200 import EngineConfig, LLMEngine, Request, SamplingParams, SchedulerConfig
+    d = make_model_dir(tmp_path, "tiny_a", "float32")
+    cfg, w = plain_model(d)
+    rnd = random.Random(seed)
+    g = torch.Generator().manual_seed(seed)
+    n_req = 14
+    prompts = [torch.randint(0, cfg.V, (rnd.randint(1, 40),), generator=g).tolist() for _ in range(n_req)]
+    new = [rnd.randint(1, 24) for _ in range(n_req)]
+    arrive = sorted(rnd.randint(0, 30) for _ in range(n_req))
+    want = [pm.generate(cfg, w, p, n) for p, n in zip(prompts, new)]
+    stops = {}
+    for i in range(n_req):
+        if rnd.random() < 0.3 and len(want[i]) > 2:
+            k = rnd.randrange(1, len(want[i]))
+            stops[i] = want[i][k]
+            want[i] = want[i][:want[i].index(stops[i]) + 1]
+    aborted = {i for i in range(n_req) if rnd.random() < 0.15}
+    with torch.inference_mode():
+        eng = LLMEngine.from_model_dir(d, EngineConfig(dtype="float32", page_size=8, max_cache_tokens=pool, max_requests=16),
+                                       SchedulerConfig(max_running=rnd.choice([3, 6, 11]), max_prefill_per_step=rnd.choice([1, 3]),
+                                                       max_prefill_tokens=rnd.choice([8, 24, 64])), seed=seed)
+        ids, got, step, nxt = {}, {}, 0, 0
+        while nxt < n_req or eng.has_unfinished():
+            while nxt < n_req and arrive[nxt] <= step:
+                sp = SamplingParams(max_new_tokens=new[nxt], stop_token_ids=[stops[nxt]] if nxt in stops else [])
+                ids[nxt] = eng.add_request(Request(prompt=prompts[nxt], sampling=sp, request_id=f"t{nxt}"))
+                got[ids[nxt]] = []
+                if nxt in aborted and rnd.random() < 0.5:
+                    eng.abort(ids[nxt])                       # before it ever ran
+                nxt += 1
+            for dl in eng.step():
+                got[dl.request_id].extend(dl.new_token_ids)
+            for i in list(aborted):
+                if i in ids and len(got[ids[i]]) >= 2:
+                    eng.abort(ids[i])                         # while it decodes
+                    aborted.discard(i)
+                    want[i] = None
+            step += 1
+            assert step < 3000
+            eng.runner.cache.check_invariants()
+        from omniserver_b200 import ops
+        ops.kernels().check_device_errors()
+    for i in range(n_req):
+        if want[i] is None or i in aborted:
+            continue       # aborted: whatever it produced before is a prefix
+        assert got[ids[i]] == want[i], (i, got[ids[i]], want[i])
+    if pool == 96:
+        assert eng.stats()["preemptions"] >= 1
+    assert all(x == 0 for x in eng.runner.cache.pages_in_use()) and not eng.runner.cache.requests
