@@ -117,6 +117,9 @@ class ModelRunner:
         #: a graph is built when its shape comes by for this many-th time; before that the step is launched kernel
         #: by kernel (1: build at once)
         self.graph_min_uses = 1
+        #: the same for steps that bring portions of prompts (0: never a graph for them). Their shapes (tokens per
+        #: request) are many, and most come by once
+        self.graph_min_uses_prompt = 3
         self._graph_seen: Dict[Any, int] = {}
         #: rows that pad a decode step to the next batch size for which graphs are kept (``_graph_bucket``): requests
         #: of one token at position 0 on spare state slots, whose page goes back after every step
@@ -404,6 +407,8 @@ class ModelRunner:
         before they step again."""
         if self.use_graphs and self._graphable(entries):
             return self._graph_step(entries, copy_logits)
+        if self.use_graphs and self._shape_graphable(entries):
+            return self._shape_graph_step(entries, copy_logits)
         self._before_step()
         try:
             ctx = self.build_context(entries)
@@ -512,7 +517,6 @@ class ModelRunner:
         buffer at a fixed address (one host-to-device copy); everything the kernels need that
         changes from step to step is read from that buffer or from the state slots.
         """
-        k = ops.kernels()
         round_to = self.graph_bt_round
         self._before_step()
         n_real = len(entries)
@@ -524,16 +528,47 @@ class ModelRunner:
             self._rollback(entries)
             raise
         key = (plan["S"], tuple(plan["bt_widths"]), plan["uneven"])   # (the attention's splits depend on the last)
+        return self._replay(key, plan, real, fill, copy_logits, self.graph_min_uses)
+
+    def _shape_graphable(self, entries: Sequence[StepEntry]) -> bool:
+        """Steps that bring portions of prompts have a fixed launch sequence too, for given token counts per
+        request: all that changes from one such step to the next (tokens, positions, tables, wanted rows) is data in
+        the step's buffer. Not with given embedding rows (a tensor of the step's own)."""
+        if self.device.type != "cuda" or len(entries) > self.graph_max_batch or self.graph_min_uses_prompt <= 0:
+            return False
+        return all(e.embed_rows is None for e in entries)
+
+    def _shape_graph_step(self, entries: Sequence[StepEntry], copy_logits: bool = True) -> torch.Tensor:
+        """A step of any shape replayed from a CUDA graph once its shape (tokens and wanted rows per request,
+        block-table width bucket) has come by ``graph_min_uses_prompt`` times: a 2,048-token portion is 232 launches,
+        which the host issues in 3.4 ms while the device needs 5.1 ms for them and waits now and then (5.8 ms from
+        the call to the logits launched kernel by kernel, 5.1 ms replayed)."""
+        self._before_step()
+        try:
+            plan = self._plan(entries, bt_round=self.graph_bt_round)
+        except Exception:
+            self._rollback(entries)
+            raise
+        key = ("shape", tuple(plan["q_lens"]), tuple(len(e.want) for e in entries), tuple(plan["bt_widths"]),
+               plan["uneven"], plan["explicit_positions"])
+        return self._replay(key, plan, entries, [], copy_logits, self.graph_min_uses_prompt)
+
+    def _replay(self, key, plan: Dict[str, Any], real: Sequence[StepEntry], fill: Sequence[StepEntry],
+                copy_logits: bool, min_uses: int) -> torch.Tensor:
+        """Runs a planned step from the graph of its shape (built now if the shape has come by often enough, else
+        the step is launched kernel by kernel)."""
+        k = ops.kernels()
+        entries = list(real) + list(fill)
+        n_real = len(real)
         slot = self._graphs.get(key)
-        if slot is None and self.graph_min_uses > 1:
+        if slot is None and min_uses > 1:
             # Building a graph costs about as much as ten steps (a warm-up forward, a wait for the device, the
-            # capture): a shape that comes by once or twice, as the batch sizes do while the last requests of a
-            # run end one after the other, is launched kernel by kernel instead.
+            # capture): a shape that comes by once or twice is launched kernel by kernel instead.
             if len(self._graph_seen) > 4096:
                 self._graph_seen.clear()
             seen = self._graph_seen.get(key, 0) + 1
             self._graph_seen[key] = seen
-            if seen < self.graph_min_uses:
+            if seen < min_uses:
                 return self._planned_step(real, plan, fill)
         if slot is not None:
             self._graphs.move_to_end(key)
@@ -590,6 +625,6 @@ class ModelRunner:
         for e in fill:
             self.cache.rollback(e.request_id)       # the filler's page goes back; it stays at position 0
         o, n = slot["offs"]["logit_slots"]
-        self.logit_slots = slot["dev"][o:o + n_real]
-        logits = slot["logits"][:n_real]
+        self.logit_slots = slot["dev"][o:o + n] if not fill else slot["dev"][o:o + n_real]
+        logits = slot["logits"] if not fill else slot["logits"][:n_real]
         return logits.clone() if copy_logits else logits

@@ -198,6 +198,7 @@ def test_a_decode_graph_may_wait_until_its_shape_comes_back(tmp_path):
     runner = runner_for(d, "bfloat16", 512)
     assert runner.use_graphs and runner.graph_min_uses == 1
     runner.graph_min_uses = 3
+    runner.graph_min_uses_prompt = 0       # (no graphs for the prompts' steps: only decode shapes are counted below)
     got = {r: {} for r in reqs}
     n_graphs = []
     with torch.inference_mode():
@@ -235,6 +236,7 @@ def test_decode_steps_are_padded_to_the_batch_sizes_of_graphs(tmp_path):
                                                                max_requests=12))
     runner.cache.poison_freed = True
     runner.graph_min_uses = 1
+    runner.graph_min_uses_prompt = 0
     got = {r: {} for r in reqs}
     names = list(reqs)
     with torch.inference_mode():
@@ -262,6 +264,56 @@ def test_decode_steps_are_padded_to_the_batch_sizes_of_graphs(tmp_path):
         want = pm.forward(cfg, w, torch.tensor(toks))
         rows = sorted(got[r])
         check(torch.stack([got[r][p] for p in rows]), want[rows], "bfloat16", f"padded/{r}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_with_prompt_portions_replay_graphs_of_their_shape(dtype, tmp_path):
+    """A long prompt in portions of 16 tokens beside two decoding requests: the shape (1, 1, 16 tokens) comes by
+    again and again and is replayed from a graph from its third time on, with other tokens, positions in the cache,
+    pages and wanted rows every time; so is a lone portion of 24 tokens of several requests. Logits against the plain
+    model at every wanted place."""
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_b", dtype)
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V, (140, 60, 50, 72, 72, 72, 72), seed=51)
+    runner = runner_for(d, dtype, 1024)
+    assert runner.use_graphs and runner.graph_min_uses_prompt == 3
+    got = {r: {} for r in reqs}
+    names = list(reqs)
+    long, d1, d2 = names[:3]
+    with torch.inference_mode():
+        for r in (d1, d2):
+            runner.start_request(r)
+            runner.step([StepEntry(r, reqs[r][:30], want=[])])
+        pos = {d1: 30, d2: 30, long: 0}
+        runner.start_request(long)
+        shape_graphs = []
+        for step in range(8):           # 8 x 16 = 128 tokens of the long prompt, each beside two decoded tokens
+            entries = [StepEntry(d1, [reqs[d1][pos[d1]]], want=[0]), StepEntry(d2, [reqs[d2][pos[d2]]], want=[0]),
+                       StepEntry(long, reqs[long][pos[long]:pos[long] + 16], want=[step % 15, 15])]   # two rows, other places
+            lg = runner.step(entries).float().cpu()
+            got[d1][pos[d1]], got[d2][pos[d2]] = lg[0], lg[1]
+            for j, wrow in enumerate(entries[2].want):
+                got[long][pos[long] + wrow] = lg[2 + j]
+            pos[d1] += 1; pos[d2] += 1; pos[long] += 16
+            shape_graphs.append(sum(1 for k in runner._graphs if k[0] == "shape"))
+            runner.cache.check_invariants()
+        assert shape_graphs == [0, 0, 1, 1, 1, 1, 1, 1], shape_graphs
+        for r in (long, d1, d2):
+            runner.end_request(r)
+        # lone portions of 24 tokens of four other requests, three portions each
+        for r in names[3:]:
+            runner.start_request(r)
+            for o in range(0, 72, 24):
+                lg = runner.step([StepEntry(r, reqs[r][o:o + 24], want=[23])]).float().cpu()
+                got[r][o + 23] = lg[0]
+            runner.end_request(r)
+        assert sum(1 for k in runner._graphs if k[0] == "shape") >= 2
+    for r, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        rows = sorted(got[r])
+        assert rows
+        check(torch.stack([got[r][p] for p in rows]), want[rows], dtype, f"shape graphs/{r}")
 
 
 def test_the_number_of_decode_graphs_is_bounded(tmp_path):
