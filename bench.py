@@ -161,7 +161,7 @@ def run_ours(args):
     e2e = None
     kernels = None
     if points_on:
-        for B in batches:
+        for B in sorted(batches, reverse=True):     # (the largest first: it takes the most pages of the pool)
             if B != batch:
                 r = b.decode(B, max(8, args.steps // 2), max(3, args.warmup // 2), trials=args.trials)
                 points[f"decode_b{B}"] = round(r["tokens_per_s"], 1)

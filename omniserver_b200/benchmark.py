@@ -259,7 +259,9 @@ class Bench:
             sampler_proc = ClockSampler() if clocks else None
             if sampler_proc:
                 sampler_proc.start()
-                time.sleep(0.3)
+            # the prompts' prefills just before ran the tensor cores at the power limit; the decode steps are timed
+            # after a short pause, at the clocks a decoding GPU has and not at those that burst left behind
+            time.sleep(0.3)
             per_step, launches = [], 0
             for _ in range(max(1, trials)):
                 l0 = K.launches

@@ -120,6 +120,7 @@ class ModelRunner:
         #: the same for steps that bring portions of prompts (0: never a graph for them). Their shapes (tokens per
         #: request) are many, and most come by once
         self.graph_min_uses_prompt = 3
+        self.graph_min_free_bytes = 8 << 30     # no new graph for such a step with less free device memory than this
         self._graph_seen: Dict[Any, int] = {}
         #: rows that pad a decode step to the next batch size for which graphs are kept (``_graph_bucket``): requests
         #: of one token at position 0 on spare state slots, whose page goes back after every step
@@ -551,6 +552,8 @@ class ModelRunner:
             raise
         key = ("shape", tuple(plan["q_lens"]), tuple(len(e.want) for e in entries), tuple(plan["bt_widths"]),
                plan["uneven"], plan["explicit_positions"])
+        if key not in self._graphs and torch.cuda.mem_get_info(self.device)[0] < self.graph_min_free_bytes:
+            return self._planned_step(entries, plan)     # a graph keeps the step's activations: not with memory this short
         return self._replay(key, plan, entries, [], copy_logits, self.graph_min_uses_prompt)
 
     def _replay(self, key, plan: Dict[str, Any], real: Sequence[StepEntry], fill: Sequence[StepEntry],
