@@ -160,17 +160,17 @@ def run_ours(args):
     points = {}
     e2e = None
     kernels = None
+    if not fast:
+        e2e = b.e2e_decode(batch, args.steps, args.warmup)     # (before the points: same state of the process as `value`)
     if points_on:
-        for B in sorted(batches, reverse=True):     # (the largest first: it takes the most pages of the pool)
+        for B in sorted(batches, reverse=True):
             if B != batch:
                 r = b.decode(B, max(8, args.steps // 2), max(3, args.warmup // 2), trials=args.trials)
                 points[f"decode_b{B}"] = round(r["tokens_per_s"], 1)
                 points[f"decode_b{B}_ms"] = round(r["ms_per_step"], 4)
                 points[f"decode_b{B}_frac"] = round(r["frac"], 4)
-    if not fast:
-        e2e = b.e2e_decode(batch, args.steps, args.warmup)
-        if args.profile or points_on:
-            kernels = b.profile(batch)
+    if not fast and (args.profile or points_on):
+        kernels = b.profile(batch)
     line = {
         "metric": "decode tokens/s (Qwen2-VL-%s text decoder, batch %d, %d-token contexts)" % (model.upper(), batch, CONTEXT),
         "value": round(main["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
