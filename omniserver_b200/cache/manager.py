@@ -293,9 +293,16 @@ class CacheManager:
             t[rc.slot].zero_()
 
     # ------------------------------------------------------------------ per-step tables
-    def block_table(self, group: int, request_ids: Sequence[str], round_to: int = 1) -> np.ndarray:
+    def block_table(self, group: int, request_ids: Sequence[str], round_to: int = 1, pow2: bool = False) -> np.ndarray:
+        """[requests, width] page ids, -1 where a request has none. The width is that of the longest table, rounded up
+        to a multiple of ``round_to``, or (``pow2``) to ``round_to`` times a power of two."""
         width = max(1, max((len(self.requests[r].tables[group]) for r in request_ids), default=1))
         width = -(-width // round_to) * round_to
+        if pow2:
+            w = round_to
+            while w < width:
+                w *= 2
+            width = w
         bt = np.full((len(request_ids), width), -1, dtype=np.int32)
         for i, r in enumerate(request_ids):
             t = self.requests[r].tables[group].array()

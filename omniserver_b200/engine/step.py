@@ -110,7 +110,7 @@ class ModelRunner:
         #: replay pure decode steps from CUDA graphs (one per batch size and block-table width)
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self.graph_max_batch = 256
-        self.graph_bt_round = 32          # block-table width is rounded up to this many pages
+        self.graph_bt_round = 32          # block-table width is rounded up to this many pages times a power of two
         #: most graphs kept; the one used longest ago goes when another is needed. All graphs allocate from one
         #: memory pool (they replay one after the other on one stream), so their activations share memory.
         self.graph_max_count = 32
@@ -256,7 +256,7 @@ class ModelRunner:
             cache.reserve(r, n)
         slots = np.asarray([cache.requests[r].slot for r in rids], dtype=np.int32)
         G = len(cache.groups)
-        bts = [cache.block_table(g, rids, bt_round) for g in range(G)]
+        bts = [cache.block_table(g, rids, bt_round, pow2=bt_round > 1) for g in range(G)]
         sms = [cache.slot_map(g, rids, q_lens) for g in range(G)]
         ql = np.asarray(q_lens)
         single = ql == 1
@@ -308,7 +308,7 @@ class ModelRunner:
         cursors = np.fromiter((rc.cursor for rc in rcs), dtype=np.int32, count=S)
         ar = np.arange(S + 1, dtype=np.int32)
         G = len(cache.groups)
-        bts = [cache.block_table(g, rids, bt_round) for g in range(G)]
+        bts = [cache.block_table(g, rids, bt_round, pow2=bt_round > 1) for g in range(G)]
         sms = []
         for g in range(G):
             pages = np.fromiter((rc.tables[g][rc.cursor // ps] for rc in rcs), dtype=np.int32, count=S)
