@@ -34,6 +34,7 @@ class CudaKernels(PersistentDecodeOps):
     #: (measured on B200: it wins up to 16 rows, the library GEMM from 32 rows on)
     SKINNY_MAX_ROWS = 16
     SKINNY_TWO_TILE_MAX_ELEMS = 1 << 25   # 9 to 16 rows: matrices from 64 MB on go to the library
+    FEWROWS_MAX_ROWS_KERNEL = 128         # what ``gemm_fewrows`` takes
     #: splits of a request's keys that one thread-block cluster of the decode attention merges
     CLUSTER_MAX_SPLITS = 8
 
@@ -66,6 +67,10 @@ class CudaKernels(PersistentDecodeOps):
         # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
+        # 17 to this many rows: the tcgen05 kernel with W on the M side (csrc/gemm_fewrows_tc.cu) for the gate/up
+        # product with its activation and for products with a long K over few features
+        self.fewrows_tc = True
+        self.fewrows_max_rows = 64
         self._pinned_stream: Optional[ctypes.c_void_p] = None
         # decode steps of up to 16 rows: the weight-streaming kernels (csrc/decode_stream.cu) for the feed-forward
         # half, for a projection with the norm in front of it, and for a plain projection
@@ -291,6 +296,11 @@ class CudaKernels(PersistentDecodeOps):
             # (with 9 to 16 rows the kernel's two-column-tile form streams a large matrix, the head over the
             # vocabulary, at 0.71 to 0.74 of the copy rate where the library reaches 0.93)
             return self.gemm_skinny(x, w, bias, out_dtype)
+        if self.can_gemm_fewrows(x, w, out_dtype) and K >= 2 * N:
+            # (measured at 24 to 64 rows: a long K over few features, the down projection, runs in 11 to 12 / 27 to
+            # 28 / 76 to 79 us at the three model sizes where the library takes 14 / 30 to 31 / 73 to 81; squarer
+            # matrices run in 5 to 6 us in the library, at the floor of a dependent kernel, and 6 to 7 here)
+            return self.gemm_fewrows(x, w, bias)
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows and K % 8 == 0 and x.data_ptr() % 16 == 0
                 and w.data_ptr() % 16 == 0):
             return self.gemm_tcgen05(x, w, bias, out_dtype)
@@ -339,6 +349,38 @@ class CudaKernels(PersistentDecodeOps):
         self._ok(rc, "gemm_tcgen05_2cta_bf16" if pairs else "gemm_tcgen05_bf16")
         return y
 
+    def gemm_fewrows(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, swiglu: bool = False,
+                     splits: int = 0, form: int = 0, wait_limit: int = 0, tx_extra: int = 0) -> torch.Tensor:
+        """bf16 product for up to 128 rows of x on tcgen05 with W on the M side of the MMA (128 rows of W per CTA, the
+        rows of x as 32, 64 or 128 accumulator columns), K cut into ``splits`` parts (1 to 8) that are the CTAs of a
+        cluster (0: from the shape). ``swiglu``: w is [2I, K] (gate rows first) and the result is
+        silu(x Wg^T) * (x Wu^T); ``form`` 1: a CTA has 128 gate and 128 up rows in two accumulators, 2: 64 and 64 in
+        one, 0: from the shape. ``wait_limit`` / ``tx_extra``: only for the test that makes a wait inside the kernel
+        run out."""
+        _cuda_contig("x", x, torch.bfloat16)
+        _cuda_contig("w", w, torch.bfloat16)
+        M, K = x.shape
+        N = w.shape[0]
+        _check(w.dim() == 2 and w.shape[1] == K and 0 < M <= self.FEWROWS_MAX_ROWS_KERNEL,
+               "gemm_fewrows: x [M<=128,K], w [N,K]")
+        if bias is not None:
+            _cuda_contig("bias", bias)
+            _check(bias.shape == (N,) and not swiglu, "gemm_fewrows: bias [N], none with the activation")
+        y = torch.empty((M, N // 2 if swiglu else N), dtype=torch.bfloat16, device=x.device)
+        rc = self.lib.osb_gemm_fewrows_tc(_p(y), _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, M, N, K,
+                                          1 if swiglu else 0, int(splits), int(form), _p(self.err_flag(x.device)),
+                                          int(wait_limit), int(tx_extra), self._stream())
+        self._ok(rc, "gemm_fewrows_tc")
+        return y
+
+    def can_gemm_fewrows(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> bool:
+        """Whether these operands may go to ``gemm_fewrows``: more rows than the streaming kernels take, few enough
+        that a 128-row tile of x would be mostly padding."""
+        M, K = x.shape
+        return (self.fewrows_tc and x.dtype == w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+                and self.SKINNY_MAX_ROWS < M <= self.fewrows_max_rows and K % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].
 
@@ -361,6 +403,11 @@ class CudaKernels(PersistentDecodeOps):
                                                self._stream())
             self._ok(rc, "gemm_skinny_bf16(swiglu)")
             return y
+        if self.can_gemm_fewrows(x, w, out_dtype) and M < self.tcgen05_min_rows_swiglu:
+            # (measured at 24 to 48 rows: 12.4 to 13.7 / 46 / 153 us at the three model sizes where the library and
+            # the activation kernel take 14.2 to 15.1 / 51 / 169; from 64 rows the kernel with 128-row tiles of x
+            # is as fast and then faster)
+            return self.gemm_fewrows(x, w, None, swiglu=True)
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows_swiglu and x.dtype == torch.bfloat16
                 and w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
                 and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):

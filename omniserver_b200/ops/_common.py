@@ -34,6 +34,9 @@ _DEVICE_ERR = {
     122: "tcgen05 GEMM (CTA pairs): the MMA issuer waited too long for operands",
     123: "tcgen05 GEMM (CTA pairs): the epilogue waited too long for the accumulator",
     124: "tcgen05 GEMM (CTA pairs): the MMA issuer waited too long for a drained accumulator",
+    151: "tcgen05 GEMM (few rows): the TMA producer waited too long for a free stage",
+    152: "tcgen05 GEMM (few rows): the MMA issuer waited too long for operands",
+    153: "tcgen05 GEMM (few rows): the epilogue waited too long for the accumulator",
     111: "tcgen05 attention: the TMA producer waited too long for a free key/value stage",
     112: "tcgen05 attention: the MMA issuer waited too long for operands",
     113: "tcgen05 attention: the softmax warps waited too long for scores or the output",

@@ -54,7 +54,7 @@ def bench_gemm(args, K, dev, peak) -> None:
             x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
             out_dt = torch.float32 if name == "head" else torch.bfloat16
             cols = []
-            for warps in args.warps if M <= 64 else []:
+            for warps in args.warps if M <= (16 if mode else 64) else []:
                 K.skinny_warps = warps
                 if mode:
                     us = graph_time_us(lambda i: K.gate_up_silu(x, ws[i], out_dt), n_rot)
@@ -81,9 +81,23 @@ def bench_gemm(args, K, dev, peak) -> None:
                     us1 = graph_time_us(lambda i: K.stream_linear(x, ws[i], None, norm=(res, gm, 1e-6)), n_rot)
                     txt = f"norm inside: {us1:7.1f} us | " + txt
                 cols.append(txt)
+            if name != "head" and 16 < M <= K.FEWROWS_MAX_ROWS_KERNEL:
+                for sp in args.splits:
+                    for form in ((1, 2) if mode and sp else (0,)):
+                        us = graph_time_us(lambda i: K.gemm_fewrows(x, ws[i], None, swiglu=bool(mode), splits=sp, form=form), n_rot)
+                        gbs = N * Kd * 2 / us / 1e3
+                        plan = K.lib.osb_gemm_fewrows_tc_plan(M, N, Kd, mode)
+                        what = f"K in {sp}" + (", 64 + 64 rows" if form == 2 else "") if sp else \
+                            f"its choice (K in {plan % 100}" + (", 64 + 64 rows)" if plan >= 100 else ")")
+                        cols.append(f"few rows, {what}: {us:7.1f} us {gbs:6.0f} GB/s {gbs / peak:4.2f}")
             if not mode:
                 us = graph_time_us(lambda i: torch.mm(x, ws[i].t()), n_rot)
                 cols.append(f"library: {us:7.1f} us {N * Kd * 2 / us / 1e3:6.0f} GB/s")
+            elif M > 16:
+                us = graph_time_us(lambda i: K.silu_mul(torch.mm(x, ws[i].t()), torch.bfloat16), n_rot)
+                cols.append(f"library + activation: {us:7.1f} us {N * Kd * 2 / us / 1e3:6.0f} GB/s")
+                us = graph_time_us(lambda i: K.gemm_tcgen05(x, ws[i], None, torch.bfloat16, swiglu=True, pairs=False), n_rot)
+                cols.append(f"128-row tiles of x: {us:7.1f} us {N * Kd * 2 / us / 1e3:6.0f} GB/s")
             print(f"{name:13s} M={M:3d} N={N:6d} K={Kd:5d} | " + " | ".join(cols), flush=True)
 
 
@@ -230,6 +244,7 @@ def main() -> None:
     ap.add_argument("--inter", type=int, default=8960)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--splits", default="0", help="parts of K of the few-rows GEMM to try (0 = its own choice)")
     ap.add_argument("--warps", default="0", help="K splits of the skinny GEMM to try (0 = its own choice)")
     ap.add_argument("--no-stream", action="store_true", help="decode attention: the shared-memory kernel instead of the streaming one")
     ap.add_argument("--no-clusters", action="store_true", help="decode attention: merge splits through global memory")
@@ -240,6 +255,7 @@ def main() -> None:
     args.rows = [int(b) for b in args.rows.split(",")]
     args.only = [x for x in args.only.split(",") if x]
     args.warps = [int(b) for b in args.warps.split(",")]
+    args.splits = [int(b) for b in args.splits.split(",")]
     args.target_ctas = [int(b) for b in args.target_ctas.split(",")]
     dev = torch.device("cuda:0")
     K = ops.kernels()

@@ -380,6 +380,93 @@ def test_gemm_tcgen05_swiglu(M, I, K_, pairs):
     assert_swiglu_close(got, x, w, I)
 
 
+@pytest.mark.parametrize("M,N,K_", [(64, 128, 64), (17, 2048, 1536), (64, 1536, 8960), (33, 264, 200), (40, 1000, 72), (128, 1536, 1536),
+                                    (100, 24, 520), (1, 130, 64), (64, 19072, 128)])
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 4, 5, 7, 8])
+def test_gemm_fewrows(M, N, K_, splits):
+    """The product with W on the M side of the MMA: tile-aligned and ragged shapes (rows of x below and at the
+    tile's 32, 64 and 128, features and K that are no multiples of the tile, more tiles than SMs), K whole and cut
+    into parts that a cluster adds up (more parts than K has blocks are cut back by the launcher)."""
+    x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(N, K_, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = rnd(N, dtype=torch.bfloat16, seed=2)
+    want0 = REF.linear(x.double(), w.double(), None, torch.float64)
+    for bias in (None, b, b.float()):
+        got = K().gemm_fewrows(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, splits=splits)
+        K().check_device_errors()
+        want = want0 if bias is None else want0 + bias.double()
+        assert got.shape == (M, N) and got.dtype == torch.bfloat16
+        assert torch.allclose(got.double().cpu(), want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("M,I,K_", [(64, 128, 64), (64, 8960, 1536), (24, 200, 96), (33, 176, 80), (128, 1000, 264), (50, 19000, 64)])
+@pytest.mark.parametrize("splits", [0, 1, 2, 6, 8])
+@pytest.mark.parametrize("form", [0, 1, 2])
+def test_gemm_fewrows_swiglu(M, I, K_, splits, form):
+    """With the activation, in both forms: 128 gate and 128 up rows per CTA in two accumulators, and 64 and 64 in the
+    two halves of one (gate and up of a feature then lie in different warps' lanes)."""
+    x, w = rnd(M, K_, dtype=torch.bfloat16), rnd(2 * I, K_, dtype=torch.bfloat16, seed=1, scale=0.1)
+    got = K().gemm_fewrows(x.to(DEV), w.to(DEV), None, swiglu=True, splits=splits, form=form)
+    K().check_device_errors()
+    assert got.shape == (M, I)
+    assert_swiglu_close(got, x, w, I)
+
+
+def test_gemm_fewrows_does_not_depend_on_the_other_rows():
+    """A row's result is the same bits whatever the other rows of the step are, and whichever of the tile's columns it
+    occupies: the parts of K are added in a fixed order."""
+    k = K()
+    x, w = rnd(64, 1536, dtype=torch.bfloat16), rnd(2048, 1536, dtype=torch.bfloat16, seed=1, scale=0.05)
+    full = k.gemm_fewrows(x.to(DEV), w.to(DEV))
+    part = k.gemm_fewrows(x[20:45].contiguous().to(DEV), w.to(DEV))
+    assert torch.equal(full[20:45], part)
+    x2 = x.clone()
+    x2[:20] = 7.0
+    assert torch.equal(k.gemm_fewrows(x2.to(DEV), w.to(DEV))[20:], full[20:])
+
+
+def test_products_of_17_to_64_rows_take_the_fewrows_kernel_where_it_was_measured_faster():
+    """``linear`` sends a long K over few features (a down projection) to the few-rows kernel and a squarer matrix
+    to the library; ``gate_up_silu`` sends 17 to 63 rows to it; the results agree with the plain product."""
+    k = K()
+    x = rnd(40, 1024, dtype=torch.bfloat16)
+    w_down, w_sq = rnd(256, 1024, dtype=torch.bfloat16, seed=1, scale=0.05), rnd(1024, 1024, dtype=torch.bfloat16, seed=2, scale=0.05)
+    before = k.counts["gemm_fewrows_tc"]
+    got = k.linear(x.to(DEV), w_down.to(DEV), None, torch.bfloat16)
+    assert k.counts["gemm_fewrows_tc"] == before + 1
+    assert torch.allclose(got.double().cpu(), REF.linear(x.double(), w_down.double(), None, torch.float64), **tol(torch.bfloat16))
+    got = k.linear(x.to(DEV), w_sq.to(DEV), None, torch.bfloat16)
+    assert k.counts["gemm_fewrows_tc"] == before + 1
+    assert torch.allclose(got.double().cpu(), REF.linear(x.double(), w_sq.double(), None, torch.float64), **tol(torch.bfloat16))
+    w_gu = rnd(2 * 320, 1024, dtype=torch.bfloat16, seed=3, scale=0.05)
+    got = k.gate_up_silu(x.to(DEV), w_gu.to(DEV), torch.bfloat16)
+    assert k.counts["gemm_fewrows_tc"] == before + 2
+    assert_swiglu_close(got, x, w_gu, 320)
+    k.check_device_errors()
+
+
+def test_a_wait_inside_the_fewrows_gemm_runs_out_and_reports():
+    """As for the other tcgen05 kernels: the producer announces 16 bytes more to every stage than it copies, so no
+    stage becomes full and the waits give up after 4,096 polls; the CTAs still meet their cluster at its barriers,
+    free their tensor memory and return, the host's check raises, and the same product launched normally is right."""
+    from omniserver_b200.ops import KernelError
+    x, w = rnd(48, 512, dtype=torch.bfloat16), rnd(384, 512, dtype=torch.bfloat16, seed=1, scale=0.05)
+    k = K()
+    k.check_device_errors()
+    for splits in (1, 4):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        k.gemm_fewrows(x.to(DEV), w.to(DEV), splits=splits, wait_limit=4096, tx_extra=16)
+        t1.record()
+        torch.cuda.synchronize()          # the kernel returned
+        assert t0.elapsed_time(t1) < 2000.0
+        with pytest.raises(KernelError, match=r"tcgen05 GEMM \(few rows\): the (MMA issuer|epilogue) waited too long"):
+            k.check_device_errors()
+        got = k.gemm_fewrows(x.to(DEV), w.to(DEV), splits=splits)
+        k.check_device_errors()
+        want = REF.linear(x.double(), w.double(), None, torch.float64)
+        assert torch.allclose(got.double().cpu(), want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(dtype):
     gu = rnd(5, 2 * 200, dtype=dtype, scale=3.0)
