@@ -194,7 +194,7 @@ def run_ours(args):
             r = b7.decode(8, max(8, args.steps // 2), max(3, args.warmup // 2), trials=args.trials)
             points.update({"7b_decode_b8": round(r["tokens_per_s"], 1), "7b_decode_b8_ms": round(r["ms_per_step"], 4),
                            "7b_decode_b8_frac": round(r["frac"], 4)})
-            m = b7.mixed()
+            m = b7.mixed(trials=args.trials)
             points.update({"7b_mixed_output_tok_s": m["output_tokens_per_s"], "7b_mixed_prefill_tok_s": m["prefill_tokens_per_s"],
                            "7b_mixed_frac": m["roofline_frac"], "7b_mixed_wall_s": m["wall_s"]})
             b7.close()
@@ -217,7 +217,7 @@ def run_ours(args):
     if args.workload == "mixed":
         bmx = bm.Bench(model, args.layers, 64, 4096, 320, args.page_size, pk, graphs=not args.no_graphs,
                        pool_tokens=64 * 4416 + 4096, max_requests=64)
-        line["mixed"] = bmx.mixed()
+        line["mixed"] = bmx.mixed(trials=args.trials)
         bmx.close()
     print(json.dumps(line))
     return 0

@@ -111,7 +111,8 @@ def cmd_bench(args) -> int:
         b = bm.Bench(args.model, args.layers, args.max_running, args.prompt_hi, args.max_new_tokens + 64, args.page_size, pk,
                      graphs=not args.no_cuda_graph, pool_tokens=args.max_running * (args.prompt_hi + args.max_new_tokens + 64) + 4096,
                      max_requests=args.max_running)
-        out = b.mixed(args.requests, args.prompt_lo, args.prompt_hi, args.max_new_tokens, args.chunk, args.max_running)
+        out = b.mixed(args.requests, args.prompt_lo, args.prompt_hi, args.max_new_tokens, args.chunk, args.max_running,
+                      trials=args.trials)
     elif args.what == "prefill":
         b = bm.Bench(args.model, args.layers, 1, args.tokens, 64, args.page_size, pk, graphs=not args.no_cuda_graph)
         out = b.prefill(args.tokens, trials=args.trials)

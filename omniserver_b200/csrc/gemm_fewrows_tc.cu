@@ -477,3 +477,11 @@ OSB_API int osb_gemm_fewrows_tc_plan(int M, int N, int K, int mode) {
   const int n_out = mode == 1 ? N / 2 : N;
   return M <= 32 ? plan<32>(n_out, K, mode) : M <= 64 ? plan<64>(n_out, K, mode) : plan<128>(n_out, K, mode);
 }
+
+// Asks the device once how many clusters of each size it holds (the answers are kept), so that no launch has to ask
+// while a CUDA graph is being captured.
+OSB_API int osb_gemm_fewrows_tc_prepare() {
+  for (int shallow = 0; shallow < 2; ++shallow)
+    for (int s = 2; s <= MAX_SPLITS; ++s) (void)active_clusters(shallow != 0, s);
+  return OSB_OK;
+}

@@ -71,6 +71,8 @@ class CudaKernels(PersistentDecodeOps):
         # product with its activation and for products with a long K over few features
         self.fewrows_tc = True
         self.fewrows_max_rows = 64
+        if torch.cuda.is_available():
+            self.lib.osb_gemm_fewrows_tc_prepare()   # its questions to the device, before any graph is captured
         self._pinned_stream: Optional[ctypes.c_void_p] = None
         # decode steps of up to 16 rows: the weight-streaming kernels (csrc/decode_stream.cu) for the feed-forward
         # half, for a projection with the norm in front of it, and for a plain projection

@@ -97,6 +97,9 @@ def test_replay_through_the_serving_kernels_of_decode_steps(family, tmp_path):
     if family in ("tail", "mixed"):
         for what in ("stream_ffn", "stream_linear", "attn_decode_stream"):
             assert counts.get(what, 0) > before.get(what, 0), f"{what} did not run in the {family} family"
+    if family == "portions":
+        # portions of 17 to 63 tokens: the gate/up product of the few-rows tcgen05 kernel
+        assert counts.get("gemm_fewrows_tc", 0) > before.get("gemm_fewrows_tc", 0)
     for rid, toks in reqs.items():
         want = pm.forward(cfg, w, torch.tensor(toks))
         assert torch.isfinite(got[rid]).all()
