@@ -211,6 +211,10 @@ def run_ours(args):
                                f"72b_decode_b{B}_frac": round(r["frac"], 4)})
             p72 = b72.prefill(CONTEXT, trials=3, warmup=1, back_to_back=1)
             points.update({"72b_prefill_tok_s": p72["value"], "72b_prefill_ms": p72["ms"], "72b_prefill_frac": p72["frac"]})
+            sustained = bm.read_sustained_tflops(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+            if sustained:
+                # a step of a quarter of a second runs under the power cap: also against the library's rate there
+                points["72b_prefill_frac_of_sustained"] = round(p72["tflops"] / sustained, 4)
             b72.close()
         except Exception as e:
             points["72b_error"] = f"{type(e).__name__}: {str(e)[:160]}"

@@ -55,6 +55,17 @@ def read_peaks(path: Optional[str]):
     return hbm, tf, "fallback"
 
 
+def read_sustained_tflops(path: Optional[str]) -> Optional[float]:
+    """The bf16 GEMM rate that the same file gives for a loop of seconds under the power cap, if it has one: the
+    denominator for a step that itself runs long enough to be power-limited."""
+    try:
+        with open(path) as f:
+            v = json.load(f).get("bf16_tflops_sustained")
+        return float(v) if v else None
+    except Exception:
+        return None
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
 
