@@ -129,7 +129,8 @@ def test_full_width_logits_match_plain_for_every_cut(dtype):
 
 def test_full_width_many_live_requests_bfloat16():
     """24 live requests at the real layer sizes: their prompts packed into two steps, then four steps that
-    decode all of them at once. That is the regime of the library GEMM (17 .. rows), of the streaming decode
+    decode all of them at once. That is the regime of the few-rows tcgen05 kernel (gate/up with its activation and
+    the down projection at 17 to 64 rows) and of the library GEMM (qkv, o), of the streaming decode
     attention with several splits merged through scratch memory, and of CUDA-graph replay at a batch size
     the other tests do not reach. Logits of every request at every decoded place against the plain model."""
     from omniserver_b200 import EngineConfig, build_runner
