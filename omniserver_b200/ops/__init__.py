@@ -54,6 +54,7 @@ class CudaKernels(PersistentDecodeOps):
         self.decode_clusters = True   # decode attention: merge a request's splits inside a cluster
         self.tc_prefill = True        # prompt attention on tcgen05 where the head size allows (64, 128)
         self.stream_max_splits = 32   # of the keys of one (request, kv head); batch 1 measured 2 % faster with 32 than 16
+        self.stream_max_splits_long = 64   # ... of very long requests
         self.decode_stream = True     # decode attention that streams K and V into MMA registers (head size 64, 128)
         self.stream_target_ctas = 148  # CTAs of that kernel the GPU holds at once (one per SM)
         self.stream_cluster_sizes = (2, 4)   # split counts merged inside a thread-block cluster
@@ -546,8 +547,11 @@ class CudaKernels(PersistentDecodeOps):
                 # scratch memory by the CTA that finishes last: a cluster of CTAs that each fill an SM has to wait
                 # until that many SMs of one GPC are free at once, which for 3 or 8 cost more than it saved
                 # (measured in full decode steps at batch 8 and 24)
+                # (one request of 32,768 / 131,072 keys: 16.4 / 48.4 us with 32 splits, 15.1 / 32.2 us with 47 / 64;
+                # of 8,192 keys: 8.4 us with 32, 9.2 with 43: a split should keep some 640 keys)
+                most = max(self.stream_max_splits, min(self.stream_max_splits_long, max_kv_len // 640))
                 chunk, nsplits = self.decode_splits(n_decode, nkv, nh // nkv, max_kv_len, self.stream_target_ctas,
-                                                    max_splits=self.stream_max_splits, uneven=uneven)
+                                                    max_splits=most, uneven=uneven)
                 use_cluster = 1 if self.decode_clusters and nsplits in self.stream_cluster_sizes else 0
                 if nsplits > 1 and not use_cluster and nsplits * n_decode * nkv > self.stream_target_ctas:
                     # the CTA that merges waits for the others: the grid must fit on the GPU at once

@@ -138,20 +138,20 @@ def bench_attn_decode(args, K, dev, peak) -> None:
         sl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
         ts = torch.arange(B, device=dev, dtype=torch.int32)
         pool = {}
-        for target in args.target_ctas:
-            orig = ops.CudaKernels.decode_splits
-            ops.CudaKernels.decode_splits = staticmethod(
-                lambda n, k, g, m, target_ctas=target, _o=orig, **kw: _o(n, k, g, m, target_ctas, **kw))
+        for target, K.stream_max_splits, K.stream_max_splits_long in [(t, m, max(m, 64)) for t in args.target_ctas for m in args.max_splits]:
+            keep = K.stream_target_ctas
+            K.stream_target_ctas = target
             try:
                 us = graph_time_us(lambda i: K.paged_attention(
                     qkv, kc[i], vc[i], bt, cu_q, sl, ts, nh, nkv, hd, hd ** -0.5, None, 1, ctx, torch.bfloat16,
                     decode_index=ts, n_decode=B, n_multi=0, scratch=pool), n_rot)
             finally:
-                ops.CudaKernels.decode_splits = orig
+                K.stream_target_ctas = keep
+            orig = ops.CudaKernels.decode_splits
             gbs = B * ctx * nkv * hd * 2 * 2 / us / 1e3
             stream = K.decode_stream and hd in (64, 128) and nh // nkv <= 8
             if stream:
-                chunk, nsp = orig(B, nkv, nh // nkv, ctx, K.stream_target_ctas, max_splits=16)
+                chunk, nsp = orig(B, nkv, nh // nkv, ctx, target, max_splits=max(K.stream_max_splits, min(K.stream_max_splits_long, ctx // 640)))
                 how = "streaming kernel, " + ("cluster merge" if nsp in K.stream_cluster_sizes else
                                               "one split" if nsp == 1 else "merge by the last CTA")
             else:
@@ -249,7 +249,8 @@ def main() -> None:
     ap.add_argument("--no-stream", action="store_true", help="decode attention: the shared-memory kernel instead of the streaming one")
     ap.add_argument("--no-clusters", action="store_true", help="decode attention: merge splits through global memory")
     ap.add_argument("--peak-gbs", type=float, default=6650.0, help="the copy bandwidth the fractions are taken of")
-    ap.add_argument("--target-ctas", default="296", help="CTA targets of the decode attention's key split to try")
+    ap.add_argument("--target-ctas", default="148", help="CTA targets of the decode attention's key split to try")
+    ap.add_argument("--max-splits", default="32", help="most splits of a request's keys to try")
     args = ap.parse_args()
     args.batch = [int(b) for b in args.batch.split(",")]
     args.rows = [int(b) for b in args.rows.split(",")]
@@ -257,6 +258,7 @@ def main() -> None:
     args.warps = [int(b) for b in args.warps.split(",")]
     args.splits = [int(b) for b in args.splits.split(",")]
     args.target_ctas = [int(b) for b in args.target_ctas.split(",")]
+    args.max_splits = [int(b) for b in args.max_splits.split(",")]
     dev = torch.device("cuda:0")
     K = ops.kernels()
     K.decode_clusters = not args.no_clusters

@@ -726,6 +726,31 @@ def test_decode_attention_finds_one_key_that_matters(window):
             assert got[0].abs().mean() < 2.0, f"key {j} must be invisible"
 
 
+def test_decode_attention_of_one_very_long_request_takes_more_splits():
+    """One request of 40,000 keys: its keys are cut into more than 32 splits (62 of 704 keys here), merged by the
+    CTA that finishes last. One key dominates, placed in the first, a middle and the last split and at split edges."""
+    nh, nkv, hd, ps, dtype = 12, 2, 128, 32, torch.bfloat16
+    kv_len = 40000
+    chunk, nsplits = K().decode_splits(1, nkv, nh // nkv, kv_len, K().stream_target_ctas,
+                                       max_splits=max(K().stream_max_splits, min(K().stream_max_splits_long, kv_len // 640)))
+    assert 32 < nsplits <= 64 and nsplits * nkv <= 148
+    for j in (0, chunk - 1, chunk, 20 * chunk + 5, (nsplits - 1) * chunk, kv_len - 1):
+        case = list(_paged_case([1], [kv_len], nh, nkv, hd, ps, dtype, seed=j + 1))
+        qkv, kc, vc, bt = case[0], case[1], case[2], case[3]
+        g = nh // nkv
+        for kvh in range(nkv):
+            qh = qkv[0, kvh * g * hd:(kvh * g + 1) * hd].float()
+            for h in range(kvh * g, (kvh + 1) * g):
+                qkv[0, h * hd:(h + 1) * hd] = qh.to(dtype)
+            kvec = qh / qh.norm() ** 2 * 40.0 * math.sqrt(hd)
+            page = int(bt[0, j // ps])
+            kc[page, kvh, j % ps] = kvec.to(dtype)
+            vc[page, kvh, j % ps] = 7.0
+        got, want = _run_attn(tuple(case), nh, nkv, hd, None, dtype)
+        assert torch.allclose(got, want, **tol(dtype)), f"key {j}"
+        assert got[0].mean() > 6.5, f"key {j} should dominate"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [None, 24])
 def test_paged_attention_finds_one_key_that_matters(dtype, window):
