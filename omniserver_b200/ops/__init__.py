@@ -35,6 +35,7 @@ class CudaKernels(PersistentDecodeOps):
     SKINNY_MAX_ROWS = 16
     SKINNY_TWO_TILE_MAX_ELEMS = 1 << 25   # 9 to 16 rows: matrices from 64 MB on go to the library
     FEWROWS_MAX_ROWS_KERNEL = 128         # what ``gemm_fewrows`` takes
+    FEWROWS_GATED_MIN_ROWS = 9            # a large gate/up matrix with its activation goes there from this many rows
     #: splits of a request's keys that one thread-block cluster of the decode attention merges
     CLUSTER_MAX_SPLITS = 8
 
@@ -68,8 +69,9 @@ class CudaKernels(PersistentDecodeOps):
         # from this many rows two CTAs share a 256-row tile (cta_group::2); measured cross-over with the
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
-        # 17 to this many rows: the tcgen05 kernel with W on the M side (csrc/gemm_fewrows_tc.cu) for the gate/up
-        # product with its activation and for products with a long K over few features
+        # up to this many rows: the tcgen05 kernel with W on the M side (csrc/gemm_fewrows_tc.cu) for the gate/up
+        # product with its activation (from 17 rows; a large matrix from 9) and for the plain products that
+        # ``prefer_gemm_fewrows`` names
         self.fewrows_tc = True
         self.fewrows_max_rows = 64
         if torch.cuda.is_available():
@@ -255,6 +257,8 @@ class CudaKernels(PersistentDecodeOps):
         M, K = x.shape
         N = w.shape[0]
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            if self.can_gemm_fewrows(x, w, out_dtype) and self.prefer_gemm_fewrows(M, N, K):
+                return self.gemm_fewrows(x, w, bias)
             if (self.stream_linear_decode and out_dtype == torch.bfloat16 and N <= self.STREAM_LINEAR_MAX_N
                     and self.can_stream_linear(x, w, bias)):
                 # a few rows: the weight-streaming kernel without a norm
@@ -299,11 +303,6 @@ class CudaKernels(PersistentDecodeOps):
             # (with 9 to 16 rows the kernel's two-column-tile form streams a large matrix, the head over the
             # vocabulary, at 0.71 to 0.74 of the copy rate where the library reaches 0.93)
             return self.gemm_skinny(x, w, bias, out_dtype)
-        if self.can_gemm_fewrows(x, w, out_dtype) and K >= 2 * N:
-            # (measured at 24 to 64 rows: a long K over few features, the down projection, runs in 11 to 12 / 27 to
-            # 28 / 76 to 79 us at the three model sizes where the library takes 14 / 30 to 31 / 73 to 81; squarer
-            # matrices run in 5 to 6 us in the library, at the floor of a dependent kernel, and 6 to 7 here)
-            return self.gemm_fewrows(x, w, bias)
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows and K % 8 == 0 and x.data_ptr() % 16 == 0
                 and w.data_ptr() % 16 == 0):
             return self.gemm_tcgen05(x, w, bias, out_dtype)
@@ -377,12 +376,24 @@ class CudaKernels(PersistentDecodeOps):
         return y
 
     def can_gemm_fewrows(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> bool:
-        """Whether these operands may go to ``gemm_fewrows``: more rows than the streaming kernels take, few enough
-        that a 128-row tile of x would be mostly padding."""
+        """Whether these operands may go to ``gemm_fewrows``: bf16, few enough rows that a 128-row tile of x would
+        be mostly padding, and what TMA asks of the addresses."""
         M, K = x.shape
         return (self.fewrows_tc and x.dtype == w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
-                and self.SKINNY_MAX_ROWS < M <= self.fewrows_max_rows and K % 8 == 0
+                and 0 < M <= self.fewrows_max_rows and K % 8 == 0
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def prefer_gemm_fewrows(self, M: int, N: int, K: int) -> bool:
+        """Whether a plain product of these sizes is faster in ``gemm_fewrows`` than in the streaming kernels (up to
+        16 rows) or the library (more). Measured on a B200, us: at 24 to 64 rows a long K over few features (the
+        down projections) 11 to 12 / 27 to 28 / 76 to 79 at the three model sizes against the library's 14 / 30 to
+        31 / 73 to 81, squarer matrices of a few MB 6 to 7 against 5 (the floor of a kernel that depends on the one
+        in front); at 1 to 16 rows matrices from 64 MB on (7B down; 72B qkv, o, down) 26 / 29 to 31, 24 to 26, 74
+        to 75 against the streaming kernel's 26 to 27 / 31 to 32, 26 to 27, 79 to 82, smaller ones (2B down) 10.8
+        against 7.6."""
+        if M > self.SKINNY_MAX_ROWS:
+            return K >= 2 * N
+        return N * K >= self.SKINNY_TWO_TILE_MAX_ELEMS and N <= self.STREAM_LINEAR_MAX_N
 
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].
@@ -396,6 +407,14 @@ class CudaKernels(PersistentDecodeOps):
                "gate_up_silu: x [M,K], w [2I,K]")
         M, K = x.shape
         N = w.shape[0]
+        if (self.can_gemm_fewrows(x, w, out_dtype) and M < self.tcgen05_min_rows_swiglu
+                and (M > self.SKINNY_MAX_ROWS
+                     or (M >= self.FEWROWS_GATED_MIN_ROWS and N * K >= self.SKINNY_TWO_TILE_MAX_ELEMS))):
+            # (measured, us at the three model sizes: 24 to 48 rows 12.4 to 13.7 / 46 / 153 against 14.2 to 15.1 /
+            # 51 / 169 of the library and the activation kernel; from 64 rows the kernel with 128-row tiles of x is
+            # as fast and then faster; 9 to 16 rows 12.1 / 45 / 152 against the streaming kernel's 12.2 / 53 / 155,
+            # but inside a step the 2B size lost 3 % there, so only matrices from 64 MB on)
+            return self.gemm_fewrows(x, w, None, swiglu=True)
         if self.stream_linear_decode and out_dtype == torch.bfloat16 and self.can_stream_linear(x, w, None):
             # a few rows: the weight-streaming kernel (as fast as the skinny one at 8 rows, ahead of it from 9)
             return self.stream_linear(x, w, None, gated=True)
@@ -406,11 +425,6 @@ class CudaKernels(PersistentDecodeOps):
                                                self._stream())
             self._ok(rc, "gemm_skinny_bf16(swiglu)")
             return y
-        if self.can_gemm_fewrows(x, w, out_dtype) and M < self.tcgen05_min_rows_swiglu:
-            # (measured at 24 to 48 rows: 12.4 to 13.7 / 46 / 153 us at the three model sizes where the library and
-            # the activation kernel take 14.2 to 15.1 / 51 / 169; from 64 rows the kernel with 128-row tiles of x
-            # is as fast and then faster)
-            return self.gemm_fewrows(x, w, None, swiglu=True)
         if (self.use_tcgen05 and M >= self.tcgen05_min_rows_swiglu and x.dtype == torch.bfloat16
                 and w.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
                 and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):

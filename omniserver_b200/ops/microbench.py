@@ -81,7 +81,7 @@ def bench_gemm(args, K, dev, peak) -> None:
                     us1 = graph_time_us(lambda i: K.stream_linear(x, ws[i], None, norm=(res, gm, 1e-6)), n_rot)
                     txt = f"norm inside: {us1:7.1f} us | " + txt
                 cols.append(txt)
-            if name != "head" and 16 < M <= K.FEWROWS_MAX_ROWS_KERNEL:
+            if name != "head" and M <= K.FEWROWS_MAX_ROWS_KERNEL:
                 for sp in args.splits:
                     for form in ((1, 2) if mode and sp else (0,)):
                         us = graph_time_us(lambda i: K.gemm_fewrows(x, ws[i], None, swiglu=bool(mode), splits=sp, form=form), n_rot)

@@ -424,9 +424,10 @@ def test_gemm_fewrows_does_not_depend_on_the_other_rows():
     assert torch.equal(k.gemm_fewrows(x2.to(DEV), w.to(DEV))[20:], full[20:])
 
 
-def test_products_of_17_to_64_rows_take_the_fewrows_kernel_where_it_was_measured_faster():
-    """``linear`` sends a long K over few features (a down projection) to the few-rows kernel and a squarer matrix
-    to the library; ``gate_up_silu`` sends 17 to 63 rows to it; the results agree with the plain product."""
+def test_products_of_few_rows_take_the_fewrows_kernel_where_it_was_measured_faster():
+    """``linear`` sends 17 to 64 rows over a long K and few features (a down projection) to the few-rows kernel and a
+    squarer matrix to the library, and up to 16 rows only over a large matrix; ``gate_up_silu`` sends 17 to 63 rows
+    to it, and 9 to 16 over a large matrix; the results agree with the plain product."""
     k = K()
     x = rnd(40, 1024, dtype=torch.bfloat16)
     w_down, w_sq = rnd(256, 1024, dtype=torch.bfloat16, seed=1, scale=0.05), rnd(1024, 1024, dtype=torch.bfloat16, seed=2, scale=0.05)
@@ -441,6 +442,25 @@ def test_products_of_17_to_64_rows_take_the_fewrows_kernel_where_it_was_measured
     got = k.gate_up_silu(x.to(DEV), w_gu.to(DEV), torch.bfloat16)
     assert k.counts["gemm_fewrows_tc"] == before + 2
     assert_swiglu_close(got, x, w_gu, 320)
+    # up to 16 rows: only over matrices of 64 MB and more (gate/up from 9 rows)
+    n0 = k.counts["gemm_fewrows_tc"]
+    got = k.gate_up_silu(x[:12].contiguous().to(DEV), w_gu.to(DEV), torch.bfloat16)
+    assert k.counts["gemm_fewrows_tc"] == n0
+    assert_swiglu_close(got, x[:12], w_gu, 320)
+    xg, w_gu_big = rnd(12, 4096, dtype=torch.bfloat16, seed=6), rnd(2 * 4096, 4096, dtype=torch.bfloat16, seed=7, scale=0.03)
+    for rows, expect in ((12, 1), (8, 0)):
+        n0 = k.counts["gemm_fewrows_tc"]
+        got = k.gate_up_silu(xg[:rows].contiguous().to(DEV), w_gu_big.to(DEV), torch.bfloat16)
+        assert k.counts["gemm_fewrows_tc"] == n0 + expect
+        assert_swiglu_close(got, xg[:rows], w_gu_big, 4096)
+    xb, w_big = rnd(12, 8192, dtype=torch.bfloat16, seed=4), rnd(4096, 8192, dtype=torch.bfloat16, seed=5, scale=0.02)
+    n0 = k.counts["gemm_fewrows_tc"]
+    got = k.linear(xb.to(DEV), w_big.to(DEV), None, torch.bfloat16)
+    assert k.counts["gemm_fewrows_tc"] == n0 + 1
+    assert torch.allclose(got.double().cpu(), REF.linear(xb.double(), w_big.double(), None, torch.float64), **tol(torch.bfloat16))
+    got = k.linear(x[:12].contiguous().to(DEV), w_down.to(DEV), None, torch.bfloat16)
+    assert k.counts["gemm_fewrows_tc"] == n0 + 1
+    assert torch.allclose(got.double().cpu(), REF.linear(x[:12].double(), w_down.double(), None, torch.float64), **tol(torch.bfloat16))
     k.check_device_errors()
 
 
