@@ -121,7 +121,8 @@ class ModelRunner:
         #: request) are many, and most come by once
         self.graph_min_uses_prompt = 3
         self.graph_min_free_bytes = 8 << 30     # no new graph for such a step with less free device memory than this
-        self._graph_seen: Dict[Any, int] = {}
+        self.graph_use_window = 64              # steps within which a shape has to come back for its uses to add up
+        self._graph_seen: Dict[Any, Tuple[int, int]] = {}    # shape -> (uses that followed one another, step of the last)
         #: rows that pad a decode step to the next batch size for which graphs are kept (``_graph_bucket``): requests
         #: of one token at position 0 on spare state slots, whose page goes back after every step
         self._filler_ids: List[str] = []
@@ -567,10 +568,14 @@ class ModelRunner:
         if slot is None and min_uses > 1:
             # Building a graph costs about as much as ten steps (a warm-up forward, a wait for the device, the
             # capture): a shape that comes by once or twice is launched kernel by kernel instead.
+            # And only uses that follow one another within ``graph_use_window`` steps count: shapes that a workload
+            # brings back now and then (the same requests served again a few hundred steps later) would otherwise
+            # all be built on their third visit, more of them than are kept, each built again on its next.
             if len(self._graph_seen) > 4096:
                 self._graph_seen.clear()
-            seen = self._graph_seen.get(key, 0) + 1
-            self._graph_seen[key] = seen
+            seen, last = self._graph_seen.get(key, (0, self.steps))
+            seen = seen + 1 if self.steps - last <= self.graph_use_window else 1
+            self._graph_seen[key] = (seen, self.steps)
             if seen < min_uses:
                 return self._planned_step(real, plan, fill)
         if slot is not None:

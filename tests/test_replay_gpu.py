@@ -225,6 +225,41 @@ def test_a_decode_graph_may_wait_until_its_shape_comes_back(tmp_path):
         check(torch.stack([got[r][p] for p in rows]), want[rows], "bfloat16", f"late graphs/{r}")
 
 
+def test_only_uses_that_follow_one_another_count_towards_a_graph(tmp_path):
+    """Two shapes of decode step in turn, each coming back every second step: with ``graph_use_window`` = 1 their
+    uses never add up and no graph is built (a workload that brings many shapes back now and then must not build
+    them all, more than are kept, again and again); with a window of 2 both get their graph on their next use."""
+    from omniserver_b200.engine.step import StepEntry
+    d = make_model_dir(tmp_path, "tiny_b", "bfloat16")
+    cfg, w = plain_model(d)
+    reqs = requests_for(cfg.V, (40, 33), seed=37)
+    runner = runner_for(d, "bfloat16", 512)
+    runner.graph_min_uses, runner.graph_min_uses_prompt, runner.graph_use_window = 2, 0, 1
+    names = list(reqs)
+    got = {r: {} for r in reqs}
+    n_graphs = []
+    with torch.inference_mode():
+        for r, toks in reqs.items():
+            runner.start_request(r)
+            runner.step([StepEntry(r, toks[:20], want=[])])
+        pos = {r: 20 for r in reqs}
+        for i, live in enumerate([names, names[:1]] * 5):
+            if i == 6:
+                runner.graph_use_window = 2
+            lg = runner.step([StepEntry(r, [reqs[r][pos[r]]], want=[0]) for r in live]).float().cpu()
+            for j, r in enumerate(live):
+                got[r][pos[r]] = lg[j]
+                pos[r] += 1
+            n_graphs.append(len(runner._graphs))
+        for r in reqs:
+            runner.end_request(r)
+    assert n_graphs == [0, 0, 0, 0, 0, 0, 1, 2, 2, 2], n_graphs     # (the use two steps back counts once the window is 2)
+    for r, toks in reqs.items():
+        want = pm.forward(cfg, w, torch.tensor(toks))
+        rows = sorted(got[r])
+        check(torch.stack([got[r][p] for p in rows]), want[rows], "bfloat16", f"graph window/{r}")
+
+
 def test_decode_steps_are_padded_to_the_batch_sizes_of_graphs(tmp_path):
     """Eleven, nine, five and then four decoding requests: the steps of eleven and of nine replay the graph of sixteen
     rows, that of five the graph of eight, padded with rows that are no requests (spare state slots, a page that
