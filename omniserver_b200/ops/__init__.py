@@ -33,9 +33,11 @@ class CudaKernels(PersistentDecodeOps):
     #: rows up to which the bf16 weight-streaming GEMM is used instead of the tiled tensor-core GEMM
     #: (measured on B200: it wins up to 16 rows, the library GEMM from 32 rows on)
     SKINNY_MAX_ROWS = 16
-    SKINNY_TWO_TILE_MAX_ELEMS = 1 << 25   # 9 to 16 rows: matrices from 64 MB on go to the library
+    #: matrices from 64 MB on: at up to 16 rows they go to the few-rows tcgen05 kernel (the head over the vocabulary,
+    #: with its fp32 logits, to the library from 9 rows) instead of the streaming and skinny kernels
+    LARGE_MATRIX_ELEMS = 1 << 25
     FEWROWS_MAX_ROWS_KERNEL = 128         # what ``gemm_fewrows`` takes
-    FEWROWS_GATED_MIN_ROWS = 9            # a large gate/up matrix with its activation goes there from this many rows
+    FEWROWS_GATED_MIN_ROWS = 1            # a large gate/up matrix with its activation goes there from this many rows
     #: splits of a request's keys that one thread-block cluster of the decode attention merges
     CLUSTER_MAX_SPLITS = 8
 
@@ -70,7 +72,7 @@ class CudaKernels(PersistentDecodeOps):
         # one-CTA kernel: about 2,000 rows for the fused SwiGLU form, 4,000 for the others
         self.tcgen05_pair_min_rows = 4096
         # up to this many rows: the tcgen05 kernel with W on the M side (csrc/gemm_fewrows_tc.cu) for the gate/up
-        # product with its activation (from 17 rows; a large matrix from 9) and for the plain products that
+        # product with its activation (from 17 rows; a large matrix from one row) and for the plain products that
         # ``prefer_gemm_fewrows`` names
         self.fewrows_tc = True
         self.fewrows_max_rows = 64
@@ -299,7 +301,7 @@ class CudaKernels(PersistentDecodeOps):
                      ) -> torch.Tensor:
         M, K = x.shape
         N = w.shape[0]
-        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and (M <= 8 or N * K < self.SKINNY_TWO_TILE_MAX_ELEMS or N % 8 != 0):
+        if M <= self.SKINNY_MAX_ROWS and K % 8 == 0 and (M <= 8 or N * K < self.LARGE_MATRIX_ELEMS or N % 8 != 0):
             # (with 9 to 16 rows the kernel's two-column-tile form streams a large matrix, the head over the
             # vocabulary, at 0.71 to 0.74 of the copy rate where the library reaches 0.93)
             return self.gemm_skinny(x, w, bias, out_dtype)
@@ -393,7 +395,7 @@ class CudaKernels(PersistentDecodeOps):
         against 7.6."""
         if M > self.SKINNY_MAX_ROWS:
             return K >= 2 * N
-        return N * K >= self.SKINNY_TWO_TILE_MAX_ELEMS and N <= self.STREAM_LINEAR_MAX_N
+        return N * K >= self.LARGE_MATRIX_ELEMS and N <= self.STREAM_LINEAR_MAX_N
 
     def gate_up_silu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for w = [Wg; Wu] of shape [2I, K]: y [M, I].
@@ -409,11 +411,11 @@ class CudaKernels(PersistentDecodeOps):
         N = w.shape[0]
         if (self.can_gemm_fewrows(x, w, out_dtype) and M < self.tcgen05_min_rows_swiglu
                 and (M > self.SKINNY_MAX_ROWS
-                     or (M >= self.FEWROWS_GATED_MIN_ROWS and N * K >= self.SKINNY_TWO_TILE_MAX_ELEMS))):
+                     or (M >= self.FEWROWS_GATED_MIN_ROWS and N * K >= self.LARGE_MATRIX_ELEMS))):
             # (measured, us at the three model sizes: 24 to 48 rows 12.4 to 13.7 / 46 / 153 against 14.2 to 15.1 /
             # 51 / 169 of the library and the activation kernel; from 64 rows the kernel with 128-row tiles of x is
-            # as fast and then faster; 9 to 16 rows 12.1 / 45 / 152 against the streaming kernel's 12.2 / 53 / 155,
-            # but inside a step the 2B size lost 3 % there, so only matrices from 64 MB on)
+            # as fast and then faster; up to 16 rows 12.1 / 45 / 151 against the streaming kernel's 12.2 / 50 to 53 /
+            # 151 to 155, but inside a step the 2B size lost 3 % there, so only matrices from 64 MB on)
             return self.gemm_fewrows(x, w, None, swiglu=True)
         if self.stream_linear_decode and out_dtype == torch.bfloat16 and self.can_stream_linear(x, w, None):
             # a few rows: the weight-streaming kernel (as fast as the skinny one at 8 rows, ahead of it from 9)

@@ -97,12 +97,18 @@ class PersistentDecodeOps:
     STREAM_FFN_PREFER_ROWS = 8
     STREAM_FFN_PREFER_WIDTH = 3584
 
-    def prefer_stream_ffn(self, x: torch.Tensor) -> bool:
+    def prefer_stream_ffn(self, x: torch.Tensor, w_gate_up: Optional[torch.Tensor] = None) -> bool:
         """Whether the one-kernel feed-forward half is the faster form for these rows. Measured on a B200 against
         add + norm, gate/up with the activation, down as three streaming kernels (us, 1 / 8 / 16 rows): width 1,536:
         17.6 / 18.5 / 25.4 against 20.2 / 19.7 / 21.8; width 3,584: 70 / 73 / 94 against 78 / 78 / 82; width 4,096 (and
         14,336 between): - / 69.5 / - against - / 65.2 / -; width 8,192: 296 / 299 / - against 230 / 235 / 239. The one kernel keeps the normalised rows in shared memory beside its
-        weight tiles: with 16 rows (two column tiles) or rows of 8,192 elements too little is left for the tiles."""
+        weight tiles: with 16 rows (two column tiles) or rows of 8,192 elements too little is left for the tiles.
+        Where the gate/up matrix is large enough for the few-rows tcgen05 kernel (64 MB: the 7B size) the norm
+        kernel and that kernel for both products are faster still: a 7B decode step of 1 / 8 requests 2.996 / 3.216
+        -> 2.966 / 3.153 ms (72B, which never took the one kernel, 24.24 / 25.55 -> 24.09 / 25.36 ms)."""
+        if (w_gate_up is not None and getattr(self, "fewrows_tc", False)
+                and w_gate_up.numel() >= self.LARGE_MATRIX_ELEMS):
+            return False
         return x.shape[0] <= self.STREAM_FFN_PREFER_ROWS and x.shape[1] <= self.STREAM_FFN_PREFER_WIDTH
 
     def stream_ffn(self, x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,

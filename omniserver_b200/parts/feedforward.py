@@ -37,7 +37,7 @@ class SwiGLU(FeedForward):
         k = ops.kernels()
         rms = norm.rms_operands()
         if (rms is not None and k.can_stream_ffn(x, rms[0], self.gate_up.weight, self.down.weight)
-                and k.prefer_stream_ffn(x)):
+                and k.prefer_stream_ffn(x, self.gate_up.weight)):
             return k.stream_ffn(x, residual, rms[0], rms[1], self.gate_up.weight, self.down.weight)
         return super().forward_prenorm(ctx, x, residual, norm)
 
